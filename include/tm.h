@@ -1,0 +1,152 @@
+/*
+ * tm.h - the C ABI of libtmcuda.
+ *
+ * libtmcuda is a CUDA (sm_100a) implementation of the two hot kernels of
+ * triton-metal - the tl.dot matmul and FlashAttention-2 forward/backward -
+ * behind that project's handle-based `tm_*` C ABI.  The 23 `tm_*` functions
+ * below have the signatures the reference's ctypes shim binds
+ * (python/triton_metal/_core.py:70-100); each comment names the reference
+ * export it replaces.  Everything prefixed `tmx_` is additive: the reference
+ * has no counterpart, and no `tm_*` signature depends on it.
+ *
+ * Conventions (Sources/TritonMetalCore/Compiler.swift:172-177):
+ *   - a returned `char*` is malloc'd; the caller releases it with tm_free;
+ *   - handle-returning calls give 0 on failure, status calls give -1;
+ *   - the reason for the most recent failure is read (and cleared) by
+ *     tm_last_error, which returns "no error" when nothing is stored;
+ *   - handles are int64 values from one process-wide table, the first is 1;
+ *   - no call throws, aborts or longjmps across the boundary.
+ */
+#ifndef TM_H
+#define TM_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- strings, errors, device ------------------------------------------- */
+
+/* "0.0.1".  Replaces tm_version, Compiler.swift:180-183. */
+char *tm_version(void);
+/* free() for strings this library returned.  Replaces tm_free, Compiler.swift:185-188. */
+void tm_free(void *ptr);
+/* Take and clear the last error.  Replaces tm_last_error, Compiler.swift:456-459. */
+char *tm_last_error(void);
+/* 1 when a CUDA device is present.  Replaces tm_is_active, Runtime.swift:295-298. */
+int32_t tm_is_active(void);
+/* 1 when the selected device runs sm_100a code (probe kernel launched once and
+ * cached).  Replaces tm_is_usable, Runtime.swift:305-308. */
+int32_t tm_is_usable(void);
+/* Why tm_is_usable is 0, or NULL.  Replaces tm_unusable_reason, Runtime.swift:312-315. */
+char *tm_unusable_reason(void);
+/* Device name, or NULL without a device.  Replaces tm_device_name, Runtime.swift:318-321. */
+char *tm_device_name(void);
+
+/* ---- "compiler": Triton IR text -> kernel descriptor -------------------- */
+
+/* Scan the tt.func signature (and the first tt.dot / rank-2 tensor type) of
+ * `ttir` and return a kernel descriptor text - not MSL, and not a compiler:
+ * the kernels are precompiled sm_100a functions selected by entry name and
+ * element type.  `num_simdgroups` is accepted for signature compatibility and
+ * only echoed into threads_per_threadgroup.  NULL on failure.
+ * Replaces tm_emit_msl, Compiler.swift:192-210. */
+char *tm_emit_msl(const char *ttir, int32_t num_simdgroups);
+/* Launch metadata as JSON: {"kernels":[{"name","block_size","block_shape",
+ * "threads_per_threadgroup","args":[{"index","kind","dtype"}]}]}.
+ * Replaces tm_kernel_info, Compiler.swift:214-232 (JSON shape :146-170). */
+char *tm_kernel_info(const char *ttir, int32_t num_simdgroups);
+/* Turn a descriptor returned by tm_emit_msl into a library handle.
+ * Replaces tm_compile_msl, Compiler.swift:235-247. */
+int64_t tm_compile_msl(const char *source);
+/* Same, from a byte image of the descriptor (the cached-binary path).
+ * Replaces tm_load_metallib, Compiler.swift:250-263. */
+int64_t tm_load_metallib(const void *bytes, int64_t length);
+/* Replaces tm_release_library, Compiler.swift:383-386. */
+int32_t tm_release_library(int64_t library);
+
+/* ---- runtime ------------------------------------------------------------ */
+
+/* Bind `name` in `library` to its precompiled function.  Unknown names fail with
+ * "kernel 'x' not found in library (available: ...)".
+ * Replaces tm_load_kernel, Compiler.swift:266-281. */
+int64_t tm_load_kernel(int64_t library, const char *name);
+/* 1024, or -1.  Replaces tm_kernel_max_threads, Compiler.swift:284-293. */
+int64_t tm_kernel_max_threads(int64_t kernel);
+/* Replaces tm_release_kernel, Compiler.swift:378-381. */
+int32_t tm_release_kernel(int64_t kernel);
+/* Allocate `nbytes` of memory that both the host and the GPU address (CUDA
+ * managed memory, resident on the device until the host touches it).
+ * nbytes <= 0 is an error.  Replaces tm_alloc_buffer, Compiler.swift:296-304. */
+int64_t tm_alloc_buffer(int64_t nbytes);
+/* Host-addressable pointer to the buffer, valid until tm_free_buffer.
+ * Replaces tm_buffer_contents, Compiler.swift:307-315. */
+void *tm_buffer_contents(int64_t buffer);
+/* Replaces tm_buffer_length, Compiler.swift:317-325. */
+int64_t tm_buffer_length(int64_t buffer);
+/* Bounds-checked host -> buffer copy.  Replaces tm_buffer_write, Compiler.swift:328-335. */
+int32_t tm_buffer_write(int64_t buffer, int64_t offset, const void *source, int64_t length);
+/* Bounds-checked buffer -> host copy.  Replaces tm_buffer_read, Compiler.swift:338-348. */
+int32_t tm_buffer_read(int64_t buffer, int64_t offset, void *destination, int64_t length);
+/* Replaces tm_free_buffer, Compiler.swift:373-376. */
+int32_t tm_free_buffer(int64_t buffer);
+/* Run `kernel` and wait for it.  Argument i is tt.func argument i; kinds:
+ * 0 buffer handle, 1 i32 (low 32 bits), 2 f32 bit pattern (low 32 bits), 3 i64.
+ * grid_x/grid_y keep the reference's meaning (one program per block of the
+ * descriptor's BLOCK shape; grid_y is batch*heads for the attention kernels):
+ * rows or columns beyond grid*BLOCK are not computed, exactly as if those
+ * programs had not been dispatched.  The CUDA kernels choose their own CTA
+ * shape.  Replaces tm_launch, Compiler.swift:403-448 + Runtime.swift:195-243. */
+int32_t tm_launch(int64_t kernel, int64_t grid_x, int64_t grid_y, int64_t grid_z,
+                  int64_t threads_per_threadgroup, const int32_t *kinds,
+                  const int64_t *values, int32_t arg_count);
+/* Replaces tm_live_handle_count, Compiler.swift:451-454. */
+int64_t tm_live_handle_count(void);
+
+/* ---- additive entry points (no counterpart in the reference) ------------- */
+
+/* Select the CUDA device for this process (one process per GPU).  Must come
+ * before the first allocation or launch; default is $TMCUDA_DEVICE or 0. */
+int32_t tmx_set_device(int32_t ordinal);
+int32_t tmx_get_device(void);
+/* Number of streaming multiprocessors of the selected device, or -1. */
+int32_t tmx_sm_count(void);
+/* Set an integer option on a loaded kernel.  Known options: "causal" (attention
+ * kernels: mask key j > query i), "path" (0 = automatic, 1 = force the generic
+ * SIMT kernel, 2 = require the tcgen05 kernel and fail if the shape is not
+ * eligible).  0 / -1. */
+int32_t tmx_kernel_set_option(int64_t kernel, const char *name, int64_t value);
+/* Which implementation the most recent launch of `kernel` used:
+ * 0 none yet, 1 generic SIMT, 2 tcgen05.  -1 on a bad handle. */
+int32_t tmx_kernel_last_path(int64_t kernel);
+/* tm_launch without the wait: enqueue on the library's stream and return. */
+int32_t tmx_launch_async(int64_t kernel, int64_t grid_x, int64_t grid_y, int64_t grid_z,
+                         int64_t threads_per_threadgroup, const int32_t *kinds,
+                         const int64_t *values, int32_t arg_count);
+/* Enqueue `repeats` back-to-back launches between two CUDA events on the
+ * library's stream, wait, and store the elapsed milliseconds for all of them in
+ * *elapsed_ms (the reference packs `repeats` dispatches into one command buffer
+ * the same way: Sources/TritonMetalBench/GEMMBenchmark.swift:256-277). */
+int32_t tmx_launch_timed(int64_t kernel, int64_t grid_x, int64_t grid_y, int64_t grid_z,
+                         int64_t threads_per_threadgroup, const int32_t *kinds,
+                         const int64_t *values, int32_t arg_count, int32_t repeats,
+                         float *elapsed_ms);
+/* Wait for everything enqueued on the library's stream; surfaces device-side
+ * status words (bounded waits that gave up) as -1. */
+int32_t tmx_synchronize(void);
+/* Asynchronous copies on the library's stream (host memory should be pinned). */
+int32_t tmx_buffer_write_async(int64_t buffer, int64_t offset, const void *source, int64_t length);
+int32_t tmx_buffer_read_async(int64_t buffer, int64_t offset, void *destination, int64_t length);
+/* Fill `length` bytes of the buffer with `byte` (asynchronous). */
+int32_t tmx_buffer_fill(int64_t buffer, int64_t offset, int32_t byte, int64_t length);
+/* Event pair on the library's stream: begin/end bracket a timed region. */
+int32_t tmx_timer_begin(void);
+int32_t tmx_timer_end(float *elapsed_ms);
+/* Count of kernels this library has launched since load (for launch accounting). */
+int64_t tmx_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TM_H */

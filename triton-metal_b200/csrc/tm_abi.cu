@@ -1,0 +1,912 @@
+// The tm_* C ABI of libtmcuda: handle table, error slot, buffers, descriptor
+// "libraries", and launch marshalling.  Mirrors the behaviour of the reference's
+// exports (Sources/TritonMetalCore/Compiler.swift:172-479 and
+// Sources/TritonMetalCore/Runtime.swift:250-321) over the CUDA runtime.
+
+#include "../../include/tm.h"
+#include "tm_core.h"
+
+#include <algorithm>
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+using namespace tmc;
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// Last-error slot: one per process, lock protected, cleared by tm_last_error
+// (Compiler.swift:461-479).
+// ---------------------------------------------------------------------------
+std::mutex g_error_lock;
+std::string g_error;
+bool g_has_error = false;
+
+void store_error(const std::string& message) {
+  std::lock_guard<std::mutex> guard(g_error_lock);
+  g_error = message;
+  g_has_error = true;
+}
+
+char* dup_string(const std::string& s) {
+  char* out = (char*)std::malloc(s.size() + 1);
+  if (out) std::memcpy(out, s.c_str(), s.size() + 1);
+  return out;
+}
+
+std::string invalid_argument(const std::string& m) { return "invalid argument: " + m; }
+std::string invalid_handle(const std::string& m) { return "invalid handle: " + m; }
+std::string cuda_error(const std::string& m) { return "metal error: " + m; }  // CoreError.metal wording
+
+// ---------------------------------------------------------------------------
+// Objects behind handles
+// ---------------------------------------------------------------------------
+enum class ObjKind { Library, Kernel, Buffer };
+
+struct Object {
+  ObjKind kind;
+  virtual ~Object() {}
+  explicit Object(ObjKind k) : kind(k) {}
+};
+
+struct LibraryObj : Object {
+  std::vector<KernelDesc> kernels;
+  LibraryObj() : Object(ObjKind::Library) {}
+};
+
+struct KernelObj : Object {
+  KernelDesc desc;
+  int path_option = 0;   // 0 auto, 1 SIMT, 2 tcgen05 required
+  int last_path = 0;
+  KernelObj() : Object(ObjKind::Kernel) {}
+};
+
+struct BufferObj : Object {
+  void* ptr = nullptr;
+  int64_t length = 0;
+  bool host_exposed = false;   // tm_buffer_contents handed the pointer to the host
+  BufferObj() : Object(ObjKind::Buffer) {}
+  ~BufferObj() override {
+    if (ptr) cudaFree(ptr);
+  }
+};
+
+const char* kind_word(ObjKind k) {
+  return k == ObjKind::Library ? "library" : (k == ObjKind::Kernel ? "kernel" : "buffer");
+}
+
+// One process-wide table; handle 0 is never valid; first handle is 1
+// (Runtime.swift:250-290).
+class HandleTable {
+ public:
+  int64_t insert(std::shared_ptr<Object> obj) {
+    std::lock_guard<std::mutex> guard(lock_);
+    int64_t h = next_++;
+    table_[h] = std::move(obj);
+    return h;
+  }
+  // Typed lookup with the reference's two messages.
+  std::shared_ptr<Object> lookup(int64_t handle, ObjKind kind, std::string& err) {
+    std::lock_guard<std::mutex> guard(lock_);
+    auto it = table_.find(handle);
+    if (it == table_.end()) {
+      err = invalid_handle(std::string(kind_word(kind)) + " handle " + std::to_string(handle) +
+                           " is not live");
+      return nullptr;
+    }
+    if (it->second->kind != kind) {
+      err = invalid_handle("handle " + std::to_string(handle) + " is not a " + kind_word(kind));
+      return nullptr;
+    }
+    return it->second;
+  }
+  bool remove(int64_t handle) {
+    std::shared_ptr<Object> victim;   // destroyed outside the lock
+    {
+      std::lock_guard<std::mutex> guard(lock_);
+      auto it = table_.find(handle);
+      if (it == table_.end()) return false;
+      victim = std::move(it->second);
+      table_.erase(it);
+    }
+    return true;
+  }
+  int64_t count() {
+    std::lock_guard<std::mutex> guard(lock_);
+    return (int64_t)table_.size();
+  }
+
+ private:
+  std::mutex lock_;
+  std::map<int64_t, std::shared_ptr<Object>> table_;
+  int64_t next_ = 1;
+};
+
+HandleTable g_handles;
+
+template <class T>
+std::shared_ptr<T> lookup_as(int64_t handle, ObjKind kind, std::string& err) {
+  return std::static_pointer_cast<T>(g_handles.lookup(handle, kind, err));
+}
+
+// ---------------------------------------------------------------------------
+// Device context: one device, one stream per process (Runtime.swift:10-11)
+// ---------------------------------------------------------------------------
+struct Device {
+  std::mutex lock;
+  bool tried = false;
+  bool ok = false;
+  std::string why;           // why not ok
+  int ordinal = -1;          // -1: take $TMCUDA_DEVICE or 0
+  int count = 0;
+  cudaDeviceProp prop{};
+  cudaStream_t stream = nullptr;
+  DeviceStatus* status = nullptr;   // pinned, device-visible
+  cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+  // capability probe
+  bool probed = false;
+  std::string unusable;      // empty when usable
+  int64_t launches = 0;
+};
+
+Device g_dev;
+
+bool ensure_device(std::string& err) {
+  std::lock_guard<std::mutex> guard(g_dev.lock);
+  if (g_dev.tried) {
+    if (!g_dev.ok) err = g_dev.why;
+    return g_dev.ok;
+  }
+  g_dev.tried = true;
+  auto fail = [&](const std::string& m) {
+    g_dev.why = cuda_error(m);
+    err = g_dev.why;
+    return false;
+  };
+  cudaError_t e = cudaGetDeviceCount(&g_dev.count);
+  if (e != cudaSuccess || g_dev.count == 0) {
+    cudaGetLastError();
+    return fail("no CUDA device available on this system");
+  }
+  if (g_dev.ordinal < 0) {
+    const char* env = std::getenv("TMCUDA_DEVICE");
+    g_dev.ordinal = env ? std::atoi(env) : 0;
+  }
+  if (g_dev.ordinal >= g_dev.count)
+    return fail("device ordinal " + std::to_string(g_dev.ordinal) + " out of range (" +
+                std::to_string(g_dev.count) + " devices)");
+  if ((e = cudaSetDevice(g_dev.ordinal)) != cudaSuccess)
+    return fail(std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+  if ((e = cudaGetDeviceProperties(&g_dev.prop, g_dev.ordinal)) != cudaSuccess)
+    return fail(std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+  if ((e = cudaStreamCreateWithFlags(&g_dev.stream, cudaStreamNonBlocking)) != cudaSuccess)
+    return fail(std::string("could not create a CUDA stream: ") + cudaGetErrorString(e));
+  if ((e = cudaHostAlloc((void**)&g_dev.status, sizeof(DeviceStatus), cudaHostAllocMapped)) !=
+      cudaSuccess)
+    return fail(std::string("could not allocate the status word: ") + cudaGetErrorString(e));
+  std::memset(g_dev.status, 0, sizeof(DeviceStatus));
+  cudaEventCreate(&g_dev.ev_begin);
+  cudaEventCreate(&g_dev.ev_end);
+  g_dev.ok = true;
+  return true;
+}
+
+// The calling thread must have the library's device current before any CUDA call.
+bool bind_device(std::string& err) {
+  if (!ensure_device(err)) return false;
+  cudaSetDevice(g_dev.ordinal);
+  return true;
+}
+
+LaunchCtx launch_ctx() {
+  LaunchCtx c;
+  c.stream = g_dev.stream;
+  c.sm_count = g_dev.prop.multiProcessorCount;
+  c.status = g_dev.status;
+  c.launches = &g_dev.launches;
+  return c;
+}
+
+// Capability probe, once per process (Runtime.swift:125-178): the device must be
+// compute capability 10.x and run a kernel of this library that stores a value.
+const std::string& unusable_reason() {
+  std::string err;
+  if (!bind_device(err)) {
+    static std::string none;
+    none = err.rfind("metal error: ", 0) == 0 ? err.substr(13) : err;
+    return none;
+  }
+  std::lock_guard<std::mutex> guard(g_dev.lock);
+  if (g_dev.probed) return g_dev.unusable;
+  g_dev.probed = true;
+  if (g_dev.prop.major != 10) {
+    g_dev.unusable = std::string("device '") + g_dev.prop.name + "' is sm_" +
+                     std::to_string(g_dev.prop.major) + std::to_string(g_dev.prop.minor) +
+                     "; libtmcuda holds sm_100a code only";
+    return g_dev.unusable;
+  }
+  int got = 0;
+  std::string e = launch_probe(launch_ctx(), &got);
+  if (!e.empty()) g_dev.unusable = "probe kernel failed: " + e;
+  else if (got != 0x7a11) g_dev.unusable = "probe kernel stored the wrong value";
+  return g_dev.unusable;
+}
+
+// Wait for the stream and surface device-side status.
+bool sync_stream(std::string& err) {
+  cudaError_t e = cudaStreamSynchronize(g_dev.stream);
+  if (e != cudaSuccess) {
+    err = cuda_error(std::string("kernel execution failed: ") + cudaGetErrorString(e));
+    return false;
+  }
+  if (g_dev.status->code != 0) {
+    DeviceStatus s = *g_dev.status;
+    std::memset(g_dev.status, 0, sizeof(DeviceStatus));
+    err = cuda_error("kernel execution failed: a bounded wait gave up inside the kernel (code " +
+                     std::to_string(s.code) + ", site " + std::to_string(s.where) + ", block " +
+                     std::to_string(s.block) + ", detail " + std::to_string(s.extra) +
+                     "); the results of this launch are not valid");
+    return false;
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// Launch marshalling
+// ---------------------------------------------------------------------------
+struct Decoded {
+  std::map<int, std::shared_ptr<BufferObj>> buffers;   // by Role
+  std::map<int, int64_t> ints;
+  float sm_scale = 0.f;
+};
+
+bool decode_args(KernelObj& k, const int32_t* kinds, const int64_t* values, int32_t argc,
+                 Decoded& out, std::string& err) {
+  if (argc > 0 && (!kinds || !values)) {
+    err = invalid_argument("tm_launch received NULL argument arrays");
+    return false;
+  }
+  // Kinds are validated for every position first, as the reference does while
+  // it builds its argument list (Compiler.swift:419-436).
+  for (int i = 0; i < argc; ++i) {
+    if (kinds[i] < 0 || kinds[i] > 3) {
+      err = invalid_argument("unknown launch argument kind " + std::to_string(kinds[i]) +
+                             " at position " + std::to_string(i));
+      return false;
+    }
+  }
+  const auto& args = k.desc.args;
+  if (argc != (int)args.size()) {
+    err = invalid_argument(std::string(kernel_entry_name(k.desc.id)) + " takes " +
+                           std::to_string(args.size()) + " arguments, tm_launch received " +
+                           std::to_string(argc));
+    return false;
+  }
+  for (int i = 0; i < argc; ++i) {
+    const ArgInfo& a = args[i];
+    if (a.is_pointer) {
+      if (kinds[i] != 0) {
+        err = invalid_argument("argument " + std::to_string(i) + " of " +
+                               kernel_entry_name(k.desc.id) + " is a pointer; expected kind 0, got " +
+                               std::to_string(kinds[i]));
+        return false;
+      }
+      auto b = lookup_as<BufferObj>(values[i], ObjKind::Buffer, err);
+      if (!b) return false;
+      out.buffers[(int)a.role] = b;
+    } else if (a.dtype == "f32") {
+      if (kinds[i] != 2) {
+        err = invalid_argument("argument " + std::to_string(i) + " of " +
+                               kernel_entry_name(k.desc.id) + " is an f32 scalar; expected kind 2, got " +
+                               std::to_string(kinds[i]));
+        return false;
+      }
+      uint32_t bits = (uint32_t)(values[i] & 0xffffffffu);
+      float f;
+      std::memcpy(&f, &bits, 4);
+      if (a.role == Role::SmScale) out.sm_scale = f;
+    } else {
+      if (kinds[i] != 1 && kinds[i] != 3) {
+        err = invalid_argument("argument " + std::to_string(i) + " of " +
+                               kernel_entry_name(k.desc.id) +
+                               " is an integer scalar; expected kind 1 or 3, got " +
+                               std::to_string(kinds[i]));
+        return false;
+      }
+      int64_t v = kinds[i] == 1 ? (int64_t)(int32_t)(values[i] & 0xffffffff) : values[i];
+      out.ints[(int)a.role] = v;
+    }
+  }
+  return true;
+}
+
+bool check_extent(const BufferObj& b, int64_t last_elem, int elt_bytes, const char* what,
+                  std::string& err) {
+  // last_elem: the largest element index the kernel may touch (or -1 for none).
+  if (last_elem < 0) return true;
+  __int128 need = ((__int128)last_elem + 1) * elt_bytes;
+  if (need > (__int128)b.length) {
+    err = invalid_argument(std::string("launch would address ") + std::to_string((long long)need) +
+                           " bytes of " + what + ", beyond its " + std::to_string(b.length) +
+                           "-byte buffer");
+    return false;
+  }
+  return true;
+}
+
+int64_t get_int(const Decoded& d, Role r, int64_t fallback) {
+  auto it = d.ints.find((int)r);
+  return it == d.ints.end() ? fallback : it->second;
+}
+
+void prefetch_exposed(const Decoded& d) {
+  // Buffers whose host pointer was handed out may have migrated to the host;
+  // bring them back before the kernel touches them (the migration is not part of
+  // any timed region: benchmarks never expose their buffers).
+  for (auto& kv : d.buffers) {
+    if (kv.second->host_exposed)
+      cudaMemPrefetchAsync(kv.second->ptr, (size_t)kv.second->length, g_dev.ordinal, g_dev.stream);
+  }
+}
+
+// Enqueue one launch (no wait).  Returns false with `err` on failure.
+bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
+             const int32_t* kinds, const int64_t* values, int32_t argc, int repeats,
+             std::string& err) {
+  Decoded d;
+  if (!decode_args(k, kinds, values, argc, d, err)) return false;
+  // Runtime.swift:201-211
+  if (gx <= 0 || gy <= 0 || gz <= 0) {
+    err = invalid_argument("threadgroup grid must be positive in every dimension");
+    return false;
+  }
+  if (threads <= 0) {
+    err = invalid_argument("threadsPerThreadgroup must be positive");
+    return false;
+  }
+  if (threads > 1024) {
+    err = invalid_argument("threadsPerThreadgroup " + std::to_string(threads) +
+                           " exceeds the pipeline maximum 1024");
+    return false;
+  }
+  if (!bind_device(err)) return false;
+  {
+    const std::string& why = unusable_reason();
+    if (!why.empty()) {
+      err = cuda_error(why);
+      return false;
+    }
+  }
+  LaunchCtx ctx = launch_ctx();
+  const KernelDesc& desc = k.desc;
+  const int eb = elt_size(desc.elt);
+  auto buf = [&](Role r) -> BufferObj* {
+    auto it = d.buffers.find((int)r);
+    return it == d.buffers.end() ? nullptr : it->second.get();
+  };
+  auto nonneg = [&](int64_t v, const char* name) {
+    if (v < 0) {
+      err = invalid_argument(std::string(name) + " must not be negative, got " + std::to_string(v));
+      return false;
+    }
+    return true;
+  };
+
+  if (desc.id == KernelId::Matmul) {
+    GemmProblem p{};
+    p.elt = desc.elt;
+    int64_t M = get_int(d, Role::M, 0), N = get_int(d, Role::N, 0), K = get_int(d, Role::K, 0);
+    p.sam = get_int(d, Role::StrideAm, K);   // absent strides: row-major with unit inner stride
+    p.sak = get_int(d, Role::StrideAk, 1);
+    p.sbk = get_int(d, Role::StrideBk, N);
+    p.sbn = get_int(d, Role::StrideBn, 1);
+    p.scm = get_int(d, Role::StrideCm, N);
+    p.scn = get_int(d, Role::StrideCn, 1);
+    if (!nonneg(M, "M") || !nonneg(N, "N") || !nonneg(K, "K") || !nonneg(p.sam, "stride_am") ||
+        !nonneg(p.sak, "stride_ak") || !nonneg(p.sbk, "stride_bk") || !nonneg(p.sbn, "stride_bn") ||
+        !nonneg(p.scm, "stride_cm") || !nonneg(p.scn, "stride_cn"))
+      return false;
+    // Programs beyond the grid were never dispatched: their tiles stay untouched.
+    if (desc.block_m > 0) M = std::min<int64_t>(M, gx * (int64_t)desc.block_m);
+    if (desc.block_n > 0) N = std::min<int64_t>(N, gy * (int64_t)desc.block_n);
+    p.M = M; p.N = N; p.K = K;
+    BufferObj *A = buf(Role::A), *B = buf(Role::B), *C = buf(Role::C);
+    p.a = A->ptr; p.b = B->ptr; p.c = C->ptr;
+    if (M == 0 || N == 0) return true;
+    if (K > 0) {
+      if (!check_extent(*A, (M - 1) * p.sam + (K - 1) * p.sak, eb, "A", err)) return false;
+      if (!check_extent(*B, (K - 1) * p.sbk + (N - 1) * p.sbn, eb, "B", err)) return false;
+    }
+    if (!check_extent(*C, (M - 1) * p.scm + (N - 1) * p.scn, eb, "C", err)) return false;
+    prefetch_exposed(d);
+    std::string why;
+    bool tc = k.path_option != 1 && gemm_tc_eligible(p, &why);
+    if (k.path_option == 2 && !tc) {
+      err = invalid_argument("the tcgen05 path was required but this launch is not eligible: " + why);
+      return false;
+    }
+    for (int r = 0; r < repeats; ++r) {
+      std::string e = tc ? launch_gemm_tc(p, ctx) : launch_gemm_simt(p, ctx);
+      if (!e.empty()) { err = cuda_error(e); return false; }
+    }
+    k.last_path = tc ? 2 : 1;
+    return true;
+  }
+
+  // ---- attention kernels ----
+  AttnProblem p{};
+  p.elt = desc.elt;
+  p.sm_scale = d.sm_scale;
+  p.stride_head = get_int(d, Role::StrideHead, 0);
+  p.stride_seq = get_int(d, Role::StrideSeq, 0);
+  p.stride_lse = get_int(d, Role::StrideLse, 0);
+  p.n_ctx = get_int(d, Role::NCtx, 0);
+  p.bh = gy;
+  p.causal = desc.causal;
+  p.head_dim = desc.head_dim > 0 ? desc.head_dim : (int)p.stride_seq;
+  if (!nonneg(p.stride_head, "stride_head") || !nonneg(p.stride_seq, "stride_seq") ||
+      !nonneg(p.stride_lse, "stride_lse") || !nonneg(p.n_ctx, "n_ctx"))
+    return false;
+  if (p.head_dim <= 0 || p.head_dim > 256) {
+    err = invalid_argument("head dimension " + std::to_string(p.head_dim) +
+                           " is outside the supported range 1...256");
+    return false;
+  }
+  int block_rows = desc.id == KernelId::AttnBwdDkdv ? desc.block_n : desc.block_m;
+  p.rows = p.n_ctx;
+  if (block_rows > 0) p.rows = std::min<int64_t>(p.n_ctx, gx * (int64_t)block_rows);
+  if (p.n_ctx == 0 || p.rows == 0) return true;
+  const int64_t last_data = (p.bh - 1) * p.stride_head + (p.n_ctx - 1) * p.stride_seq + p.head_dim - 1;
+  const int64_t last_stat = (p.bh - 1) * p.stride_lse + p.n_ctx - 1;
+  auto data = [&](Role r, const char* what, const void** slot) {
+    BufferObj* b = buf(r);
+    if (!b) return true;
+    if (!check_extent(*b, last_data, eb, what, err)) return false;
+    *slot = b->ptr;
+    return true;
+  };
+  auto stat = [&](Role r, const char* what, const void** slot) {
+    BufferObj* b = buf(r);
+    if (!b) return true;
+    if (!check_extent(*b, last_stat, 4, what, err)) return false;
+    *slot = b->ptr;
+    return true;
+  };
+  const void *dq = nullptr, *dk = nullptr, *dv = nullptr, *lse = nullptr, *delta = nullptr;
+  if (!data(Role::Q, "Q", &p.q) || !data(Role::Kt, "K", &p.k) || !data(Role::V, "V", &p.v) ||
+      !data(Role::O, "O", &p.o) || !data(Role::DO, "dO", &p.d_o) || !data(Role::DQ, "dQ", &dq) ||
+      !data(Role::DK, "dK", &dk) || !data(Role::DV, "dV", &dv) || !stat(Role::L, "L", &lse) ||
+      !stat(Role::Delta, "Delta", &delta))
+    return false;
+  p.lse = (float*)lse;
+  p.delta = (const float*)delta;
+  prefetch_exposed(d);
+  std::string why, e;
+  bool tc = false;
+  for (int r = 0; r < repeats; ++r) {
+    switch (desc.id) {
+      case KernelId::AttnFwd:
+        p.out0 = (void*)p.o;
+        tc = k.path_option != 1 && attn_fwd_tc_eligible(p, &why);
+        if (k.path_option == 2 && !tc) goto not_eligible;
+        e = tc ? launch_attn_fwd_tc(p, ctx) : launch_attn_fwd_simt(p, ctx);
+        break;
+      case KernelId::AttnBwdPreprocess:
+        p.out0 = (void*)delta;
+        tc = false;
+        e = launch_attn_bwd_preprocess(p, ctx);
+        break;
+      case KernelId::AttnBwdDq:
+        p.out0 = (void*)dq;
+        tc = k.path_option != 1 && attn_bwd_tc_eligible(p, &why);
+        if (k.path_option == 2 && !tc) goto not_eligible;
+        e = tc ? launch_attn_bwd_dq_tc(p, ctx) : launch_attn_bwd_dq_simt(p, ctx);
+        break;
+      case KernelId::AttnBwdDkdv:
+        p.out0 = (void*)dk;
+        p.out1 = (void*)dv;
+        tc = k.path_option != 1 && attn_bwd_tc_eligible(p, &why);
+        if (k.path_option == 2 && !tc) goto not_eligible;
+        e = tc ? launch_attn_bwd_dkdv_tc(p, ctx) : launch_attn_bwd_dkdv_simt(p, ctx);
+        break;
+      default:
+        e = "unknown kernel";
+    }
+    if (!e.empty()) { err = cuda_error(e); return false; }
+  }
+  k.last_path = tc ? 2 : 1;
+  return true;
+not_eligible:
+  err = invalid_argument("the tcgen05 path was required but this launch is not eligible: " + why);
+  return false;
+}
+
+int32_t do_launch(int64_t kernel, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
+                  const int32_t* kinds, const int64_t* values, int32_t argc, int repeats, bool wait,
+                  float* elapsed_ms) {
+  std::string err;
+  auto k = lookup_as<KernelObj>(kernel, ObjKind::Kernel, err);
+  if (!k) { store_error(err); return -1; }
+  if (elapsed_ms) {
+    if (!bind_device(err)) { store_error(err); return -1; }
+    cudaEventRecord(g_dev.ev_begin, g_dev.stream);
+  }
+  if (!enqueue(*k, gx, gy, gz, threads, kinds, values, argc, repeats, err)) {
+    store_error(err);
+    return -1;
+  }
+  if (elapsed_ms) cudaEventRecord(g_dev.ev_end, g_dev.stream);
+  if (wait) {
+    if (!bind_device(err) || !sync_stream(err)) { store_error(err); return -1; }
+    if (elapsed_ms) cudaEventElapsedTime(elapsed_ms, g_dev.ev_begin, g_dev.ev_end);
+  }
+  return 0;
+}
+
+int32_t do_copy(int64_t buffer, int64_t offset, const void* host, int64_t length, bool to_device,
+                bool wait) {
+  // NULL / negative bounds are refused before the handle is looked at
+  // (Compiler.swift:354-357).
+  if (!host || length < 0 || offset < 0) {
+    store_error(invalid_argument("buffer copy received invalid bounds"));
+    return -1;
+  }
+  std::string err;
+  auto b = lookup_as<BufferObj>(buffer, ObjKind::Buffer, err);
+  if (!b) { store_error(err); return -1; }
+  if ((__int128)offset + (__int128)length > (__int128)b->length) {
+    store_error(invalid_argument("copy of " + std::to_string(length) + " bytes at offset " +
+                                 std::to_string(offset) + " exceeds the " +
+                                 std::to_string(b->length) + "-byte buffer"));
+    return -1;
+  }
+  if (length == 0) return 0;
+  if (!bind_device(err)) { store_error(err); return -1; }
+  char* dev = (char*)b->ptr + offset;
+  cudaError_t e = to_device
+      ? cudaMemcpyAsync(dev, host, (size_t)length, cudaMemcpyDefault, g_dev.stream)
+      : cudaMemcpyAsync((void*)host, dev, (size_t)length, cudaMemcpyDefault, g_dev.stream);
+  if (e != cudaSuccess) {
+    store_error(cuda_error(std::string("buffer copy failed: ") + cudaGetErrorString(e)));
+    return -1;
+  }
+  if (wait && !sync_stream(err)) { store_error(err); return -1; }
+  return 0;
+}
+
+}  // namespace
+
+// ===========================================================================
+// Exports
+// ===========================================================================
+extern "C" {
+
+char* tm_version(void) { return dup_string("0.0.1"); }
+
+void tm_free(void* ptr) { std::free(ptr); }
+
+char* tm_last_error(void) {
+  std::lock_guard<std::mutex> guard(g_error_lock);
+  std::string out = g_has_error ? g_error : std::string("no error");
+  g_error.clear();
+  g_has_error = false;
+  return dup_string(out);
+}
+
+int32_t tm_is_active(void) {
+  std::string err;
+  return ensure_device(err) ? 1 : 0;
+}
+
+int32_t tm_is_usable(void) { return unusable_reason().empty() ? 1 : 0; }
+
+char* tm_unusable_reason(void) {
+  const std::string& why = unusable_reason();
+  return why.empty() ? nullptr : dup_string(why);
+}
+
+char* tm_device_name(void) {
+  std::string err;
+  if (!ensure_device(err)) return nullptr;
+  return dup_string(g_dev.prop.name);
+}
+
+char* tm_emit_msl(const char* ttir, int32_t num_simdgroups) {
+  if (!ttir) {
+    store_error(invalid_argument("tm_emit_msl received a NULL module"));
+    return nullptr;
+  }
+  std::vector<KernelDesc> kernels;
+  std::string err;
+  if (!scan_module(ttir, num_simdgroups, kernels, err)) {
+    store_error(err);
+    return nullptr;
+  }
+  return dup_string(descriptor_text(kernels));
+}
+
+char* tm_kernel_info(const char* ttir, int32_t num_simdgroups) {
+  if (!ttir) {
+    store_error(invalid_argument("tm_kernel_info received a NULL module"));
+    return nullptr;
+  }
+  std::vector<KernelDesc> kernels;
+  std::string err;
+  if (!scan_module(ttir, num_simdgroups, kernels, err)) {
+    store_error(err);
+    return nullptr;
+  }
+  return dup_string(kernel_info_json(kernels));
+}
+
+int64_t tm_compile_msl(const char* source) {
+  if (!source) {
+    store_error(invalid_argument("tm_compile_msl received NULL source"));
+    return 0;
+  }
+  auto lib = std::make_shared<LibraryObj>();
+  std::string err;
+  if (!parse_descriptor(source, lib->kernels, err)) {
+    store_error(err);
+    return 0;
+  }
+  return g_handles.insert(lib);
+}
+
+int64_t tm_load_metallib(const void* bytes, int64_t length) {
+  if (!bytes || length <= 0) {
+    store_error(invalid_argument("tm_load_metallib received an empty image"));
+    return 0;
+  }
+  std::string text((const char*)bytes, (size_t)length);
+  auto lib = std::make_shared<LibraryObj>();
+  std::string err;
+  if (!parse_descriptor(text, lib->kernels, err)) {
+    store_error(cuda_error("could not load metallib: the image is not a tmcuda kernel descriptor"));
+    return 0;
+  }
+  return g_handles.insert(lib);
+}
+
+int32_t tm_release_library(int64_t library) { return g_handles.remove(library) ? 0 : -1; }
+
+int64_t tm_load_kernel(int64_t library, const char* name) {
+  if (!name) {
+    store_error(invalid_argument("tm_load_kernel received a NULL kernel name"));
+    return 0;
+  }
+  std::string err;
+  auto lib = lookup_as<LibraryObj>(library, ObjKind::Library, err);
+  if (!lib) { store_error(err); return 0; }
+  for (auto& k : lib->kernels) {
+    if (std::string(name) == kernel_entry_name(k.id)) {
+      auto obj = std::make_shared<KernelObj>();
+      obj->desc = k;
+      return g_handles.insert(obj);
+    }
+  }
+  std::vector<std::string> names;
+  for (auto& k : lib->kernels) names.push_back(kernel_entry_name(k.id));
+  std::sort(names.begin(), names.end());
+  std::string available;
+  for (auto& n : names) available += (available.empty() ? "" : ", ") + n;
+  store_error(cuda_error(std::string("kernel '") + name + "' not found in library (available: " +
+                         (available.empty() ? "none" : available) + ")"));
+  return 0;
+}
+
+int64_t tm_kernel_max_threads(int64_t kernel) {
+  std::string err;
+  auto k = lookup_as<KernelObj>(kernel, ObjKind::Kernel, err);
+  if (!k) { store_error(err); return -1; }
+  return 1024;
+}
+
+int32_t tm_release_kernel(int64_t kernel) { return g_handles.remove(kernel) ? 0 : -1; }
+
+int64_t tm_alloc_buffer(int64_t nbytes) {
+  if (nbytes <= 0) {
+    store_error(invalid_argument("buffer length must be positive, got " + std::to_string(nbytes)));
+    return 0;
+  }
+  std::string err;
+  if (!bind_device(err)) { store_error(err); return 0; }
+  auto b = std::make_shared<BufferObj>();
+  cudaError_t e = cudaMallocManaged(&b->ptr, (size_t)nbytes, cudaMemAttachGlobal);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    b->ptr = nullptr;
+    store_error(cuda_error("could not allocate a " + std::to_string(nbytes) + "-byte shared buffer: " +
+                           cudaGetErrorString(e)));
+    return 0;
+  }
+  b->length = nbytes;
+  // Resident on the device, and zero-filled like a new MTLBuffer.
+  cudaMemPrefetchAsync(b->ptr, (size_t)nbytes, g_dev.ordinal, g_dev.stream);
+  cudaMemsetAsync(b->ptr, 0, (size_t)nbytes, g_dev.stream);
+  e = cudaStreamSynchronize(g_dev.stream);
+  if (e != cudaSuccess) {
+    store_error(cuda_error(std::string("could not initialise the buffer: ") + cudaGetErrorString(e)));
+    return 0;
+  }
+  return g_handles.insert(b);
+}
+
+void* tm_buffer_contents(int64_t buffer) {
+  std::string err;
+  auto b = lookup_as<BufferObj>(buffer, ObjKind::Buffer, err);
+  if (!b) { store_error(err); return nullptr; }
+  b->host_exposed = true;
+  return b->ptr;
+}
+
+int64_t tm_buffer_length(int64_t buffer) {
+  std::string err;
+  auto b = lookup_as<BufferObj>(buffer, ObjKind::Buffer, err);
+  if (!b) { store_error(err); return -1; }
+  return b->length;
+}
+
+int32_t tm_buffer_write(int64_t buffer, int64_t offset, const void* source, int64_t length) {
+  return do_copy(buffer, offset, source, length, true, true);
+}
+
+int32_t tm_buffer_read(int64_t buffer, int64_t offset, void* destination, int64_t length) {
+  return do_copy(buffer, offset, destination, length, false, true);
+}
+
+int32_t tm_free_buffer(int64_t buffer) {
+  std::string err;
+  // The object is destroyed (cudaFree) with the library's device current.
+  if (g_dev.ok) cudaSetDevice(g_dev.ordinal);
+  return g_handles.remove(buffer) ? 0 : -1;
+}
+
+int32_t tm_launch(int64_t kernel, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
+                  const int32_t* kinds, const int64_t* values, int32_t argc) {
+  return do_launch(kernel, gx, gy, gz, threads, kinds, values, argc, 1, true, nullptr);
+}
+
+int64_t tm_live_handle_count(void) { return g_handles.count(); }
+
+// ---- additive -------------------------------------------------------------
+
+int32_t tmx_set_device(int32_t ordinal) {
+  std::lock_guard<std::mutex> guard(g_dev.lock);
+  if (g_dev.tried && g_dev.ordinal != ordinal) {
+    store_error(invalid_argument("tmx_set_device must be called before the first use of the device"));
+    return -1;
+  }
+  if (ordinal < 0) {
+    store_error(invalid_argument("device ordinal must not be negative"));
+    return -1;
+  }
+  g_dev.ordinal = ordinal;
+  return 0;
+}
+
+int32_t tmx_get_device(void) {
+  std::string err;
+  if (!ensure_device(err)) { store_error(err); return -1; }
+  return g_dev.ordinal;
+}
+
+int32_t tmx_sm_count(void) {
+  std::string err;
+  if (!ensure_device(err)) { store_error(err); return -1; }
+  return g_dev.prop.multiProcessorCount;
+}
+
+int32_t tmx_kernel_set_option(int64_t kernel, const char* name, int64_t value) {
+  std::string err;
+  auto k = lookup_as<KernelObj>(kernel, ObjKind::Kernel, err);
+  if (!k) { store_error(err); return -1; }
+  if (!name) { store_error(invalid_argument("tmx_kernel_set_option received a NULL name")); return -1; }
+  std::string n(name);
+  if (n == "causal") {
+    if (k->desc.id == KernelId::Matmul || k->desc.id == KernelId::AttnBwdPreprocess) {
+      store_error(invalid_argument(std::string("option 'causal' does not apply to ") +
+                                   kernel_entry_name(k->desc.id)));
+      return -1;
+    }
+    k->desc.causal = value != 0;
+    return 0;
+  }
+  if (n == "path") {
+    if (value < 0 || value > 2) {
+      store_error(invalid_argument("option 'path' takes 0, 1 or 2"));
+      return -1;
+    }
+    k->path_option = (int)value;
+    return 0;
+  }
+  store_error(invalid_argument("unknown kernel option '" + n + "'"));
+  return -1;
+}
+
+int32_t tmx_kernel_last_path(int64_t kernel) {
+  std::string err;
+  auto k = lookup_as<KernelObj>(kernel, ObjKind::Kernel, err);
+  if (!k) { store_error(err); return -1; }
+  return k->last_path;
+}
+
+int32_t tmx_launch_async(int64_t kernel, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
+                         const int32_t* kinds, const int64_t* values, int32_t argc) {
+  return do_launch(kernel, gx, gy, gz, threads, kinds, values, argc, 1, false, nullptr);
+}
+
+int32_t tmx_launch_timed(int64_t kernel, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
+                         const int32_t* kinds, const int64_t* values, int32_t argc, int32_t repeats,
+                         float* elapsed_ms) {
+  if (!elapsed_ms || repeats <= 0) {
+    store_error(invalid_argument("tmx_launch_timed needs repeats > 0 and a result pointer"));
+    return -1;
+  }
+  return do_launch(kernel, gx, gy, gz, threads, kinds, values, argc, repeats, true, elapsed_ms);
+}
+
+int32_t tmx_synchronize(void) {
+  std::string err;
+  if (!bind_device(err) || !sync_stream(err)) { store_error(err); return -1; }
+  return 0;
+}
+
+int32_t tmx_buffer_write_async(int64_t buffer, int64_t offset, const void* source, int64_t length) {
+  return do_copy(buffer, offset, source, length, true, false);
+}
+
+int32_t tmx_buffer_read_async(int64_t buffer, int64_t offset, void* destination, int64_t length) {
+  return do_copy(buffer, offset, destination, length, false, false);
+}
+
+int32_t tmx_buffer_fill(int64_t buffer, int64_t offset, int32_t byte, int64_t length) {
+  std::string err;
+  if (length < 0 || offset < 0) {
+    store_error(invalid_argument("buffer fill received invalid bounds"));
+    return -1;
+  }
+  auto b = lookup_as<BufferObj>(buffer, ObjKind::Buffer, err);
+  if (!b) { store_error(err); return -1; }
+  if ((__int128)offset + (__int128)length > (__int128)b->length) {
+    store_error(invalid_argument("fill of " + std::to_string(length) + " bytes at offset " +
+                                 std::to_string(offset) + " exceeds the " +
+                                 std::to_string(b->length) + "-byte buffer"));
+    return -1;
+  }
+  if (!bind_device(err)) { store_error(err); return -1; }
+  cudaError_t e = cudaMemsetAsync((char*)b->ptr + offset, byte, (size_t)length, g_dev.stream);
+  if (e != cudaSuccess) {
+    store_error(cuda_error(std::string("buffer fill failed: ") + cudaGetErrorString(e)));
+    return -1;
+  }
+  return 0;
+}
+
+int32_t tmx_timer_begin(void) {
+  std::string err;
+  if (!bind_device(err)) { store_error(err); return -1; }
+  cudaEventRecord(g_dev.ev_begin, g_dev.stream);
+  return 0;
+}
+
+int32_t tmx_timer_end(float* elapsed_ms) {
+  std::string err;
+  if (!elapsed_ms) { store_error(invalid_argument("tmx_timer_end needs a result pointer")); return -1; }
+  if (!bind_device(err)) { store_error(err); return -1; }
+  cudaEventRecord(g_dev.ev_end, g_dev.stream);
+  if (!sync_stream(err)) { store_error(err); return -1; }
+  cudaEventElapsedTime(elapsed_ms, g_dev.ev_begin, g_dev.ev_end);
+  return 0;
+}
+
+int64_t tmx_launch_count(void) { return g_dev.launches; }
+
+}  // extern "C"

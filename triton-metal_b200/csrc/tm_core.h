@@ -1,0 +1,130 @@
+// Internal declarations shared by the translation units of libtmcuda.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+namespace tmc {
+
+// ---------------------------------------------------------------------------
+// Element types and kernel identities
+// ---------------------------------------------------------------------------
+
+enum class Elt : int { F32 = 0, F16 = 1, BF16 = 2 };
+
+inline int elt_size(Elt e) { return e == Elt::F32 ? 4 : 2; }
+inline const char* elt_name(Elt e) {
+  return e == Elt::F32 ? "f32" : (e == Elt::F16 ? "f16" : "bf16");
+}
+
+enum class KernelId : int {
+  Matmul = 0,
+  AttnFwd = 1,
+  AttnBwdPreprocess = 2,
+  AttnBwdDq = 3,
+  AttnBwdDkdv = 4,
+  Count = 5
+};
+
+const char* kernel_entry_name(KernelId id);
+
+// The role of one tt.func argument, resolved from its name or position.
+enum class Role : int {
+  Unknown = 0,
+  // matmul_kernel
+  A, B, C, M, N, K, StrideAm, StrideAk, StrideBk, StrideBn, StrideCm, StrideCn,
+  // attention kernels
+  Q, Kt, V, O, DO, DQ, DK, DV, L, Delta, SmScale, StrideHead, StrideSeq, StrideLse, NCtx
+};
+
+struct ArgInfo {
+  int index = 0;
+  bool is_pointer = false;
+  std::string dtype;   // "f32" "f16" "bf16" "i32" "i64" "i1" ...
+  std::string name;    // without the leading '%'
+  Role role = Role::Unknown;
+};
+
+// What tm_emit_msl extracts from a module and what a "library" holds.
+struct KernelDesc {
+  KernelId id = KernelId::Matmul;
+  Elt elt = Elt::F32;
+  int block_m = 0, block_n = 0, block_k = 0, head_dim = 0;
+  int threads = 128;
+  int causal = 0;
+  std::vector<ArgInfo> args;
+};
+
+// ir_scan.cpp -----------------------------------------------------------------
+// Scan Triton IR text.  On failure returns false and fills `error` with a
+// message in the reference's CoreError wording.
+bool scan_module(const std::string& ttir, int num_simdgroups,
+                 std::vector<KernelDesc>& out, std::string& error);
+std::string descriptor_text(const std::vector<KernelDesc>& kernels);
+bool parse_descriptor(const std::string& text, std::vector<KernelDesc>& out, std::string& error);
+std::string kernel_info_json(const std::vector<KernelDesc>& kernels);
+
+// ---------------------------------------------------------------------------
+// Problem descriptions handed to the kernel launchers (device pointers)
+// ---------------------------------------------------------------------------
+
+struct GemmProblem {
+  Elt elt;
+  const void* a; const void* b; void* c;
+  int64_t M, N, K;                 // effective extents (already clamped by the grid)
+  int64_t sam, sak, sbk, sbn, scm, scn;   // strides in elements
+};
+
+struct AttnProblem {
+  Elt elt;
+  const void* q; const void* k; const void* v; const void* o; const void* d_o;
+  void* out0;       // O (fwd), Delta (preprocess), dQ (dq), dK (dkdv)
+  void* out1;       // dV (dkdv) or nullptr
+  float* lse;       // L: written by fwd (may be null), read by bwd
+  const float* delta;
+  float sm_scale;
+  int64_t stride_head, stride_seq, stride_lse;
+  int64_t n_ctx;
+  int64_t rows;     // query rows (fwd, preprocess, dq) or key rows (dkdv) covered by the grid
+  int64_t bh;       // batch*heads = grid_y
+  int head_dim;
+  int causal;
+};
+
+// Device status word: non-zero after a bounded wait inside a kernel gave up.
+struct DeviceStatus {
+  unsigned int code;      // 0 ok
+  unsigned int where;     // role / barrier id that gave up
+  unsigned int block;
+  unsigned int extra;
+};
+
+struct LaunchCtx {
+  cudaStream_t stream;
+  int sm_count;
+  DeviceStatus* status;   // device pointer
+  int64_t* launches;      // incremented by each launcher per kernel launched
+};
+
+// Launchers.  Return nullptr on success or a static/owned error string.
+// path_used: 1 SIMT, 2 tcgen05.
+std::string launch_gemm_simt(const GemmProblem& p, const LaunchCtx& ctx);
+std::string launch_attn_fwd_simt(const AttnProblem& p, const LaunchCtx& ctx);
+std::string launch_attn_bwd_preprocess(const AttnProblem& p, const LaunchCtx& ctx);
+std::string launch_attn_bwd_dq_simt(const AttnProblem& p, const LaunchCtx& ctx);
+std::string launch_attn_bwd_dkdv_simt(const AttnProblem& p, const LaunchCtx& ctx);
+
+// tcgen05 paths: `eligible` says whether the shape can take the path.
+bool gemm_tc_eligible(const GemmProblem& p, std::string* why);
+std::string launch_gemm_tc(const GemmProblem& p, const LaunchCtx& ctx);
+bool attn_fwd_tc_eligible(const AttnProblem& p, std::string* why);
+std::string launch_attn_fwd_tc(const AttnProblem& p, const LaunchCtx& ctx);
+bool attn_bwd_tc_eligible(const AttnProblem& p, std::string* why);
+std::string launch_attn_bwd_dq_tc(const AttnProblem& p, const LaunchCtx& ctx);
+std::string launch_attn_bwd_dkdv_tc(const AttnProblem& p, const LaunchCtx& ctx);
+
+std::string launch_probe(const LaunchCtx& ctx, int* out_host);
+
+}  // namespace tmc

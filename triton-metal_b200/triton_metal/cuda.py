@@ -1,0 +1,108 @@
+"""Bindings of libtmcuda's additive `tmx_*` entry points (no counterpart in the
+reference): device selection, kernel options, asynchronous and timed launches."""
+
+import ctypes
+
+from . import _core
+
+_lib = _core._lib
+_I32, _I64, _PTR, _STR = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_char_p
+_I32P, _I64P, _F32P = (ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int64),
+                       ctypes.POINTER(ctypes.c_float))
+
+_LAUNCH = (_I64, _I64, _I64, _I64, _I64, _I32P, _I64P, _I32)
+
+EXPORTS = {
+    "tmx_set_device": (_I32, (_I32,)),
+    "tmx_get_device": (_I32, ()),
+    "tmx_sm_count": (_I32, ()),
+    "tmx_kernel_set_option": (_I32, (_I64, _STR, _I64)),
+    "tmx_kernel_last_path": (_I32, (_I64,)),
+    "tmx_launch_async": (_I32, _LAUNCH),
+    "tmx_launch_timed": (_I32, _LAUNCH + (_I32, _F32P)),
+    "tmx_synchronize": (_I32, ()),
+    "tmx_buffer_write_async": (_I32, (_I64, _I64, _PTR, _I64)),
+    "tmx_buffer_read_async": (_I32, (_I64, _I64, _PTR, _I64)),
+    "tmx_buffer_fill": (_I32, (_I64, _I64, _I32, _I64)),
+    "tmx_timer_begin": (_I32, ()),
+    "tmx_timer_end": (_I32, (_F32P,)),
+    "tmx_launch_count": (_I64, ()),
+}
+
+for _symbol, (_ret, _args) in EXPORTS.items():
+    _entry = getattr(_lib, _symbol)
+    _entry.restype = _ret
+    _entry.argtypes = list(_args)
+
+PATH_AUTO, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
+
+
+def _ok(status):
+    if status == -1:
+        raise RuntimeError(_core.last_error())
+    return status
+
+
+def set_device(ordinal: int) -> None:
+    _ok(_lib.tmx_set_device(ordinal))
+
+
+def get_device() -> int:
+    return _ok(_lib.tmx_get_device())
+
+
+def sm_count() -> int:
+    return _ok(_lib.tmx_sm_count())
+
+
+def set_option(kernel: int, name: str, value: int) -> None:
+    _ok(_lib.tmx_kernel_set_option(kernel, name.encode(), value))
+
+
+def last_path(kernel: int) -> int:
+    return _ok(_lib.tmx_kernel_last_path(kernel))
+
+
+def launch_async(kernel, grid, threads, kinds, values) -> None:
+    k, v, n = _core.pack_arguments(kinds, values)
+    _ok(_lib.tmx_launch_async(kernel, grid[0], grid[1], grid[2], threads, k, v, n))
+
+
+def launch_timed(kernel, grid, threads, kinds, values, repeats: int) -> float:
+    """Milliseconds for `repeats` back-to-back launches (CUDA events on the
+    library's stream)."""
+    k, v, n = _core.pack_arguments(kinds, values)
+    elapsed = ctypes.c_float(0.0)
+    _ok(_lib.tmx_launch_timed(kernel, grid[0], grid[1], grid[2], threads, k, v, n, repeats,
+                              ctypes.byref(elapsed)))
+    return elapsed.value
+
+
+def synchronize() -> None:
+    _ok(_lib.tmx_synchronize())
+
+
+def write_async(handle, offset, address, nbytes) -> None:
+    _ok(_lib.tmx_buffer_write_async(handle, offset, ctypes.c_void_p(address), nbytes))
+
+
+def read_async(handle, offset, address, nbytes) -> None:
+    _ok(_lib.tmx_buffer_read_async(handle, offset, ctypes.c_void_p(address), nbytes))
+
+
+def fill(handle, offset, byte, nbytes) -> None:
+    _ok(_lib.tmx_buffer_fill(handle, offset, byte, nbytes))
+
+
+def timer_begin() -> None:
+    _ok(_lib.tmx_timer_begin())
+
+
+def timer_end() -> float:
+    elapsed = ctypes.c_float(0.0)
+    _ok(_lib.tmx_timer_end(ctypes.byref(elapsed)))
+    return elapsed.value
+
+
+def launch_count() -> int:
+    return _lib.tmx_launch_count()

@@ -1,0 +1,208 @@
+"""The five hot kernels as callables over the `tm_*` ABI.
+
+The reference reaches its kernels by handing Triton IR to `tm_emit_msl`
+(Sources/TritonMetalBench/{GEMMKernel,AttentionKernel,AttentionBackwardKernel}.swift
+generate that IR; python/examples/*.py get it from `@triton.jit`).  libtmcuda
+only scans the `tt.func` header and the first `tt.dot`, so the modules built
+here are signature-level: header, one `tt.dot` carrying the BLOCK shape, return.
+Argument order is the Python order of python/examples/attention_training.py and
+python/examples/matmul.py with all six strides present.
+"""
+
+import math
+
+from . import _core, cuda
+
+ELEMENT = {"float32": "f32", "float16": "f16", "bfloat16": "bf16",
+           "f32": "f32", "f16": "f16", "bf16": "bf16"}
+
+
+def matmul_ir(block_m=128, block_n=128, block_k=64, element="f32"):
+    e = ELEMENT[element]
+    return f"""module {{
+  tt.func public @matmul_kernel(
+      %a_ptr: !tt.ptr<{e}>, %b_ptr: !tt.ptr<{e}>, %c_ptr: !tt.ptr<{e}>,
+      %M: i32, %N: i32, %K: i32,
+      %stride_am: i32, %stride_ak: i32, %stride_bk: i32, %stride_bn: i32,
+      %stride_cm: i32, %stride_cn: i32) {{
+    %acc = tt.dot %a, %b, %zero, inputPrecision = tf32 : tensor<{block_m}x{block_k}x{e}> * tensor<{block_k}x{block_n}x{e}> -> tensor<{block_m}x{block_n}xf32>
+    tt.return
+  }}
+}}
+"""
+
+
+def _attn_ir(name, arguments, lhs, rhs, out, element, causal):
+    e = ELEMENT[element]
+    attributes = " attributes {tm.causal = true}" if causal else ""
+    dot = ""
+    if rhs is not None:
+        dot = (f"    %s = tt.dot %x, %y, %z : tensor<{lhs[0]}x{lhs[1]}x{e}> * "
+               f"tensor<{rhs[0]}x{rhs[1]}x{e}> -> tensor<{out[0]}x{out[1]}xf32>\n")
+    else:
+        dot = f"    %o = tt.load %p : tensor<{lhs[0]}x{lhs[1]}x{e}>\n"
+    return (f"module {{\n  tt.func public @{name}({arguments.format(e=e)}){attributes} {{\n"
+            f"{dot}    tt.return\n  }}\n}}\n")
+
+
+def attn_fwd_ir(block_m=128, block_n=128, head_dim=128, element="f32", causal=False):
+    args = ("%Q: !tt.ptr<{e}>, %K: !tt.ptr<{e}>, %V: !tt.ptr<{e}>, %O: !tt.ptr<{e}>, "
+            "%L: !tt.ptr<f32>, %sm_scale: f32, %stride_head: i32, %stride_seq: i32, "
+            "%stride_lse: i32, %N_CTX: i32")
+    return _attn_ir("attn_fwd", args, (block_m, head_dim), (head_dim, block_n),
+                    (block_m, block_n), element, causal)
+
+
+def attn_bwd_preprocess_ir(block_m=128, head_dim=128, element="f32"):
+    args = ("%O: !tt.ptr<{e}>, %DO: !tt.ptr<{e}>, %Delta: !tt.ptr<f32>, %stride_head: i32, "
+            "%stride_seq: i32, %stride_lse: i32, %N_CTX: i32")
+    return _attn_ir("attn_bwd_preprocess", args, (block_m, head_dim), None, None, element, False)
+
+
+def attn_bwd_dq_ir(block_m=128, block_n=128, head_dim=128, element="f32", causal=False):
+    args = ("%Q: !tt.ptr<{e}>, %K: !tt.ptr<{e}>, %V: !tt.ptr<{e}>, %DO: !tt.ptr<{e}>, "
+            "%DQ: !tt.ptr<{e}>, %L: !tt.ptr<f32>, %D: !tt.ptr<f32>, %sm_scale: f32, "
+            "%stride_head: i32, %stride_seq: i32, %stride_lse: i32, %N_CTX: i32")
+    return _attn_ir("attn_bwd_dq", args, (block_m, head_dim), (head_dim, block_n),
+                    (block_m, block_n), element, causal)
+
+
+def attn_bwd_dkdv_ir(block_m=128, block_n=128, head_dim=128, element="f32", causal=False):
+    args = ("%Q: !tt.ptr<{e}>, %K: !tt.ptr<{e}>, %V: !tt.ptr<{e}>, %DO: !tt.ptr<{e}>, "
+            "%DK: !tt.ptr<{e}>, %DV: !tt.ptr<{e}>, %L: !tt.ptr<f32>, %D: !tt.ptr<f32>, "
+            "%sm_scale: f32, %stride_head: i32, %stride_seq: i32, %stride_lse: i32, %N_CTX: i32")
+    return _attn_ir("attn_bwd_dkdv", args, (block_n, head_dim), (head_dim, block_m),
+                    (block_n, block_m), element, causal)
+
+
+class Kernel:
+    """emit -> compile -> load, the flow of MetalUtils.load_binary
+    (python/plugin/backend/driver.py:31-40); `release()` drops both handles."""
+
+    def __init__(self, ir, name, num_warps=4):
+        self.name = name
+        self.threads = 32 * num_warps
+        self.descriptor = _core.emit_msl(ir, num_warps)
+        self.library = _core.compile_msl(self.descriptor)
+        try:
+            self.handle = _core.load_kernel(self.library, name)
+        except Exception:
+            _core.release_library(self.library)
+            raise
+
+    def set_path(self, path):
+        cuda.set_option(self.handle, "path", path)
+
+    def set_causal(self, causal):
+        cuda.set_option(self.handle, "causal", int(bool(causal)))
+
+    def last_path(self):
+        return cuda.last_path(self.handle)
+
+    def launch(self, grid, kinds, values):
+        _core.launch(self.handle, grid, self.threads, kinds, values)
+
+    def launch_async(self, grid, kinds, values):
+        cuda.launch_async(self.handle, grid, self.threads, kinds, values)
+
+    def time(self, grid, kinds, values, repeats):
+        return cuda.launch_timed(self.handle, grid, self.threads, kinds, values, repeats)
+
+    def release(self):
+        if self.handle:
+            _core.release_kernel(self.handle)
+            _core.release_library(self.library)
+            self.handle = self.library = 0
+
+
+B, I, F = _core.ARG_BUFFER, _core.ARG_I32, _core.ARG_F32
+
+
+def cdiv(a, b):
+    return (a + b - 1) // b
+
+
+class Matmul(Kernel):
+    """`matmul_kernel`: C[M,N] = A[M,K] @ B[K,N], fp32 accumulate."""
+
+    def __init__(self, element="f32", block=(128, 128, 64), num_warps=4):
+        self.block = block
+        super().__init__(matmul_ir(*block, element=element), "matmul_kernel", num_warps)
+
+    def arguments(self, a, b, c, M, N, K, strides=None):
+        if strides is None:
+            strides = (K, 1, N, 1, N, 1)
+        kinds = [B, B, B] + [I] * 9
+        values = [a, b, c, M, N, K, *strides]
+        grid = (cdiv(M, self.block[0]), cdiv(N, self.block[1]), 1)
+        return grid, kinds, values
+
+    def __call__(self, a, b, c, M, N, K, strides=None):
+        self.launch(*self.arguments(a, b, c, M, N, K, strides))
+
+
+class AttnFwd(Kernel):
+    def __init__(self, element="f32", head_dim=128, block=(128, 128), causal=False, num_warps=4):
+        self.block, self.head_dim = block, head_dim
+        super().__init__(attn_fwd_ir(block[0], block[1], head_dim, element, causal), "attn_fwd",
+                         num_warps)
+
+    def arguments(self, q, k, v, o, lse, scale, bh, seq):
+        d = self.head_dim
+        kinds = [B, B, B, B, B, F, I, I, I, I]
+        values = [q, k, v, o, lse, _core.float_bits(scale), seq * d, d, seq, seq]
+        return (cdiv(seq, self.block[0]), bh, 1), kinds, values
+
+    def __call__(self, *args):
+        self.launch(*self.arguments(*args))
+
+
+class AttnBwdPreprocess(Kernel):
+    def __init__(self, element="f32", head_dim=128, block_m=128, num_warps=4):
+        self.block_m, self.head_dim = block_m, head_dim
+        super().__init__(attn_bwd_preprocess_ir(block_m, head_dim, element),
+                         "attn_bwd_preprocess", num_warps)
+
+    def arguments(self, o, do, delta, bh, seq):
+        d = self.head_dim
+        return ((cdiv(seq, self.block_m), bh, 1), [B, B, B, I, I, I, I],
+                [o, do, delta, seq * d, d, seq, seq])
+
+    def __call__(self, *args):
+        self.launch(*self.arguments(*args))
+
+
+class AttnBwdDq(Kernel):
+    def __init__(self, element="f32", head_dim=128, block=(128, 128), causal=False, num_warps=4):
+        self.block, self.head_dim = block, head_dim
+        super().__init__(attn_bwd_dq_ir(block[0], block[1], head_dim, element, causal),
+                         "attn_bwd_dq", num_warps)
+
+    def arguments(self, q, k, v, do, dq, lse, delta, scale, bh, seq):
+        d = self.head_dim
+        kinds = [B] * 7 + [F, I, I, I, I]
+        values = [q, k, v, do, dq, lse, delta, _core.float_bits(scale), seq * d, d, seq, seq]
+        return (cdiv(seq, self.block[0]), bh, 1), kinds, values
+
+    def __call__(self, *args):
+        self.launch(*self.arguments(*args))
+
+
+class AttnBwdDkdv(Kernel):
+    def __init__(self, element="f32", head_dim=128, block=(128, 128), causal=False, num_warps=4):
+        self.block, self.head_dim = block, head_dim
+        super().__init__(attn_bwd_dkdv_ir(block[0], block[1], head_dim, element, causal),
+                         "attn_bwd_dkdv", num_warps)
+
+    def arguments(self, q, k, v, do, dk, dv, lse, delta, scale, bh, seq):
+        d = self.head_dim
+        kinds = [B] * 8 + [F, I, I, I, I]
+        values = [q, k, v, do, dk, dv, lse, delta, _core.float_bits(scale), seq * d, d, seq, seq]
+        return (cdiv(seq, self.block[1]), bh, 1), kinds, values
+
+    def __call__(self, *args):
+        self.launch(*self.arguments(*args))
+
+
+def default_scale(head_dim):
+    return 1.0 / math.sqrt(head_dim)
