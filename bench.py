@@ -1,0 +1,587 @@
+#!/usr/bin/env python
+"""Benchmark of the matmul / FlashAttention-2 hot path through libtmcuda's C ABI.
+
+    python bench.py --gpus N --steps K --warmup W [--workload NAME] [--impl reference]
+
+Headline workload (default): bf16 GEMM 8192^3, fp32 accumulate, inputs
+N(0,1)/sqrt(K) rounded to bf16; row blocks of M sharded over the ranks with an
+all-gather of C.  One step = one pass of the kernel over the whole problem.
+Other workloads: gemm_skinny, attn_fwd (batch 4, heads 32, d 128, seq 4096,
+causal), attn_bwd (batch 8, heads 16, seq 4096, d 128, causal); attention is
+sharded by (batch, head) with no collective.  With `--also` (default at N=1)
+the attention workloads are measured too and reported under "also".
+
+One JSON line on stdout (rank 0).  Everything else goes to stderr.
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT), str(ROOT / "triton-metal_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+# --------------------------------------------------------------------------- #
+# Workload definitions
+# --------------------------------------------------------------------------- #
+
+WORKLOADS = {
+    "gemm_bf16_8192": dict(kind="gemm", M=8192, N=8192, K=8192, element="bf16"),
+    "gemm_bf16_skinny": dict(kind="gemm", M=16384, N=4096, K=14336, element="bf16"),
+    "attn_fwd_bf16_s4096": dict(kind="attn_fwd", batch=4, heads=32, seq=4096, d=128, causal=True,
+                                element="bf16"),
+    "attn_fwd_bf16_s4096_full": dict(kind="attn_fwd", batch=4, heads=32, seq=4096, d=128,
+                                     causal=False, element="bf16"),
+    "attn_fwd_bf16_s16384": dict(kind="attn_fwd", batch=4, heads=32, seq=16384, d=128, causal=True,
+                                 element="bf16"),
+    "attn_bwd_bf16_s4096_d128": dict(kind="attn_bwd", batch=8, heads=16, seq=4096, d=128,
+                                     causal=True, element="bf16"),
+    "attn_bwd_bf16_s4096_d64": dict(kind="attn_bwd", batch=8, heads=16, seq=4096, d=64,
+                                    causal=True, element="bf16"),
+}
+HEADLINE = "gemm_bf16_8192"
+ALSO = ["attn_fwd_bf16_s4096", "attn_bwd_bf16_s4096_d128"]
+
+
+def flops(w):
+    """The reference's accounting: GEMM 2MNK (GEMMBenchmark.swift:449-451);
+    forward 4 S^2 D per head (AttentionBenchmark.swift:66-68); backward
+    10 S^2 D per head, five GEMMs credited (AttentionBackwardBenchmark.swift:46-49);
+    a causal mask halves the credited work."""
+    if w["kind"] == "gemm":
+        return 2.0 * w["M"] * w["N"] * w["K"]
+    per_head = (4.0 if w["kind"] == "attn_fwd" else 10.0) * w["seq"] ** 2 * w["d"]
+    total = per_head * w["batch"] * w["heads"]
+    return total / 2 if w["causal"] else total
+
+
+def shard(total, rank, world):
+    """Contiguous block partition of `total` units: (first, count)."""
+    base, extra = divmod(total, world)
+    first = rank * base + min(rank, extra)
+    return first, base + (1 if rank < extra else 0)
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return dict(source="measured", hbm_gbs=p["hbm_gbs"], tf_burst=p["bf16_tflops"],
+                    tf_sustained=p["bf16_tflops_sustained"])
+    return dict(source="fallback", hbm_gbs=6650.0, tf_burst=1590.0, tf_sustained=1400.0)
+
+
+# --------------------------------------------------------------------------- #
+# Clock sampling during the timed region
+# --------------------------------------------------------------------------- #
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.proc, self.lines = device, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # median over the upper half: samples taken while the GPU was loaded
+        sm_sorted = sorted(sm)
+        loaded = sm_sorted[len(sm_sorted) // 2:]
+        return {"sm_mhz": float(np.median(loaded)), "sm_max_mhz": max(mx), "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- #
+# GPU arm
+# --------------------------------------------------------------------------- #
+
+class Dist:
+    """torch.distributed plumbing: barrier, max over ranks, all-gather of C."""
+
+    def __init__(self, gpus):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.torch = None
+        if self.world > 1:
+            import torch
+            import torch.distributed as dist
+            self.torch, self.dist = torch, dist
+            torch.cuda.set_device(self.local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+        elif gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max(self, value):
+        if self.world == 1:
+            return value
+        t = self.torch.tensor([value], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def close(self):
+        if self.world > 1:
+            self.dist.destroy_process_group()
+
+
+class DeviceView:
+    """Lets torch alias a libtmcuda buffer (for the NCCL all-gather of C)."""
+
+    def __init__(self, address, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr,
+                                         "data": (address, False), "version": 3}
+
+
+def pinned(array_like_bytes):
+    """A pinned host staging buffer of the given size (torch is the allocator)."""
+    import torch
+    return torch.empty(array_like_bytes, dtype=torch.uint8, pin_memory=True)
+
+
+class GemmJob:
+    """Row block [row0, row0+rows) of C = A @ B on this rank; with more than one
+    rank an all-gather assembles the replicated C."""
+
+    def __init__(self, w, dist, seed=0):
+        from triton_metal.synthetic import gemm_inputs_bf16
+        from triton_metal import _core, kernels
+        self.w, self.dist, self.core = w, dist, _core
+        M, N, K = w["M"], w["N"], w["K"]
+        self.row0, self.rows = shard(M, dist.rank, dist.world)
+        self.a_host, self.b_host = gemm_inputs_bf16(M, N, K, seed, self.row0, self.rows)
+        self.a = _core.alloc_buffer(max(2, self.a_host.nbytes))
+        self.b = _core.alloc_buffer(self.b_host.nbytes)
+        self.c_local = _core.alloc_buffer(max(2, self.rows * N * 2))
+        _core.buffer_write(self.a, 0, self.a_host.ctypes.data, self.a_host.nbytes)
+        _core.buffer_write(self.b, 0, self.b_host.ctypes.data, self.b_host.nbytes)
+        self.kernel = kernels.Matmul("bf16", (128, 256, 64))
+        self.launches_per_step = 1
+
+    def prepare(self):
+        w = self.w
+        self.args = self.kernel.arguments(self.a, self.b, self.c_local, self.rows, w["N"], w["K"])
+        if self.dist.world > 1:
+            torch = self.dist.torch
+            self.c_full = self.core.alloc_buffer(w["M"] * w["N"] * 2)
+            self.t_local = torch.as_tensor(
+                DeviceView(self.core.buffer_contents(self.c_local), (self.rows * w["N"],), "<i2"),
+                device="cuda")
+            self.t_full = torch.as_tensor(
+                DeviceView(self.core.buffer_contents(self.c_full), (w["M"] * w["N"],), "<i2"),
+                device="cuda")
+
+    def step(self):
+        from triton_metal import cuda
+        self.kernel.launch_async(*self.args)
+        if self.dist.world > 1:
+            cuda.synchronize()
+            self.dist.dist.all_gather_into_tensor(self.t_full, self.t_local)
+            self.dist.torch.cuda.synchronize()
+
+    def e2e_setup(self):
+        a, b = self.a_host, self.b_host
+        self.pin_a, self.pin_b = pinned(a.nbytes), pinned(b.nbytes)
+        self.pin_a.numpy()[:] = a.reshape(-1).view(np.uint8)
+        self.pin_b.numpy()[:] = b.reshape(-1).view(np.uint8)
+        self.pin_c = pinned(self.rows * self.w["N"] * 2)
+        return a.nbytes + b.nbytes, self.rows * self.w["N"] * 2
+
+    def e2e_step(self):
+        c = self.core
+        c.buffer_write(self.a, 0, self.pin_a.data_ptr(), self.pin_a.numel())
+        c.buffer_write(self.b, 0, self.pin_b.data_ptr(), self.pin_b.numel())
+        self.kernel.launch(*self.args)
+        c.buffer_read(self.c_local, 0, self.pin_c.data_ptr(), self.pin_c.numel())
+
+    def sample_output(self, rows):
+        got = np.empty((rows, self.w["N"]), dtype=np.uint16)
+        self.core.buffer_read(self.c_local, 0, got.ctypes.data, got.nbytes)
+        return got
+
+    def algorithmic_bytes(self):
+        w = self.w
+        return 2.0 * (self.rows * w["K"] + w["K"] * w["N"] + self.rows * w["N"])
+
+    def path(self):
+        return self.kernel.last_path()
+
+
+class AttnJob:
+    def __init__(self, w, dist, seed=0):
+        from triton_metal.synthetic import attention_inputs_bf16
+        from triton_metal import _core, kernels
+        self.w, self.dist, self.core = w, dist, _core
+        bh_total = w["batch"] * w["heads"]
+        self.bh0, self.bh = shard(bh_total, dist.rank, dist.world)
+        S, D = w["seq"], w["d"]
+        self.backward = w["kind"] == "attn_bwd"
+        names = ["q", "k", "v"] + (["do"] if self.backward else [])
+        self.host = attention_inputs_bf16(self.bh, S, D, seed + self.bh0, len(names))
+        self.buf = {}
+        nbytes = max(1, self.bh) * S * D * 2
+        for name, arr in zip(names, self.host):
+            self.buf[name] = _core.alloc_buffer(nbytes)
+            if self.bh:
+                _core.buffer_write(self.buf[name], 0, arr.ctypes.data, arr.nbytes)
+        outs = ["o"] + (["dq", "dk", "dv"] if self.backward else [])
+        for name in outs:
+            self.buf[name] = _core.alloc_buffer(nbytes)
+        for name in ("lse", "delta"):
+            self.buf[name] = _core.alloc_buffer(max(1, self.bh) * S * 4)
+        self.scale = kernels.default_scale(D)
+        self.fwd = kernels.AttnFwd("bf16", D, (128, 128), w["causal"])
+        self.kernels = [self.fwd]
+        if self.backward:
+            self.pre = kernels.AttnBwdPreprocess("bf16", D, 128)
+            self.dq = kernels.AttnBwdDq("bf16", D, (128, 128), w["causal"])
+            self.dkdv = kernels.AttnBwdDkdv("bf16", D, (128, 128), w["causal"])
+            self.kernels += [self.pre, self.dq, self.dkdv]
+        self.launches_per_step = 3 if self.backward else 1
+
+    def prepare(self):
+        b, S = self.buf, self.w["seq"]
+        self.fwd_args = self.fwd.arguments(b["q"], b["k"], b["v"], b["o"], b["lse"], self.scale,
+                                           self.bh, S)
+        if self.backward:
+            # the backward consumes the forward's O and L: run the forward once, untimed
+            if self.bh:
+                self.fwd.launch(*self.fwd_args)
+            self.pre_args = self.pre.arguments(b["o"], b["do"], b["delta"], self.bh, S)
+            self.dq_args = self.dq.arguments(b["q"], b["k"], b["v"], b["do"], b["dq"], b["lse"],
+                                             b["delta"], self.scale, self.bh, S)
+            self.dkdv_args = self.dkdv.arguments(b["q"], b["k"], b["v"], b["do"], b["dk"], b["dv"],
+                                                 b["lse"], b["delta"], self.scale, self.bh, S)
+
+    def step(self):
+        if not self.bh:
+            return
+        if self.backward:
+            self.pre.launch_async(*self.pre_args)
+            self.dq.launch_async(*self.dq_args)
+            self.dkdv.launch_async(*self.dkdv_args)
+        else:
+            self.fwd.launch_async(*self.fwd_args)
+
+    def e2e_setup(self):
+        self.pins = {}
+        names = ["q", "k", "v"] + (["do"] if self.backward else [])
+        h2d = 0
+        for name, arr in zip(names, self.host):
+            p = pinned(arr.nbytes)
+            p.numpy()[:] = arr.reshape(-1).view(np.uint8)
+            self.pins[name] = p
+            h2d += arr.nbytes
+        outs = ["dq", "dk", "dv"] if self.backward else ["o"]
+        self.pin_out = {name: pinned(self.bh * self.w["seq"] * self.w["d"] * 2) for name in outs}
+        return h2d, sum(p.numel() for p in self.pin_out.values())
+
+    def e2e_step(self):
+        c = self.core
+        for name, p in self.pins.items():
+            c.buffer_write(self.buf[name], 0, p.data_ptr(), p.numel())
+        if self.backward:
+            self.pre.launch(*self.pre_args)
+            self.dq.launch(*self.dq_args)
+            self.dkdv.launch(*self.dkdv_args)
+        else:
+            self.fwd.launch(*self.fwd_args)
+        for name, p in self.pin_out.items():
+            c.buffer_read(self.buf[name], 0, p.data_ptr(), p.numel())
+
+    def sample_output(self, name):
+        """Head 0 of an output tensor, as bf16 words."""
+        got = np.empty((1, self.w["seq"], self.w["d"]), dtype=np.uint16)
+        self.core.buffer_read(self.buf[name], 0, got.ctypes.data, got.nbytes)
+        return got
+
+    def algorithmic_bytes(self):
+        S, D = self.w["seq"], self.w["d"]
+        tensors = 8 if self.backward else 4      # q,k,v,do + dq,dk,dv (+o read) / q,k,v + o
+        return float(tensors * self.bh * S * D * 2)
+
+    def path(self):
+        return max(k.last_path() for k in self.kernels[1:] or self.kernels)
+
+
+def run_workload(name, args, dist, sample_clocks, with_cpu):
+    from triton_metal import cuda
+    w = WORKLOADS[name]
+    job = (GemmJob if w["kind"] == "gemm" else AttnJob)(w, dist)
+    job.prepare()
+    for _ in range(max(args.warmup, 3)):
+        job.step()
+    cuda.synchronize()
+    sampler = ClockSampler(dist.local) if sample_clocks else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.25)
+    before = cuda.launch_count()
+    dist.barrier()
+    cuda.synchronize()
+    cuda.timer_begin()
+    for _ in range(args.steps):
+        job.step()
+    ms = cuda.timer_end()
+    dist.barrier()
+    launches = cuda.launch_count() - before
+    ms = dist.max(ms)
+    clocks = None
+    if sampler:
+        time.sleep(0.15)
+        clocks = sampler.stop()
+    # end to end through the blocking tm_* calls with host buffers
+    h2d, d2h = job.e2e_setup()
+    for _ in range(2):
+        job.e2e_step()
+    e2e_steps = max(3, min(args.steps, 10))
+    dist.barrier()
+    cuda.synchronize()
+    cuda.timer_begin()
+    for _ in range(e2e_steps):
+        job.e2e_step()
+    e2e_ms = dist.max(cuda.timer_end())
+    total_flops = flops(w)
+    result = dict(
+        name=name, ms_per_step=ms / args.steps, tflops=total_flops / (ms / args.steps) / 1e9,
+        e2e_tflops=total_flops / (e2e_ms / e2e_steps) / 1e9, e2e_ms_per_step=e2e_ms / e2e_steps,
+        h2d=h2d, d2h=d2h, launches=launches, clocks=clocks, path=job.path(),
+        bytes_per_launch=job.algorithmic_bytes(), timed_ms=ms, cpu=None)
+    if with_cpu and dist.rank == 0:
+        result["cpu"] = cpu_baseline(name, job)
+    log(f"[{name}] {result['tflops']:.1f} TFLOP/s  {result['ms_per_step']:.3f} ms/step  "
+        f"e2e {result['e2e_tflops']:.2f} TFLOP/s  path {result['path']}  cpu {result['cpu']}")
+    return result
+
+
+def cpu_baseline(name, job=None, budget_s=12.0):
+    """The reference's CPU path for the workload (its numpy oracles, restated in
+    oracle/reference_math.py), timed on this machine's host cores on a bounded
+    sample of the same problem.  When the GPU job is given, the CPU result of
+    the sample doubles as the checker of the GPU output ("parity_error")."""
+    from oracle import reference_math as ref
+    from triton_metal.synthetic import attention_inputs_bf16, from_bf16_bits, gemm_inputs_bf16
+    w = WORKLOADS[name]
+    cores = os.cpu_count() or 1
+    parity = None
+    if w["kind"] == "gemm":
+        rows = min(w["M"], 2048) if job is None else min(job.rows, 2048)
+        if job is None:
+            a_bits, b_bits = gemm_inputs_bf16(w["M"], w["N"], w["K"], 0, 0, rows)
+        else:
+            a_bits, b_bits = job.a_host[:rows], job.b_host
+        a, b = from_bf16_bits(a_bits), from_bf16_bits(b_bits)
+        want = ref.matmul(a, b)
+        best, spent = float("inf"), 0.0
+        while spent < budget_s:
+            t0 = time.perf_counter()
+            ref.matmul(a, b)
+            dt = time.perf_counter() - t0
+            best, spent = min(best, dt), spent + dt
+        if job is not None:
+            parity = ref.relative_error(from_bf16_bits(job.sample_output(rows)), want)
+        value = 2.0 * rows * w["N"] * w["K"] / best / 1e12
+        return dict(value=value, unit="TFLOP/s", cores=cores, kind="port", parity_error=parity,
+                    sample=f"numpy float32 a@b on {rows} of {w['M']} rows of A (bf16-rounded "
+                           f"inputs), best time within {budget_s:.0f} s")
+    S, D = w["seq"], w["d"]
+    scale = 1.0 / np.sqrt(D)
+    if job is not None and job.bh and S <= 4096:
+        arrs = [h[:1] for h in job.host]
+        seq = S
+    else:
+        seq = min(S, 2048)
+        arrs = attention_inputs_bf16(1, seq, D, 0, 4)
+    tensors = [from_bf16_bits(a) for a in arrs]
+    q, k, v = tensors[:3]
+    t0 = time.perf_counter()
+    o, weights = ref.attention_forward(q, k, v, scale, w["causal"])
+    t_fwd = time.perf_counter() - t0
+    halve = 2 if w["causal"] else 1
+    if w["kind"] == "attn_fwd":
+        if job is not None and seq == S and job.bh:
+            parity = ref.relative_error(from_bf16_bits(job.sample_output("o")), o)
+        return dict(value=4.0 * seq * seq * D / halve / t_fwd / 1e12, unit="TFLOP/s", cores=cores,
+                    kind="port", parity_error=parity,
+                    sample=f"numpy attention forward, 1 (batch, head) slice at seq {seq} of {S}")
+    do = tensors[3]
+    t0 = time.perf_counter()
+    grads = ref.attention_backward(q, k, v, weights, do, scale)
+    t_bwd = time.perf_counter() - t0
+    if job is not None and seq == S and job.bh:
+        parity = max(ref.relative_error(from_bf16_bits(job.sample_output(n)), g)
+                     for n, g in zip(("dq", "dk", "dv"), grads))
+    return dict(value=10.0 * seq * seq * D / halve / t_bwd / 1e12, unit="TFLOP/s", cores=cores,
+                kind="port", parity_error=parity,
+                sample=f"numpy attention backward, 1 (batch, head) slice at seq {seq} of {S}")
+
+
+def reference_arm(args):
+    """`--impl reference`: the reference's CPU implementation of the headline
+    workload (numpy float32 matmul on bf16-rounded inputs) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import reference_math as ref
+    from triton_metal.synthetic import from_bf16_bits, gemm_inputs_bf16
+    name = args.workload or HEADLINE
+    w = WORKLOADS[name]
+    if w["kind"] != "gemm":
+        base = cpu_baseline(name)
+        value, ms, sample = base["value"], None, base["sample"]
+    else:
+        rows = 1024
+        a, b = gemm_inputs_bf16(w["M"], w["N"], w["K"], 0, 0, rows)
+        a, b = from_bf16_bits(a), from_bf16_bits(b)
+        for _ in range(min(args.warmup, 3)):
+            ref.matmul(a, b)
+        t0 = time.perf_counter()
+        steps = min(args.steps, 20)
+        for _ in range(steps):
+            ref.matmul(a, b)
+        dt = (time.perf_counter() - t0) / steps
+        value = 2.0 * rows * w["N"] * w["K"] / dt / 1e12
+        ms = dt * 1e3 * (w["M"] / rows)
+        sample = f"each step = numpy a@b on {rows} of {w['M']} rows of A, scaled to the full problem"
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": "bf16_gemm_fa2_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": {"workload": name, **{k: v for k, v in w.items() if k != "kind"}},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="tmcuda", choices=["tmcuda", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--also", default=None, help="comma-separated extra workloads ('none' for none)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    from triton_metal import _core, cuda
+    cuda.set_device(local)
+    if not _core.is_usable():
+        raise SystemExit("libtmcuda cannot run here: " + str(_core.unusable_reason()))
+    dist = Dist(args.gpus)
+    name = args.workload or HEADLINE
+    head = run_workload(name, args, dist, True, not args.no_cpu_baseline and dist.world == 1)
+    also = {}
+    extra = ALSO if args.also is None else [x for x in args.also.split(",") if x and x != "none"]
+    if args.workload:
+        extra = [] if args.also is None else extra
+    for other in extra:
+        r = run_workload(other, args, dist, False, not args.no_cpu_baseline and dist.world == 1)
+        also[other] = {"tflops": r["tflops"], "ms_per_step": r["ms_per_step"],
+                       "e2e_tflops": r["e2e_tflops"], "cpu_baseline": r["cpu"],
+                       "path": r["path"],
+                       "frac_of_bf16_peak": r["tflops"] / dist.world / peaks()["tf_burst"]}
+    if dist.rank == 0:
+        w = WORKLOADS[name]
+        pk = peaks()
+        long_region = head["timed_ms"] > 1000.0
+        peak = pk["tf_sustained"] if long_region else pk["tf_burst"]
+        per_gpu = head["tflops"] / dist.world
+        roofline = {
+            "bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
+            "frac": per_gpu / peak,
+            "peak_source": f"{pk['source']} cuBLAS bf16 {'sustained' if long_region else 'burst'}",
+            "traffic": None,
+            "algorithmic_bytes_per_launch": head["bytes_per_launch"],
+        }
+        line = {
+            "metric": "bf16_gemm_fa2_tflops", "value": head["tflops"], "unit": "TFLOP/s",
+            "n_gpus": dist.world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": name, **{k: v for k, v in w.items() if k != "kind"},
+                       "sharding": "rows of M + all-gather of C" if w["kind"] == "gemm" else "(batch, head)",
+                       "l2": "inputs larger than L2, no flush"},
+            "per_gpu_tflops": per_gpu,
+            "frac_of_bf16_peak": per_gpu / pk["tf_burst"],
+            "roofline": roofline,
+            "e2e": {"value": head["e2e_tflops"], "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": head["h2d"], "d2h_bytes_per_step": head["d2h"],
+                    "ms_per_step": head["e2e_ms_per_step"]},
+            "gpu_launches": head["launches"],
+            "kernel_path": {1: "simt", 2: "tcgen05"}.get(head["path"], "none"),
+            "clocks": head["clocks"],
+            "also": also,
+        }
+        if head["cpu"] is not None:
+            line["cpu_baseline"] = head["cpu"]
+        print(json.dumps(line), flush=True)
+    dist.close()
+
+
+if __name__ == "__main__":
+    main()

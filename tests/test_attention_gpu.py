@@ -1,0 +1,175 @@
+"""attn_fwd / attn_bwd_* parity through the C ABI, against the numpy oracle.
+
+Shapes follow Tests/TritonMetalCoreTests/AttentionTests.swift:119-135 (s127/512/
+96/33/64, d64/80), the overflow case :161-177, AttentionBackwardTests.swift and
+python/examples/attention_training.py:255-330 (h2 s96 d64, loss must decrease);
+tolerances: fp32 1e-5 with the reference's relative_error, 16-bit 2e-2."""
+
+import numpy as np
+import pytest
+
+import tmtest
+from oracle import inputs, reference_math as ref
+from triton_metal import cuda
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"f32": 1e-5, "f16": 2e-2, "bf16": 2e-2}
+
+
+@pytest.fixture(autouse=True)
+def _gpu():
+    tmtest.require_gpu()
+
+
+def check_all(q, k, v, do, element, causal, block=(128, 128), path=0, tol=None):
+    tol = tol or TOL[element]
+    q, k, v, do = (ref.round_to(t, element) for t in (q, k, v, do))
+    want_o, want_lse, want_dq, want_dk, want_dv = tmtest.oracle_attention(q, k, v, do, causal)
+    with tmtest.AttentionRun(q, k, v, do, element, causal, block, path) as run:
+        o, lse = run.forward()
+        dq, dk, dv = run.backward()
+        paths = run.paths()
+    assert ref.relative_error(o, want_o) <= tol, "O"
+    assert np.max(np.abs(lse - want_lse)) <= (1e-4 if element == "f32" else 2e-2), "LSE"
+    for name, got, want in (("dQ", dq, want_dq), ("dK", dk, want_dk), ("dV", dv, want_dv)):
+        assert ref.relative_error(got, want) <= tol, name
+    return paths
+
+
+@pytest.mark.parametrize("bh,seq,d", [(2, 96, 64), (1, 127, 64), (1, 512, 64), (3, 33, 80),
+                                      (2, 64, 64), (1, 48, 64), (2, 200, 128), (1, 70, 32)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp32_shapes(bh, seq, d, causal):
+    q, k, v, do = inputs.attention_normal(bh, seq, d, seed=seq + d)
+    check_all(q, k, v, do, "f32", causal, block=(16, 32))
+
+
+@pytest.mark.parametrize("element", ["f16", "bf16"])
+@pytest.mark.parametrize("bh,seq,d", [(2, 96, 64), (1, 127, 64), (2, 33, 80), (2, 256, 128)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_16bit_shapes(element, bh, seq, d, causal):
+    q, k, v, do = inputs.attention_normal(bh, seq, d, seed=seq)
+    check_all(q, k, v, do, element, causal, block=(32, 32))
+
+
+def test_golden_case_of_the_reference_example():
+    """h2 s96 d64 seed 0: the outputs of the reference's own numpy functions."""
+    from pathlib import Path
+    golden = np.load(Path(__file__).resolve().parent / "golden" / "attention_reference.npz")
+    rng = np.random.default_rng(0)
+    q, k, v, target = [rng.standard_normal((2, 96, 64), dtype=np.float32) * np.float32(0.5)
+                       for _ in range(4)]
+    with tmtest.AttentionRun(q, k, v, np.zeros_like(q), "f32", False, (16, 32)) as run:
+        o, _ = run.forward()
+        assert ref.relative_error(o, golden["h2_s96_d64_seed0.o"]) < 2e-5
+        d_out = (golden["h2_s96_d64_seed0.o"] - target).astype(np.float32)
+        run.bufs["do"].copy_from(np.ascontiguousarray(d_out).ctypes.data)
+        dq, dk, dv = run.backward()
+    for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
+        assert ref.relative_error(got, golden[f"h2_s96_d64_seed0.{name}"]) < 2e-5, name
+
+
+def test_overflow_stability():
+    """Scores spread over +-12 with scale 1 stay finite
+    (AttentionTests.swift:161-177)."""
+    q, k, v, do = inputs.attention_normal(1, 64, 64, seed=1)
+    q = q * np.float32(12.0 / 8.0)
+    k = k * np.float32(12.0 / 8.0)
+    paths = check_all(q, k, v, do, "f32", False, block=(16, 32), tol=2e-5)
+    assert paths["fwd"] == cuda.PATH_SIMT
+
+
+def test_rows_outside_the_grid_are_left_alone():
+    q, k, v, do = inputs.attention_normal(1, 64, 64, seed=8)
+    with tmtest.AttentionRun(q, k, v, do, "f32", False, (16, 32)) as run:
+        from triton_metal import _core
+        fwd = run.kernels["fwd"]
+        grid, kinds, values = fwd.arguments(run.h("q"), run.h("k"), run.h("v"), run.h("o"),
+                                            run.h("lse"), run.scale, run.bh, run.seq)
+        fwd.launch((2, 1, 1), kinds, values)            # only the first 32 query rows
+        o = tmtest.fetch(run.bufs["o"])
+    want, _ = ref.attention_forward(q, k, v, ref.default_scale(64))
+    assert ref.relative_error(o[:, :32], want[:, :32]) <= 1e-5
+    assert np.all(o[:, 32:] == 0)
+
+
+def test_gradient_descent_on_projection_weights():
+    """The small fp32 configuration's training loop: d_model 128 = 2 heads x 64,
+    seq 96, weights N(0, 0.02), MSE to an N(0,1) target, 8 SGD steps at lr 1e-3;
+    attention forward/backward on the GPU, loss must fall every step and track
+    the oracle's trajectory."""
+    rng = np.random.default_rng(0)
+    seq, d_model, heads = 96, 128, 2
+    x = rng.standard_normal((seq, d_model), dtype=np.float32)
+    target = rng.standard_normal((seq, d_model), dtype=np.float32)
+    w_gpu = [rng.standard_normal((d_model, d_model), dtype=np.float32) * np.float32(0.02)
+             for _ in range(4)]
+    w_ref = [w.copy() for w in w_gpu]
+    scale = ref.default_scale(d_model // heads)
+    zeros = np.zeros((heads, seq, d_model // heads), dtype=np.float32)
+
+    with tmtest.AttentionRun(zeros, zeros, zeros, zeros, "f32", False, (16, 32)) as run:
+        def gpu_fwd(q, k, v):
+            for name, t in (("q", q), ("k", k), ("v", v)):
+                run.bufs[name].copy_from(np.ascontiguousarray(t, dtype=np.float32).ctypes.data)
+            o, _ = run.forward()
+            return o, None
+
+        def gpu_bwd(q, k, v, aux, do):
+            run.bufs["do"].copy_from(np.ascontiguousarray(do, dtype=np.float32).ctypes.data)
+            return run.backward()
+
+        ref_fwd, ref_bwd = ref.oracle_attention(scale)
+        losses, ref_losses = [], []
+        for _ in range(8):
+            loss, grads = ref.projection_step(x, w_gpu, target, heads, scale, gpu_fwd, gpu_bwd)
+            ref_loss, ref_grads = ref.projection_step(x, w_ref, target, heads, scale, ref_fwd, ref_bwd)
+            losses.append(loss)
+            ref_losses.append(ref_loss)
+            w_gpu = [w - np.float32(1e-3) * g for w, g in zip(w_gpu, grads)]
+            w_ref = [w - np.float32(1e-3) * g for w, g in zip(w_ref, ref_grads)]
+    assert all(b < a for a, b in zip(losses, losses[1:])), losses
+    assert np.allclose(losses, ref_losses, rtol=1e-5)
+
+
+def test_direct_descent_of_the_reference_example():
+    """attention_training.py:314-329 - 8 steps on q, k, v at rate 0.5; the loss
+    after the last step is below the first."""
+    rng = np.random.default_rng(0)
+    q, k, v, target = [rng.standard_normal((2, 96, 64), dtype=np.float32) * np.float32(0.5)
+                       for _ in range(4)]
+    with tmtest.AttentionRun(q, k, v, np.zeros_like(q), "f32", False, (16, 32)) as run:
+        def step(q, k, v):
+            for name, t in (("q", q), ("k", k), ("v", v)):
+                run.bufs[name].copy_from(np.ascontiguousarray(t).ctypes.data)
+            o, _ = run.forward()
+            return o
+        first = None
+        for _ in range(8):
+            o = step(q, k, v)
+            loss = 0.5 * float(np.sum((o - target) ** 2))
+            first = loss if first is None else first
+            run.bufs["do"].copy_from(np.ascontiguousarray((o - target).astype(np.float32)).ctypes.data)
+            dq, dk, dv = run.backward()
+            q, k, v = q - 0.5 * dq, k - 0.5 * dk, v - 0.5 * dv
+        final = 0.5 * float(np.sum((step(q, k, v) - target) ** 2))
+    assert final < first
+
+
+def test_attention_argument_validation(core):
+    from triton_metal import kernels
+    fwd = kernels.AttnFwd("f32", 64, (16, 32))
+    small = tmtest.empty((1, 16, 64), "f32")
+    stat = tmtest.empty((1, 16), "f32")
+    try:
+        grid, kinds, values = fwd.arguments(small.tm_handle, small.tm_handle, small.tm_handle,
+                                            small.tm_handle, stat.tm_handle, 0.125, 1, 32)
+        with pytest.raises(RuntimeError, match="beyond its"):
+            core.launch(fwd.handle, grid, 128, kinds, values)
+        with pytest.raises(RuntimeError, match="does not apply"):
+            cuda.set_option(kernels.AttnBwdPreprocess("f32", 64).handle, "causal", 1)
+    finally:
+        fwd.release()
+        small.free()
+        stat.free()

@@ -1,0 +1,173 @@
+"""matmul_kernel parity through the C ABI, against the numpy oracle.
+
+Shapes and tolerances follow Tests/TritonMetalCoreTests/DotTests.swift (ragged
+shapes tol 1e-5 :369-396, strides :403-461, f16 :466-506, bf16 from already
+rounded inputs :514-554, guard bands :609-646) and the benchmark configurations
+(fp32 256^3 uniform[-1,1); bf16 N(0,1)/sqrt(K) squares and the skinny shape)."""
+
+import numpy as np
+import pytest
+
+import tmtest
+from oracle import inputs, reference_math as ref
+from triton_metal import cuda
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"f32": 1e-5, "f16": 2e-2, "bf16": 2e-2}
+
+
+@pytest.fixture(autouse=True)
+def _gpu():
+    tmtest.require_gpu()
+
+
+def test_fp32_256_cubed_uniform():
+    a, b = inputs.gemm_uniform(256, 256, 256, seed=0)
+    for block in ((128, 64, 32), (64, 64, 32), (64, 64, 64), (32, 32, 32)):
+        c, _ = tmtest.run_matmul(a, b, "f32", block)
+        assert ref.relative_error(c, ref.matmul(a, b)) <= 1e-5
+        assert float(np.max(np.abs(c - ref.matmul(a, b)))) < 1e-3     # matmul.py:78
+
+
+@pytest.mark.parametrize("shape", [(64, 64, 64), (129, 257, 65), (33, 17, 129), (1, 1, 1),
+                                   (128, 96, 40), (200, 120, 72)])
+@pytest.mark.parametrize("element", ["f32", "f16", "bf16"])
+def test_ragged_shapes(shape, element):
+    M, N, K = shape
+    a, b = inputs.gemm_normal(M, N, K, seed=M + N + K)
+    a, b = ref.round_to(a, element), ref.round_to(b, element)
+    c, _ = tmtest.run_matmul(a, b, element, (64, 64, 16))
+    assert ref.relative_error(c, ref.matmul(a, b)) <= TOL[element]
+
+
+def test_non_unit_and_padded_strides():
+    """A read through a transposed view, B with padded rows, C with padded rows."""
+    M, N, K = 96, 80, 72
+    a, b = inputs.gemm_normal(M, N, K, seed=5)
+    a_t = np.ascontiguousarray(a.T)                     # stored [K, M]: stride_am=1, stride_ak=M
+    b_pad = np.zeros((K, N + 24), dtype=np.float32)
+    b_pad[:, :N] = b
+    strides = (1, M, N + 24, 1, N + 8, 1)
+    ab, bb = tmtest.upload(a_t, "f32"), tmtest.upload(b_pad, "f32")
+    cb = tmtest.empty((M, N + 8), "f32")
+    from triton_metal import kernels
+    mm = kernels.Matmul("f32", (32, 32, 16))
+    try:
+        mm(ab.tm_handle, bb.tm_handle, cb.tm_handle, M, N, K, strides)
+        c = tmtest.fetch(cb)
+        assert ref.relative_error(c[:, :N], ref.matmul(a, b)) <= 1e-5
+        assert np.all(c[:, N:] == 0)                    # padding columns untouched
+    finally:
+        mm.release()
+        for buf in (ab, bb, cb):
+            buf.free()
+
+
+@pytest.mark.parametrize("element", ["f32", "bf16"])
+def test_masked_stores_never_touch_the_guard_band(element):
+    """C lives inside a larger buffer filled with a sentinel."""
+    M, N, K = 129, 136, 65
+    a, b = inputs.gemm_normal(M, N, K, seed=9)
+    a, b = ref.round_to(a, element), ref.round_to(b, element)
+    rows, cols = M + 7, N + 8
+    c, _ = tmtest.run_matmul(a, b, element, (64, 64, 16), strides=(K, 1, N, 1, cols, 1),
+                             c_shape=(rows, cols), c_fill=-7.0)
+    assert ref.relative_error(c[:M, :N], ref.matmul(a, b)) <= TOL[element]
+    assert np.all(c[M:, :] == -7.0) and np.all(c[:, N:] == -7.0)
+
+
+def test_programs_outside_the_grid_are_not_run():
+    """A grid smaller than cdiv(M,BM) x cdiv(N,BN) leaves the other tiles alone."""
+    a, b = inputs.gemm_normal(128, 128, 64, seed=2)
+    c, _ = tmtest.run_matmul(a, b, "f32", (64, 64, 16), c_fill=3.0, grid=(1, 2, 1))
+    want = ref.matmul(a, b)
+    assert ref.relative_error(c[:64], want[:64]) <= 1e-5
+    assert np.all(c[64:] == 3.0)
+
+
+@pytest.mark.parametrize("element", ["bf16", "f16"])
+@pytest.mark.parametrize("n", [1024, 2048])
+def test_square_16bit_takes_the_tensor_core_path(element, n):
+    a, b = inputs.gemm_normal(n, n, n, seed=n)
+    a, b = ref.round_to(a, element), ref.round_to(b, element)
+    c, path = tmtest.run_matmul(a, b, element)
+    assert path == cuda.PATH_TCGEN05
+    assert ref.relative_error(c, ref.matmul(a, b)) <= TOL[element]
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 64), (256, 264, 72), (384, 520, 200), (1000, 776, 136),
+                                   (130, 72, 64)])
+def test_tensor_core_path_ragged_edges(shape):
+    M, N, K = shape
+    a, b = inputs.gemm_normal(M, N, K, seed=M ^ N ^ K)
+    a, b = ref.round_to(a, "bf16"), ref.round_to(b, "bf16")
+    rows, cols = M + 3, N + 8
+    c, path = tmtest.run_matmul(a, b, "bf16", path=cuda.PATH_TCGEN05,
+                                strides=(K, 1, N, 1, cols, 1), c_shape=(rows, cols), c_fill=-5.0)
+    assert path == cuda.PATH_TCGEN05
+    assert ref.relative_error(c[:M, :N], ref.matmul(a, b)) <= 2e-2
+    assert np.all(c[M:, :] == -5.0) and np.all(c[:, N:] == -5.0)
+
+
+def test_both_paths_agree_on_bf16():
+    a, b = inputs.gemm_normal(512, 512, 512, seed=3)
+    a, b = ref.round_to(a, "bf16"), ref.round_to(b, "bf16")
+    c_tc, p1 = tmtest.run_matmul(a, b, "bf16", path=cuda.PATH_TCGEN05)
+    c_simt, p2 = tmtest.run_matmul(a, b, "bf16", path=cuda.PATH_SIMT)
+    assert (p1, p2) == (cuda.PATH_TCGEN05, cuda.PATH_SIMT)
+    # both round an fp32 accumulation once: they may differ by one bf16 ulp at most
+    assert ref.relative_error(c_tc, c_simt) <= 2 ** -7
+
+
+def test_large_bf16_against_sampled_oracle_rows():
+    """4096^3: the oracle checks sampled row blocks; linearity covers the rest."""
+    n = 4096
+    a, b = inputs.gemm_normal(n, n, n, seed=7)
+    a, b = ref.round_to(a, "bf16"), ref.round_to(b, "bf16")
+    c, path = tmtest.run_matmul(a, b, "bf16")
+    assert path == cuda.PATH_TCGEN05
+    rows = np.r_[0:64, 2000:2064, n - 64:n]
+    assert ref.relative_error(c[rows], ref.matmul(a[rows], b)) <= 2e-2
+    # checksum of checksums: column sums of C equal (column sums of A) @ B
+    want = a.astype(np.float64).sum(axis=0) @ b.astype(np.float64)
+    got = c.astype(np.float64).sum(axis=0)
+    assert np.max(np.abs(got - want)) / np.max(np.abs(want)) < 2e-2
+
+
+def test_skinny_bf16_shape_sampled():
+    M, N, K = 16384, 4096, 14336
+    rng = np.random.default_rng(1)
+    a = ref.round_to(rng.standard_normal((M, K), dtype=np.float32) / np.float32(np.sqrt(K)), "bf16")
+    b = ref.round_to(rng.standard_normal((K, N), dtype=np.float32) / np.float32(np.sqrt(K)), "bf16")
+    c, path = tmtest.run_matmul(a, b, "bf16")
+    assert path == cuda.PATH_TCGEN05
+    rows = np.r_[0:32, 8000:8032, M - 32:M]
+    assert ref.relative_error(c[rows], ref.matmul(a[rows], b)) <= 2e-2
+
+
+def test_launch_validation_on_the_device(core):
+    """Errors the reference raises at dispatch (Runtime.swift:201-211) plus the
+    host-side extent check that stands in for a memory sanitizer."""
+    from triton_metal import kernels
+    mm = kernels.Matmul("f32", (64, 64, 16))
+    a = tmtest.empty((64, 64), "f32")
+    try:
+        grid, kinds, values = mm.arguments(a.tm_handle, a.tm_handle, a.tm_handle, 64, 64, 64)
+        with pytest.raises(RuntimeError, match="grid must be positive"):
+            core.launch(mm.handle, (0, 1, 1), 128, kinds, values)
+        with pytest.raises(RuntimeError, match="threadsPerThreadgroup must be positive"):
+            core.launch(mm.handle, grid, 0, kinds, values)
+        with pytest.raises(RuntimeError, match="exceeds the pipeline maximum"):
+            core.launch(mm.handle, grid, 2048, kinds, values)
+        big = list(values)
+        big[3] = 128                                     # M = 128 rows of a 64-row buffer
+        with pytest.raises(RuntimeError, match="beyond its"):
+            core.launch(mm.handle, (2, 1, 1), 128, kinds, big)
+        kinds_bad = list(kinds)
+        kinds_bad[0] = 1
+        with pytest.raises(RuntimeError, match="is a pointer"):
+            core.launch(mm.handle, grid, 128, kinds_bad, values)
+    finally:
+        mm.release()
+        a.free()

@@ -689,6 +689,11 @@ int64_t tm_load_kernel(int64_t library, const char* name) {
     if (std::string(name) == kernel_entry_name(k.id)) {
       auto obj = std::make_shared<KernelObj>();
       obj->desc = k;
+      // $TMCUDA_FORCE_PATH=simt|tcgen05 presets the "path" option of every kernel.
+      if (const char* force = std::getenv("TMCUDA_FORCE_PATH")) {
+        if (std::string(force) == "simt") obj->path_option = 1;
+        else if (std::string(force) == "tcgen05") obj->path_option = 2;
+      }
       return g_handles.insert(obj);
     }
   }
