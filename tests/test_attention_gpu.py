@@ -64,7 +64,7 @@ def test_golden_case_of_the_reference_example():
         o, _ = run.forward()
         assert ref.relative_error(o, golden["h2_s96_d64_seed0.o"]) < 2e-5
         d_out = (golden["h2_s96_d64_seed0.o"] - target).astype(np.float32)
-        run.bufs["do"].copy_from(np.ascontiguousarray(d_out).ctypes.data)
+        tmtest.put(run.bufs["do"], d_out)
         dq, dk, dv = run.backward()
     for name, got in (("dq", dq), ("dk", dk), ("dv", dv)):
         assert ref.relative_error(got, golden[f"h2_s96_d64_seed0.{name}"]) < 2e-5, name
@@ -112,12 +112,12 @@ def test_gradient_descent_on_projection_weights():
     with tmtest.AttentionRun(zeros, zeros, zeros, zeros, "f32", False, (16, 32)) as run:
         def gpu_fwd(q, k, v):
             for name, t in (("q", q), ("k", k), ("v", v)):
-                run.bufs[name].copy_from(np.ascontiguousarray(t, dtype=np.float32).ctypes.data)
+                tmtest.put(run.bufs[name], np.asarray(t, dtype=np.float32))
             o, _ = run.forward()
             return o, None
 
         def gpu_bwd(q, k, v, aux, do):
-            run.bufs["do"].copy_from(np.ascontiguousarray(do, dtype=np.float32).ctypes.data)
+            tmtest.put(run.bufs["do"], np.asarray(do, dtype=np.float32))
             return run.backward()
 
         ref_fwd, ref_bwd = ref.oracle_attention(scale)
@@ -142,7 +142,7 @@ def test_direct_descent_of_the_reference_example():
     with tmtest.AttentionRun(q, k, v, np.zeros_like(q), "f32", False, (16, 32)) as run:
         def step(q, k, v):
             for name, t in (("q", q), ("k", k), ("v", v)):
-                run.bufs[name].copy_from(np.ascontiguousarray(t).ctypes.data)
+                tmtest.put(run.bufs[name], np.asarray(t, dtype=np.float32))
             o, _ = run.forward()
             return o
         first = None
@@ -150,7 +150,7 @@ def test_direct_descent_of_the_reference_example():
             o = step(q, k, v)
             loss = 0.5 * float(np.sum((o - target) ** 2))
             first = loss if first is None else first
-            run.bufs["do"].copy_from(np.ascontiguousarray((o - target).astype(np.float32)).ctypes.data)
+            tmtest.put(run.bufs["do"], (o - target).astype(np.float32))
             dq, dk, dv = run.backward()
             q, k, v = q - 0.5 * dq, k - 0.5 * dk, v - 0.5 * dv
         final = 0.5 * float(np.sum((step(q, k, v) - target) ** 2))
@@ -167,8 +167,10 @@ def test_attention_argument_validation(core):
                                             small.tm_handle, stat.tm_handle, 0.125, 1, 32)
         with pytest.raises(RuntimeError, match="beyond its"):
             core.launch(fwd.handle, grid, 128, kinds, values)
+        pre = kernels.AttnBwdPreprocess("f32", 64)
         with pytest.raises(RuntimeError, match="does not apply"):
-            cuda.set_option(kernels.AttnBwdPreprocess("f32", 64).handle, "causal", 1)
+            cuda.set_option(pre.handle, "causal", 1)
+        pre.release()
     finally:
         fwd.release()
         small.free()

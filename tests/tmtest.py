@@ -14,6 +14,14 @@ def upload(array, element):
     return MetalBuffer.from_numpy(np.ascontiguousarray(array).astype(ref.storage_dtype(element)))
 
 
+def put(buffer, array, element="f32"):
+    """Overwrite a buffer from a numpy array (kept alive for the whole call)."""
+    staged = np.ascontiguousarray(array).astype(ref.storage_dtype(element), copy=False)
+    staged = np.ascontiguousarray(staged)
+    buffer.copy_from(staged.ctypes.data, staged.nbytes)
+    return staged
+
+
 def empty(shape, element):
     return MetalBuffer(shape, BUFFER_DTYPE[element])
 
@@ -31,8 +39,7 @@ def run_matmul(a, b, element, block=(128, 128, 64), path=0, strides=None, c_shap
     ab, bb = upload(a, element), upload(b, element)
     cb = empty(c_shape or (M, N), element)
     if c_fill is not None:
-        filled = np.full(c_shape or (M, N), c_fill, dtype=np.float32)
-        cb.copy_from(filled.astype(ref.storage_dtype(element)).ctypes.data)
+        put(cb, np.full(c_shape or (M, N), c_fill, dtype=np.float32), element)
     mm = kernels.Matmul(element, block)
     try:
         mm.set_path(path)

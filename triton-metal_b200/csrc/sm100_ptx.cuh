@@ -60,7 +60,7 @@ struct WaitCtx {
 
 constexpr long long kWaitCycles = 2000000000ll;   // about one second
 
-__device__ __noinline__ void report_timeout(const WaitCtx& w, uint32_t site, uint32_t extra) {
+static __device__ __noinline__ void report_timeout(const WaitCtx& w, uint32_t site, uint32_t extra) {
   if (atomicCAS(&w.status->code, 0u, 1u) == 0u) {
     w.status->where = site;
     w.status->block = blockIdx.x + blockIdx.y * gridDim.x;
