@@ -1,0 +1,626 @@
+// attn_bwd_dq and attn_bwd_dkdv on tcgen05 / TMEM for 16-bit elements, head
+// dimension 64 or 128, optional causal mask.
+//
+// Semantics: Sources/TritonMetalBench/AttentionBackwardKernel.swift:151-344 (dq)
+// and :354-575 (dkdv).  P is rebuilt from the forward's row statistic L (log2
+// units): P = exp2(qk_scale * QK^T - L);  dP = dO V^T;  dS = P (dP - Delta);
+// dQ = sm_scale dS K;  dV = P^T dO;  dK = sm_scale dS^T Q.  dS and P are
+// rounded to the element type before they enter a contraction.  The two
+// directions stay separate kernels, as in the reference, so every gradient is
+// deterministic (no atomics).
+//
+// Both kernels: one CTA per 128 resident rows of one (batch, head); warp 4 issues
+// TMA loads, warp 5 issues tcgen05.mma, warps 0-3 (one thread per resident row =
+// one TMEM lane) do the exponentials and products.  The 16-bit P / dS tiles never
+// touch shared memory: they are written back into the TMEM columns their fp32
+// sources came from and feed the next MMA as TMEM operands.
+//
+// TMEM columns (512):  dq:    S[2] | dP (dS aliases) | dQ
+//                      dkdv:  S^T (P^T aliases) | dP^T (dS^T aliases) | dV | dK
+//
+// HBM layout: Q, K, V, dO, dQ, dK, dV [BH, S, D] with D contiguous; L, Delta
+// [BH, S] fp32.
+
+#include "sm100_ptx.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace tmc {
+namespace {
+
+using namespace ptx;
+
+constexpr int BLK = 128;              // rows per tile on both sides
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr float kLog2e = 1.44269504088896340736f;
+
+struct Params {
+  void* out0;         // dQ | dK
+  void* out1;         // dV
+  const float* lse;
+  const float* delta;
+  float sm_scale;
+  int64_t stride_head, stride_seq, stride_lse;
+  int n_ctx, rows, causal;
+};
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar, int row0,
+                                          int bh) {
+#pragma unroll
+  for (int h = 0; h < D / 64; ++h) tma_load_3d(dst + h * (BLK * 128), map, bar, h * 64, row0, bh);
+}
+
+// S-shaped product: D_tmem[128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles.
+template <int D>
+__device__ __forceinline__ void mma_nt(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc) {
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const uint32_t off = (kk / 4) * (BLK * 128) + (kk % 4) * 32;
+    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + off, 0, 1024), smem_desc_sw128(b_addr + off, 0, 1024),
+               idesc, kk != 0);
+  }
+}
+
+// Accumulating product with a TMEM operand: D_tmem[128 x D] (+)= A_tmem[128 x 128] * B[128 x D],
+// B a row-major (MN-major) tile of 128 rows.
+template <int D>
+__device__ __forceinline__ void mma_tn(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t idesc,
+                                       bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < BLK / 16; ++kk)
+    mma_f16_ts(d_tmem, a_tmem + kk * 8, smem_desc_sw128(b_addr + kk * 2048, BLK * 128, 1024), idesc,
+               accumulate || kk != 0);
+}
+
+__device__ __forceinline__ void drain(uint32_t bar, uint32_t parity, const WaitCtx& wc, uint32_t site) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kWaitCycles) { report_timeout(wc, site, parity); break; }
+  }
+}
+
+// ===========================================================================
+// dQ
+// ===========================================================================
+struct SharedDq {
+  alignas(8) uint64_t qdo_full;
+  alignas(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  alignas(8) uint64_t s_full[2];
+  alignas(8) uint64_t dp_full, ds_full, dq_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename T, int D, uint32_t FMT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                      Params prm, DeviceStatus* status) {
+  constexpr int TILE = BLK * D * 2;
+  constexpr int S_COL0 = 0, S_COL1 = 128, DP_COL = 256, DQ_COL = 384;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t q_addr = smem_u32(smem), do_addr = q_addr + TILE, k_addr = do_addr + TILE,
+                 v_addr = k_addr + 2 * TILE;
+  SharedDq& ss = *reinterpret_cast<SharedDq*>(smem + 6 * TILE);
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  WaitCtx wc{&ss.abort_flag, status};
+  const int m_tile = prm.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int bh = blockIdx.y;
+  const int m0 = m_tile * BLK;
+  int key_end = prm.n_ctx;
+  if (prm.causal) key_end = min(prm.n_ctx, m0 + BLK);
+  const int n_blocks = (key_end + BLK - 1) / BLK;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ss.qdo_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&ss.k_full[s]), 1);
+      mbar_init(smem_u32(&ss.k_empty[s]), 1);
+      mbar_init(smem_u32(&ss.v_full[s]), 1);
+      mbar_init(smem_u32(&ss.v_empty[s]), 1);
+      mbar_init(smem_u32(&ss.s_full[s]), 1);
+    }
+    mbar_init(smem_u32(&ss.dp_full), 1);
+    mbar_init(smem_u32(&ss.ds_full), 128);
+    mbar_init(smem_u32(&ss.dq_done), 1);
+    ss.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&ss.tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ss.tmem_base;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      tma_prefetch_desc(&map_do);
+      mbar_expect_tx(smem_u32(&ss.qdo_full), 2 * TILE);
+      load_tile<D>(q_addr, &map_q, smem_u32(&ss.qdo_full), m0, bh);
+      load_tile<D>(do_addr, &map_do, smem_u32(&ss.qdo_full), m0, bh);
+      int issued = 0;
+      for (int j = 0; j < n_blocks; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(smem_u32(&ss.k_empty[s]), ph ^ 1, wc, 31)) break;
+        mbar_expect_tx(smem_u32(&ss.k_full[s]), TILE);
+        load_tile<D>(k_addr + s * TILE, &map_k, smem_u32(&ss.k_full[s]), j * BLK, bh);
+        if (!mbar_wait(smem_u32(&ss.v_empty[s]), ph ^ 1, wc, 32)) {
+          drain(smem_u32(&ss.k_full[s]), ph, wc, 39);
+          break;
+        }
+        mbar_expect_tx(smem_u32(&ss.v_full[s]), TILE);
+        load_tile<D>(v_addr + s * TILE, &map_v, smem_u32(&ss.v_full[s]), j * BLK, bh);
+        ++issued;
+      }
+      drain(smem_u32(&ss.qdo_full), 0, wc, 39);
+      for (int j = max(0, issued - 2); j < issued; ++j) {
+        drain(smem_u32(&ss.k_full[j & 1]), (j >> 1) & 1, wc, 39);
+        drain(smem_u32(&ss.v_full[j & 1]), (j >> 1) & 1, wc, 39);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_nt = make_idesc(FMT, BLK, BLK, 0, 0);
+      constexpr uint32_t idesc_tn = make_idesc(FMT, BLK, D, 0, 1);
+      bool ok = mbar_wait(smem_u32(&ss.qdo_full), 0, wc, 33);
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(smem_u32(&ss.k_full[s]), (j >> 1) & 1, wc, 34)) return false;
+        tc_fence_after();
+        mma_nt<D>(tmem + (s ? S_COL1 : S_COL0), q_addr, k_addr + s * TILE, idesc_nt);
+        mma_commit(smem_u32(&ss.s_full[s]));
+        return true;
+      };
+      auto issue_dp = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(smem_u32(&ss.v_full[s]), (j >> 1) & 1, wc, 35)) return false;
+        tc_fence_after();
+        mma_nt<D>(tmem + DP_COL, do_addr, v_addr + s * TILE, idesc_nt);
+        mma_commit(smem_u32(&ss.v_empty[s]));
+        mma_commit(smem_u32(&ss.dp_full));
+        return true;
+      };
+      if (ok) ok = issue_qk(0) && issue_dp(0);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (j + 1 < n_blocks && !issue_qk(j + 1)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&ss.ds_full), j & 1, wc, 36)) { ok = false; break; }
+        tc_fence_after();
+        mma_tn<D>(tmem + DQ_COL, tmem + DP_COL, k_addr + (j & 1) * TILE, idesc_tn, j != 0);
+        mma_commit(smem_u32(&ss.k_empty[j & 1]));
+        if (j + 1 == n_blocks) mma_commit(smem_u32(&ss.dq_done));
+        if (j + 1 < n_blocks && !issue_dp(j + 1)) { ok = false; break; }
+      }
+    }
+  } else {
+    const int row_in_tile = warp * 32 + lane;
+    const int q_row = m0 + row_in_tile;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const float qk_scale = prm.sm_scale * kLog2e;
+    float lse = 0.f, delta = 0.f;
+    if (q_row < prm.n_ctx) {
+      lse = prm.lse[(int64_t)bh * prm.stride_lse + q_row];
+      delta = prm.delta[(int64_t)bh * prm.stride_lse + q_row];
+    }
+    bool ok = true;
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(smem_u32(&ss.s_full[s]), (j >> 1) & 1, wc, 37)) { ok = false; break; }
+      tc_fence_after();
+      const int n0 = j * BLK;
+      const bool boundary = (n0 + BLK > prm.n_ctx) || (prm.causal && n0 + BLK > m0);
+      float p[BLK];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + lane_addr + (s ? S_COL1 : S_COL0) + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = fast_exp2(fmaf(__uint_as_float(r[i]), qk_scale, -lse));
+          if (boundary) {
+            const int key = n0 + c * 32 + i;
+            if (key >= prm.n_ctx || (prm.causal && key > q_row)) v = 0.f;
+          }
+          p[c * 32 + i] = v;
+        }
+      }
+      if (!mbar_wait(smem_u32(&ss.dp_full), j & 1, wc, 38)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + lane_addr + DP_COL + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float d0 = p[c * 32 + i] * (__uint_as_float(r[i]) - delta);
+          const float d1 = p[c * 32 + i + 1] * (__uint_as_float(r[i + 1]) - delta);
+          packed[i / 2] = pack2<T>(d0, d1);
+        }
+        // dS overwrites columns of dP that have already been read
+        tmem_st_32x16(tmem + lane_addr + DP_COL + c * 16, packed);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ss.ds_full));
+    }
+    if (ok) ok = mbar_wait(smem_u32(&ss.dq_done), 0, wc, 40);
+    tc_fence_after();
+    if (ok) {
+      const bool live = q_row < prm.rows;
+      T* orow = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + lane_addr + DQ_COL + c * 32, r);
+        tmem_ld_wait();
+        if (live) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 out;
+            out.x = pack2<T>(__uint_as_float(r[v * 8 + 0]) * prm.sm_scale, __uint_as_float(r[v * 8 + 1]) * prm.sm_scale);
+            out.y = pack2<T>(__uint_as_float(r[v * 8 + 2]) * prm.sm_scale, __uint_as_float(r[v * 8 + 3]) * prm.sm_scale);
+            out.z = pack2<T>(__uint_as_float(r[v * 8 + 4]) * prm.sm_scale, __uint_as_float(r[v * 8 + 5]) * prm.sm_scale);
+            out.w = pack2<T>(__uint_as_float(r[v * 8 + 6]) * prm.sm_scale, __uint_as_float(r[v * 8 + 7]) * prm.sm_scale);
+            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = out;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ===========================================================================
+// dK, dV
+// ===========================================================================
+struct SharedDkdv {
+  alignas(8) uint64_t kv_full;
+  alignas(8) uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
+  alignas(8) uint64_t st_full, dpt_full, p_full, ds_full, done;
+  float lse[2][BLK];
+  float delta[2][BLK];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename T, int D, uint32_t FMT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                        Params prm, DeviceStatus* status) {
+  constexpr int TILE = BLK * D * 2;
+  constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t k_addr = smem_u32(smem), v_addr = k_addr + TILE, q_addr = v_addr + TILE,
+                 do_addr = q_addr + 2 * TILE;
+  SharedDkdv& ss = *reinterpret_cast<SharedDkdv*>(smem + 6 * TILE);
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  WaitCtx wc{&ss.abort_flag, status};
+  const int bh = blockIdx.y;
+  const int n0 = blockIdx.x * BLK;                       // first key row of this CTA
+  const int total_q_blocks = (prm.n_ctx + BLK - 1) / BLK;
+  const int first = prm.causal ? n0 / BLK : 0;            // earlier queries never see these keys
+  const int n_iter = total_q_blocks - first;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ss.kv_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&ss.q_full[s]), 1);
+      mbar_init(smem_u32(&ss.q_empty[s]), 1);
+      mbar_init(smem_u32(&ss.do_full[s]), 1);
+      mbar_init(smem_u32(&ss.do_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ss.st_full), 1);
+    mbar_init(smem_u32(&ss.dpt_full), 1);
+    mbar_init(smem_u32(&ss.p_full), 128);
+    mbar_init(smem_u32(&ss.ds_full), 128);
+    mbar_init(smem_u32(&ss.done), 1);
+    ss.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&ss.tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ss.tmem_base;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      tma_prefetch_desc(&map_do);
+      mbar_expect_tx(smem_u32(&ss.kv_full), 2 * TILE);
+      load_tile<D>(k_addr, &map_k, smem_u32(&ss.kv_full), n0, bh);
+      load_tile<D>(v_addr, &map_v, smem_u32(&ss.kv_full), n0, bh);
+      int issued = 0;
+      for (int t = 0; t < n_iter; ++t) {
+        const int s = t & 1;
+        const uint32_t ph = (t >> 1) & 1;
+        const int row0 = (first + t) * BLK;
+        if (!mbar_wait(smem_u32(&ss.q_empty[s]), ph ^ 1, wc, 51)) break;
+        mbar_expect_tx(smem_u32(&ss.q_full[s]), TILE);
+        load_tile<D>(q_addr + s * TILE, &map_q, smem_u32(&ss.q_full[s]), row0, bh);
+        if (!mbar_wait(smem_u32(&ss.do_empty[s]), ph ^ 1, wc, 52)) {
+          drain(smem_u32(&ss.q_full[s]), ph, wc, 59);
+          break;
+        }
+        mbar_expect_tx(smem_u32(&ss.do_full[s]), TILE);
+        load_tile<D>(do_addr + s * TILE, &map_do, smem_u32(&ss.do_full[s]), row0, bh);
+        ++issued;
+      }
+      drain(smem_u32(&ss.kv_full), 0, wc, 59);
+      for (int t = max(0, issued - 2); t < issued; ++t) {
+        drain(smem_u32(&ss.q_full[t & 1]), (t >> 1) & 1, wc, 59);
+        drain(smem_u32(&ss.do_full[t & 1]), (t >> 1) & 1, wc, 59);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_nt = make_idesc(FMT, BLK, BLK, 0, 0);
+      constexpr uint32_t idesc_tn = make_idesc(FMT, BLK, D, 0, 1);
+      bool ok = mbar_wait(smem_u32(&ss.kv_full), 0, wc, 53);
+      auto issue_st = [&](int t) -> bool {
+        const int s = t & 1;
+        if (!mbar_wait(smem_u32(&ss.q_full[s]), (t >> 1) & 1, wc, 54)) return false;
+        tc_fence_after();
+        mma_nt<D>(tmem + ST_COL, k_addr, q_addr + s * TILE, idesc_nt);
+        mma_commit(smem_u32(&ss.st_full));
+        return true;
+      };
+      auto issue_dpt = [&](int t) -> bool {
+        const int s = t & 1;
+        if (!mbar_wait(smem_u32(&ss.do_full[s]), (t >> 1) & 1, wc, 55)) return false;
+        tc_fence_after();
+        mma_nt<D>(tmem + DPT_COL, v_addr, do_addr + s * TILE, idesc_nt);
+        mma_commit(smem_u32(&ss.dpt_full));
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_st(0) && issue_dpt(0);
+      for (int t = 0; t < n_iter && ok; ++t) {
+        const int s = t & 1;
+        if (!mbar_wait(smem_u32(&ss.p_full), t & 1, wc, 56)) { ok = false; break; }
+        tc_fence_after();
+        mma_tn<D>(tmem + DV_COL, tmem + ST_COL, do_addr + s * TILE, idesc_tn, t != 0);
+        mma_commit(smem_u32(&ss.do_empty[s]));
+        if (t + 1 < n_iter && !issue_st(t + 1)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&ss.ds_full), t & 1, wc, 57)) { ok = false; break; }
+        tc_fence_after();
+        mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_addr + s * TILE, idesc_tn, t != 0);
+        mma_commit(smem_u32(&ss.q_empty[s]));
+        if (t + 1 == n_iter) mma_commit(smem_u32(&ss.done));
+        if (t + 1 < n_iter && !issue_dpt(t + 1)) { ok = false; break; }
+      }
+    }
+  } else {
+    const int row_in_tile = warp * 32 + lane;
+    const int k_row = n0 + row_in_tile;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const float qk_scale = prm.sm_scale * kLog2e;
+    const float* lse_base = prm.lse + (int64_t)bh * prm.stride_lse;
+    const float* delta_base = prm.delta + (int64_t)bh * prm.stride_lse;
+    auto stage_stats = [&](int t) {
+      // this thread fetches the statistics of query (first+t)*128 + row_in_tile;
+      // +inf as L makes exp2(x - L) vanish for queries past the end
+      const int q = (first + t) * BLK + row_in_tile;
+      const bool live = q < prm.n_ctx;
+      ss.lse[t & 1][row_in_tile] = live ? lse_base[q] : INFINITY;
+      ss.delta[t & 1][row_in_tile] = live ? delta_base[q] : 0.f;
+    };
+    if (n_iter > 0) stage_stats(0);
+    bool ok = true;
+    for (int t = 0; t < n_iter && ok; ++t) {
+      // all 128 threads: statistics of block t are visible, block t-1 is no longer read
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (t + 1 < n_iter) stage_stats(t + 1);
+      const float* lse_s = ss.lse[t & 1];
+      const float* delta_s = ss.delta[t & 1];
+      const int q0 = (first + t) * BLK;
+      const bool diagonal = prm.causal && q0 < n0 + BLK;
+      if (!mbar_wait(smem_u32(&ss.st_full), t & 1, wc, 58)) { ok = false; break; }
+      tc_fence_after();
+      float p[BLK];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + lane_addr + ST_COL + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = fast_exp2(fmaf(__uint_as_float(r[i]), qk_scale, -lse_s[c * 32 + i]));
+          if (diagonal && k_row > q0 + c * 32 + i) v = 0.f;
+          p[c * 32 + i] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) packed[i / 2] = pack2<T>(p[c * 32 + i], p[c * 32 + i + 1]);
+        tmem_st_32x16(tmem + lane_addr + ST_COL + c * 16, packed);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ss.p_full));
+      if (!mbar_wait(smem_u32(&ss.dpt_full), t & 1, wc, 60)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + lane_addr + DPT_COL + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float d0 = p[c * 32 + i] * (__uint_as_float(r[i]) - delta_s[c * 32 + i]);
+          const float d1 = p[c * 32 + i + 1] * (__uint_as_float(r[i + 1]) - delta_s[c * 32 + i + 1]);
+          packed[i / 2] = pack2<T>(d0, d1);
+        }
+        tmem_st_32x16(tmem + lane_addr + DPT_COL + c * 16, packed);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ss.ds_full));
+    }
+    if (ok && n_iter > 0) ok = mbar_wait(smem_u32(&ss.done), 0, wc, 61);
+    tc_fence_after();
+    const bool live = k_row < prm.rows;
+    T* dk_row = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq;
+    T* dv_row = (T*)prm.out1 + (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq;
+    if (ok && n_iter > 0) {
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const float scale = which ? prm.sm_scale : 1.f;
+        T* orow = which ? dk_row : dv_row;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem + lane_addr + (which ? DK_COL : DV_COL) + c * 32, r);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 out;
+              out.x = pack2<T>(__uint_as_float(r[v * 8 + 0]) * scale, __uint_as_float(r[v * 8 + 1]) * scale);
+              out.y = pack2<T>(__uint_as_float(r[v * 8 + 2]) * scale, __uint_as_float(r[v * 8 + 3]) * scale);
+              out.z = pack2<T>(__uint_as_float(r[v * 8 + 4]) * scale, __uint_as_float(r[v * 8 + 5]) * scale);
+              out.w = pack2<T>(__uint_as_float(r[v * 8 + 6]) * scale, __uint_as_float(r[v * 8 + 7]) * scale);
+              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = out;
+            }
+          }
+        }
+      }
+    } else if (ok && live) {
+      // no query attends to these keys (cannot happen with n_iter > 0 for live rows)
+      for (int d = 0; d < D; ++d) { dk_row[d] = T(0.f); dv_row[d] = T(0.f); }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+template <typename T, int D>
+std::string make_maps(const AttnProblem& p, CUtensorMapDataType type, CUtensorMap* maps) {
+  const void* bases[4] = {p.q, p.k, p.v, p.d_o};
+  for (int i = 0; i < 4; ++i) {
+    uint64_t dims[3] = {(uint64_t)D, (uint64_t)p.n_ctx, (uint64_t)p.bh};
+    uint64_t strides[2] = {(uint64_t)p.stride_seq * 2, (uint64_t)p.stride_head * 2};
+    uint32_t box[3] = {64u, (uint32_t)BLK, 1u};
+    std::string e = make_tensor_map(&maps[i], type, 3, bases[i], dims, strides, box);
+    if (!e.empty()) return e;
+  }
+  return std::string();
+}
+
+Params make_params(const AttnProblem& p) {
+  Params prm{};
+  prm.out0 = p.out0;
+  prm.out1 = p.out1;
+  prm.lse = p.lse;
+  prm.delta = p.delta;
+  prm.sm_scale = p.sm_scale;
+  prm.stride_head = p.stride_head;
+  prm.stride_seq = p.stride_seq;
+  prm.stride_lse = p.stride_lse;
+  prm.n_ctx = (int)p.n_ctx;
+  prm.rows = (int)p.rows;
+  prm.causal = p.causal;
+  return prm;
+}
+
+template <typename T, int D, uint32_t FMT>
+std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type, bool dkdv) {
+  CUtensorMap maps[4];
+  std::string err = make_maps<T, D>(p, type, maps);
+  if (!err.empty()) return err;
+  Params prm = make_params(p);
+  const char* what = dkdv ? "attn_bwd_dkdv" : "attn_bwd_dq";
+  // 6 tiles; never less than 120 KiB so two CTAs (each wanting all of TMEM) do not share an SM
+  size_t smem = 6 * (BLK * D * 2) + (dkdv ? sizeof(SharedDkdv) : sizeof(SharedDq)) + 1024;
+  if (smem < 120 * 1024) smem = 120 * 1024;
+  dim3 grid((unsigned)((p.rows + BLK - 1) / BLK), (unsigned)p.bh, 1);
+  cudaError_t e;
+  if (dkdv) {
+    auto kernel = attn_bwd_dkdv_tc_kernel<T, D, FMT>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return std::string(what) + ": " + cudaGetErrorString(e);
+    kernel<<<grid, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, ctx.status);
+  } else {
+    auto kernel = attn_bwd_dq_tc_kernel<T, D, FMT>;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return std::string(what) + ": " + cudaGetErrorString(e);
+    kernel<<<grid, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, ctx.status);
+  }
+  ++*ctx.launches;
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return std::string(what) + " launch failed: " + cudaGetErrorString(e);
+  return std::string();
+}
+
+std::string dispatch(const AttnProblem& p, const LaunchCtx& ctx, bool dkdv) {
+  if (p.elt == Elt::BF16) {
+    return p.head_dim == 64
+               ? launch_typed<__nv_bfloat16, 64, 1>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dkdv)
+               : launch_typed<__nv_bfloat16, 128, 1>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, dkdv);
+  }
+  return p.head_dim == 64 ? launch_typed<__half, 64, 0>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, dkdv)
+                          : launch_typed<__half, 128, 0>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, dkdv);
+}
+
+}  // namespace
+
+bool attn_bwd_tc_eligible(const AttnProblem& p, std::string* why) {
+  auto no = [&](const char* m) {
+    if (why) *why = m;
+    return false;
+  };
+  if (p.elt == Elt::F32) return no("fp32 attention takes the generic kernel");
+  if (p.head_dim != 64 && p.head_dim != 128) return no("head dimension is not 64 or 128");
+  if (p.stride_seq != p.head_dim) return no("rows are not contiguous (stride_seq != head_dim)");
+  if (p.stride_head % 8) return no("stride_head is not a multiple of 16 bytes");
+  if (p.stride_head < p.n_ctx * p.stride_seq) return no("heads overlap");
+  if (((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.d_o | (uintptr_t)p.out0 |
+       (uintptr_t)p.out1) % 16)
+    return no("base pointers are not 16-byte aligned");
+  if (p.n_ctx < 128) return no("sequence shorter than one 128-row tile");
+  if (p.n_ctx > 0x7fffffff / 256 || p.bh > 65535) return no("extent out of range");
+  return true;
+}
+
+std::string launch_attn_bwd_dq_tc(const AttnProblem& p, const LaunchCtx& ctx) { return dispatch(p, ctx, false); }
+std::string launch_attn_bwd_dkdv_tc(const AttnProblem& p, const LaunchCtx& ctx) { return dispatch(p, ctx, true); }
+
+}  // namespace tmc

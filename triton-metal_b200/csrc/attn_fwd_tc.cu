@@ -27,6 +27,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 namespace tmc {
 namespace {
 
@@ -62,12 +64,6 @@ struct Params {
   int n_ctx, rows, causal;
 };
 
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -78,7 +74,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <typename T, int D, uint32_t FMT>
+template <typename T, int D, uint32_t FMT, bool P_TMEM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, Params prm, DeviceStatus* status) {
@@ -208,9 +204,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
           // P: K-major, 64-key halves 16 KiB apart.  V: MN-major, 16 keys = 2048 bytes
           // further, 64-column halves HALF_BYTES apart.
-          const uint32_t p_off = (kk / 4) * (BLOCK_M * 128) + (kk % 4) * 32;
-          mma_f16_ss(tmem + O_COL, smem_desc_sw128(p_addr + p_off, 0, 1024),
-                     smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
+          if constexpr (P_TMEM) {
+            // P as a TMEM operand: 16 keys = 8 packed 32-bit columns of the score buffer
+            mma_f16_ts(tmem + O_COL, tmem + (s ? S_COL1 : S_COL0) + kk * 8,
+                       smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
+          } else {
+            const uint32_t p_off = (kk / 4) * (BLOCK_M * 128) + (kk % 4) * 32;
+            mma_f16_ss(tmem + O_COL, smem_desc_sw128(p_addr + p_off, 0, 1024),
+                       smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
+          }
         }
         mma_commit(smem_u32(&ss.v_empty[s]));
         mma_commit(smem_u32(&ss.pv_done));
@@ -272,9 +274,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       l = l * alpha + sum;
       // P(j) may only replace P(j-1) once the P.V MMA of block j-1 has finished; the
       // same event makes O safe to rescale.
-      if (j > 0 && !mbar_wait(smem_u32(&ss.pv_done), (j - 1) & 1, wc, kSoftPv)) { ok = false; break; }
+      const bool any_rescale = __any_sync(0xffffffffu, rescale);
+      if (j > 0 && (!P_TMEM || any_rescale) &&
+          !mbar_wait(smem_u32(&ss.pv_done), (j - 1) & 1, wc, kSoftPv)) { ok = false; break; }
       tc_fence_after();
-      if (__any_sync(0xffffffffu, rescale)) {
+      if (any_rescale) {
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
@@ -286,8 +290,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         tmem_st_wait();
       }
+      if constexpr (P_TMEM) {
+        // P replaces the first 64 columns of the score buffer it was computed from
+        // (two 16-bit values per 32-bit column, even key in the low half).
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = packed[c * 32 + i];
+          tmem_st_32x32(tmem + lane_addr + (s ? S_COL1 : S_COL0) + c * 32, r);
+        }
+        tmem_st_wait();
+      } else {
       // P tile: K-major, 128-byte swizzle; row r, 16-byte chunk c at (c ^ (r & 7)).
-      {
         uint8_t* prow = p_ptr + row_in_tile * 128;
         const int sw = row_in_tile & 7;
 #pragma unroll
@@ -295,8 +310,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           uint4 v = make_uint4(packed[c * 4 + 0], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
           *reinterpret_cast<uint4*>(prow + (c / 8) * (BLOCK_M * 128) + (((c % 8) ^ sw) * 16)) = v;
         }
-      }
       fence_proxy_async();
+      }
       tc_fence_before();
       mbar_arrive(smem_u32(&ss.p_full));
     }
@@ -336,8 +351,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
 }
 
-template <typename T, int D, uint32_t FMT>
-std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type) {
+template <typename T, int D, uint32_t FMT, bool P_TMEM>
+std::string launch_typed_p(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type) {
   CUtensorMap maps[3];
   const void* bases[3] = {p.q, p.k, p.v};
   for (int i = 0; i < 3; ++i) {
@@ -360,7 +375,7 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   // at least 120 KiB so that two CTAs (each wanting all 512 TMEM columns) never share an SM
   size_t smem = 5 * (BLOCK_M * D * 2) + BLOCK_M * BLOCK_N * 2 + sizeof(Shared) + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
-  auto kernel = attn_fwd_tc_kernel<T, D, FMT>;
+  auto kernel = attn_fwd_tc_kernel<T, D, FMT, P_TMEM>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return std::string("attn_fwd: ") + cudaGetErrorString(e);
   dim3 grid((unsigned)((p.rows + BLOCK_M - 1) / BLOCK_M), (unsigned)p.bh, 1);
@@ -369,6 +384,17 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   e = cudaGetLastError();
   if (e != cudaSuccess) return std::string("attn_fwd launch failed: ") + cudaGetErrorString(e);
   return std::string();
+}
+
+template <typename T, int D, uint32_t FMT>
+std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type) {
+  // $TMCUDA_ATTN_P=smem keeps P in shared memory (the first, conservative form).
+  static const bool p_smem = [] {
+    const char* e = std::getenv("TMCUDA_ATTN_P");
+    return e && std::string(e) == "smem";
+  }();
+  return p_smem ? launch_typed_p<T, D, FMT, false>(p, ctx, type)
+                : launch_typed_p<T, D, FMT, true>(p, ctx, type);
 }
 
 }  // namespace

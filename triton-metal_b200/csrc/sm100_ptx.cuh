@@ -255,6 +255,13 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- small numeric helpers shared by the attention kernels -------------------------
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 }  // namespace ptx
 
 // ---- host: tensor maps ------------------------------------------------------------
