@@ -6,19 +6,23 @@
 // (qk_scale = sm_scale*log2 e), P rounded to the element type before P.V,
 // O = acc / l, and the row statistic L = m + log2(l) in log2 units.
 //
-// One CTA owns 128 query rows of one (batch, head):
-//   warp 4    TMA: Q once, then K and V blocks of 128 keys into 2-stage rings
-//   warp 5    MMA issuer: S = Q K^T (128x128xD) into one of two TMEM score
-//             buffers, O += P V (128xDx128) into the TMEM output accumulator
-//   warps 0-3 softmax, one thread per query row (the row lives in that thread's
-//             TMEM lane, so row max / row sum need no cross-thread traffic):
-//             tcgen05.ld S, mask, running max, exp2, round P into a swizzled
-//             shared-memory tile that the P.V MMA reads, rescale O in TMEM when
-//             the running max moved by more than 2^8, final O/l and L store.
-// The running max used for the exponentials is only advanced when it grew by
-// more than 8 (in log2 units), which keeps P <= 256 and makes most iterations
-// skip the O rescale; O/l at the end is exact either way.
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that take
+// turns on the tensor core, so the exponentials of one tile overlap the MMAs of
+// the other:
+//   warps 0-3 / 4-7  softmax of tile 0 / tile 1, one thread per query row (the row
+//                    is that thread's TMEM lane: row max and row sum need no
+//                    cross-thread traffic).  Two passes over the score tile in
+//                    TMEM: max, then exp2 / sum / round, writing the 16-bit P
+//                    back over the scores it came from.
+//   warp 8           TMA: Q (both tiles) once, then K and V blocks of 128 keys
+//                    into 2-stage rings
+//   warp 9           MMA issuer: S_t = Q_t K^T (128x128xD, operands in shared
+//                    memory), O_t += P_t V (128xDx128, P read from TMEM)
+// The running max used for the exponentials only advances when it grew by more
+// than 8 (log2 units): P stays <= 256 and most iterations skip the O rescale in
+// TMEM; O/l at the end is exact either way.
 //
+// TMEM columns: S_0 | S_1 | O_0 | O_1.
 // HBM layout: Q, K, V, O [BH, S, D] with D contiguous (stride_seq == D),
 // L [BH, S] fp32.
 
@@ -35,9 +39,9 @@ namespace {
 using namespace ptx;
 
 constexpr int BLOCK_M = 128, BLOCK_N = 128;
-constexpr int NUM_THREADS = 192;
+constexpr int TILES = 2;                       // query tiles per CTA
+constexpr int NUM_THREADS = 320;
 constexpr int TMEM_COLS = 512;
-constexpr int S_COL0 = 0, S_COL1 = 128, O_COL = 256;
 constexpr float kLog2e = 1.44269504088896340736f;
 constexpr float kRescaleThreshold = 8.0f;
 
@@ -49,9 +53,7 @@ enum Site : uint32_t {
 struct Shared {
   alignas(8) uint64_t q_full;
   alignas(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-  alignas(8) uint64_t s_full[2];
-  alignas(8) uint64_t p_full;
-  alignas(8) uint64_t pv_done;
+  alignas(8) uint64_t s_full[TILES], p_full[TILES], pv_done[TILES];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -74,33 +76,128 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <typename T, int D, uint32_t FMT, bool P_TMEM>
+// ---- softmax passes over one 128-column score tile in TMEM ------------------------
+// Both passes are written as short loops (two 32-column chunks per trip, the next chunk's
+// tcgen05.ld in flight while the current one is processed) rather than fully unrolled:
+// the softmax warps execute this code once per key block, and straight-line code for 128
+// columns does not stay resident in the instruction cache.
+struct MaskInfo {
+  int n0, q_row, n_ctx, causal;
+  __device__ __forceinline__ bool masked(int col) const {
+    const int key = n0 + col;
+    return key >= n_ctx || (causal && key > q_row);
+  }
+};
+
+template <bool MASKED>
+__device__ __forceinline__ float max_pass(uint32_t s_tmem, const MaskInfo& mi) {
+  uint32_t ra[32], rb[32];
+  float m0 = -INFINITY, m1 = -INFINITY;
+  tmem_ld_32x32(s_tmem, ra);
+#pragma unroll 1
+  for (int c = 0; c < 4; c += 2) {
+    tmem_ld_wait();
+    tmem_ld_32x32(s_tmem + (c + 1) * 32, rb);
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const float a = __uint_as_float(ra[i]), b = __uint_as_float(ra[i + 1]);
+      if (MASKED) {
+        if (!mi.masked(c * 32 + i)) m0 = fmaxf(m0, a);
+        if (!mi.masked(c * 32 + i + 1)) m1 = fmaxf(m1, b);
+      } else {
+        m0 = fmaxf(m0, a);
+        m1 = fmaxf(m1, b);
+      }
+    }
+    tmem_ld_wait();
+    if (c + 2 < 4) tmem_ld_32x32(s_tmem + (c + 2) * 32, ra);
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const float a = __uint_as_float(rb[i]), b = __uint_as_float(rb[i + 1]);
+      if (MASKED) {
+        if (!mi.masked((c + 1) * 32 + i)) m0 = fmaxf(m0, a);
+        if (!mi.masked((c + 1) * 32 + i + 1)) m1 = fmaxf(m1, b);
+      } else {
+        m0 = fmaxf(m0, a);
+        m1 = fmaxf(m1, b);
+      }
+    }
+  }
+  return fmaxf(m0, m1);
+}
+
+// P = exp2(s*qk_scale + neg_m), rounded to T and written back over the scores already
+// read (16 packed columns per 32 score columns); returns the fp32 row sum.
+template <typename T, bool MASKED>
+__device__ __forceinline__ float exp_chunk(const uint32_t (&r)[32], uint32_t dst, float qk_scale,
+                                           float neg_m, int col0, const MaskInfo& mi) {
+  uint32_t packed[16];
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), qk_scale, neg_m));
+    float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), qk_scale, neg_m));
+    if (MASKED) {
+      if (mi.masked(col0 + i)) p0 = 0.f;
+      if (mi.masked(col0 + i + 1)) p1 = 0.f;
+    }
+    s0 += p0;
+    s1 += p1;
+    packed[i / 2] = pack2<T>(p0, p1);
+  }
+  tmem_st_32x16(dst, packed);
+  return s0 + s1;
+}
+
+template <typename T, bool MASKED>
+__device__ __forceinline__ float exp_pass(uint32_t s_tmem, float qk_scale, float neg_m,
+                                          const MaskInfo& mi) {
+  uint32_t ra[32], rb[32];
+  float sum = 0.f;
+  tmem_ld_32x32(s_tmem, ra);
+#pragma unroll 1
+  for (int c = 0; c < 4; c += 2) {
+    tmem_ld_wait();
+    tmem_ld_32x32(s_tmem + (c + 1) * 32, rb);
+    sum += exp_chunk<T, MASKED>(ra, s_tmem + c * 16, qk_scale, neg_m, c * 32, mi);
+    tmem_ld_wait();
+    if (c + 2 < 4) tmem_ld_32x32(s_tmem + (c + 2) * 32, ra);
+    sum += exp_chunk<T, MASKED>(rb, s_tmem + (c + 1) * 16, qk_scale, neg_m, (c + 1) * 32, mi);
+  }
+  return sum;
+}
+
+template <typename T, int D, uint32_t FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, Params prm, DeviceStatus* status) {
   constexpr int HALVES = D / 64;                        // 64-column swizzle atoms per row
-  constexpr int TILE_BYTES = BLOCK_M * D * 2;           // Q, K, V tiles: 128 rows x D
+  constexpr int TILE_BYTES = BLOCK_M * D * 2;           // one 128-row tile of Q, K or V
   constexpr int HALF_BYTES = BLOCK_M * 128;             // one [128 x 64] swizzled box
-  constexpr int P_BYTES = BLOCK_M * BLOCK_N * 2;
+  constexpr int S_COL = 0, O_COL = 256;                 // S_t at t*128, O_t at 256 + t*D
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  // layout: Q | K0 K1 | V0 V1 | P | barriers
+  // layout: Q0 Q1 | K0 K1 | V0 V1 | barriers
   const uint32_t q_addr = smem_u32(smem);
-  const uint32_t k_addr = q_addr + TILE_BYTES;
+  const uint32_t k_addr = q_addr + TILES * TILE_BYTES;
   const uint32_t v_addr = k_addr + 2 * TILE_BYTES;
-  const uint32_t p_addr = v_addr + 2 * TILE_BYTES;
-  uint8_t* p_ptr = smem + 5 * TILE_BYTES;
-  Shared& ss = *reinterpret_cast<Shared*>(smem + 5 * TILE_BYTES + P_BYTES);
+  Shared& ss = *reinterpret_cast<Shared*>(smem + (TILES + 4) * TILE_BYTES);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   WaitCtx wc{&ss.abort_flag, status};
 
   // heavy (late) query tiles first under a causal mask
-  const int m_tile = prm.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int m_pair = prm.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
   const int bh = blockIdx.y;
-  const int m0 = m_tile * BLOCK_M;
-  int key_end = prm.n_ctx;
-  if (prm.causal) key_end = min(prm.n_ctx, m0 + BLOCK_M);
-  const int n_blocks = (key_end + BLOCK_N - 1) / BLOCK_N;
+  const int m0 = m_pair * (TILES * BLOCK_M);
+  // key blocks each tile walks: everything, or up to its own diagonal
+  int nb[TILES];
+#pragma unroll
+  for (int t = 0; t < TILES; ++t) {
+    int key_end = prm.n_ctx;
+    if (prm.causal) key_end = min(prm.n_ctx, m0 + (t + 1) * BLOCK_M);
+    nb[t] = (key_end + BLOCK_N - 1) / BLOCK_N;
+  }
+  const int nb_max = nb[TILES - 1];                     // later rows see at least as many keys
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ss.q_full), 1);
@@ -109,14 +206,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       mbar_init(smem_u32(&ss.k_empty[s]), 1);
       mbar_init(smem_u32(&ss.v_full[s]), 1);
       mbar_init(smem_u32(&ss.v_empty[s]), 1);
-      mbar_init(smem_u32(&ss.s_full[s]), 1);
     }
-    mbar_init(smem_u32(&ss.p_full), 128);
-    mbar_init(smem_u32(&ss.pv_done), 1);
+    for (int t = 0; t < TILES; ++t) {
+      mbar_init(smem_u32(&ss.s_full[t]), 1);
+      mbar_init(smem_u32(&ss.p_full[t]), 128);
+      mbar_init(smem_u32(&ss.pv_done[t]), 1);
+    }
     ss.abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(smem_u32(&ss.tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
@@ -125,28 +224,36 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem = ss.tmem_base;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------------------------------------------------------- loads
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
-      mbar_expect_tx(smem_u32(&ss.q_full), TILE_BYTES);
+      mbar_expect_tx(smem_u32(&ss.q_full), TILES * TILE_BYTES);
 #pragma unroll
-      for (int h = 0; h < HALVES; ++h)
-        tma_load_3d(q_addr + h * HALF_BYTES, &map_q, smem_u32(&ss.q_full), h * 64, m0, bh);
-      bool ok = true;
+      for (int t = 0; t < TILES; ++t)
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_3d(q_addr + t * TILE_BYTES + h * HALF_BYTES, &map_q, smem_u32(&ss.q_full), h * 64,
+                      m0 + t * BLOCK_M, bh);
       int issued = 0;
-      for (int j = 0; j < n_blocks && ok; ++j) {
+      for (int j = 0; j < nb_max; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&ss.k_empty[s]), ph ^ 1, wc, kLoadKEmpty)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&ss.k_empty[s]), ph ^ 1, wc, kLoadKEmpty)) break;
         mbar_expect_tx(smem_u32(&ss.k_full[s]), TILE_BYTES);
 #pragma unroll
         for (int h = 0; h < HALVES; ++h)
           tma_load_3d(k_addr + s * TILE_BYTES + h * HALF_BYTES, &map_k, smem_u32(&ss.k_full[s]), h * 64,
                       j * BLOCK_N, bh);
-        if (!mbar_wait(smem_u32(&ss.v_empty[s]), ph ^ 1, wc, kLoadVEmpty)) { ok = false; ++issued; break; }
+        if (!mbar_wait(smem_u32(&ss.v_empty[s]), ph ^ 1, wc, kLoadVEmpty)) {
+          const long long t1 = clock64();
+          while (!mbar_try_wait(smem_u32(&ss.k_full[s]), ph)) {
+            if (clock64() - t1 > kWaitCycles) { report_timeout(wc, kDrainLoad, j + 1); break; }
+          }
+          break;
+        }
         mbar_expect_tx(smem_u32(&ss.v_full[s]), TILE_BYTES);
 #pragma unroll
         for (int h = 0; h < HALVES; ++h)
@@ -170,89 +277,83 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(FMT, BLOCK_M, BLOCK_N, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc(FMT, BLOCK_M, D, 0, 1);
       bool ok = mbar_wait(smem_u32(&ss.q_full), 0, wc, kMmaQ);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(smem_u32(&ss.k_full[s]), (j >> 1) & 1, wc, kMmaK)) return false;
-        tc_fence_after();
-        const uint32_t kb = k_addr + s * TILE_BYTES;
-        const uint32_t d_tmem = tmem + (s ? S_COL1 : S_COL0);
+      // S_t(j) = Q_t K(j)^T.  The caller has made sure K(j) has landed.
+      auto issue_qk = [&](int t, int j) {
+        const uint32_t kb = k_addr + (j & 1) * TILE_BYTES;
+        const uint32_t qb = q_addr + t * TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
-          mma_f16_ss(d_tmem, smem_desc_sw128(q_addr + off, 0, 1024), smem_desc_sw128(kb + off, 0, 1024),
-                     idesc_qk, kk != 0);
+          mma_f16_ss(tmem + S_COL + t * BLOCK_N, smem_desc_sw128(qb + off, 0, 1024),
+                     smem_desc_sw128(kb + off, 0, 1024), idesc_qk, kk != 0);
         }
-        mma_commit(smem_u32(&ss.k_empty[s]));
-        mma_commit(smem_u32(&ss.s_full[s]));
-        return true;
+        mma_commit(smem_u32(&ss.s_full[t]));
       };
-      if (ok && n_blocks > 0) ok = issue_qk(0);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        if (j + 1 < n_blocks && !issue_qk(j + 1)) { ok = false; break; }
+      if (ok) ok = mbar_wait(smem_u32(&ss.k_full[0]), 0, wc, kMmaK);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) issue_qk(t, 0);
+        mma_commit(smem_u32(&ss.k_empty[0]));      // K(0) is free once both S(0) retire
+      }
+      for (int j = 0; j < nb_max && ok; ++j) {
         const int s = j & 1;
         if (!mbar_wait(smem_u32(&ss.v_full[s]), (j >> 1) & 1, wc, kMmaV)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(&ss.p_full), j & 1, wc, kMmaP)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t vb = v_addr + s * TILE_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-          // P: K-major, 64-key halves 16 KiB apart.  V: MN-major, 16 keys = 2048 bytes
-          // further, 64-column halves HALF_BYTES apart.
-          if constexpr (P_TMEM) {
-            // P as a TMEM operand: 16 keys = 8 packed 32-bit columns of the score buffer
-            mma_f16_ts(tmem + O_COL, tmem + (s ? S_COL1 : S_COL0) + kk * 8,
-                       smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
-          } else {
-            const uint32_t p_off = (kk / 4) * (BLOCK_M * 128) + (kk % 4) * 32;
-            mma_f16_ss(tmem + O_COL, smem_desc_sw128(p_addr + p_off, 0, 1024),
-                       smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
-          }
+        if (j + 1 < nb_max && !mbar_wait(smem_u32(&ss.k_full[s ^ 1]), ((j + 1) >> 1) & 1, wc, kMmaK)) {
+          ok = false;
+          break;
         }
-        mma_commit(smem_u32(&ss.v_empty[s]));
-        mma_commit(smem_u32(&ss.pv_done));
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) {
+          if (j < nb[t]) {
+            if (!mbar_wait(smem_u32(&ss.p_full[t]), j & 1, wc, kMmaP)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t vb = v_addr + s * TILE_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+              // P: TMEM operand, 16 keys = 8 packed 32-bit columns of the score buffer.
+              // V: MN-major, 16 keys = 2048 bytes further, 64-column halves HALF_BYTES apart.
+              mma_f16_ts(tmem + O_COL + t * D, tmem + S_COL + t * BLOCK_N + kk * 8,
+                         smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
+            }
+            mma_commit(smem_u32(&ss.pv_done[t]));
+          }
+          // V(j) has been read by both tiles: release it as early as possible
+          if (t == TILES - 1) mma_commit(smem_u32(&ss.v_empty[s]));
+          // the next scores of this tile overwrite its P: MMAs run in issue order
+          if (j + 1 < nb[t]) issue_qk(t, j + 1);
+          // the last tile always walks every block: K(j+1) is free once its S retires
+          if (t == TILES - 1 && j + 1 < nb_max) mma_commit(smem_u32(&ss.k_empty[s ^ 1]));
+        }
+        if (!ok) break;
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax
-    const int row_in_tile = warp * 32 + lane;
-    const int q_row = m0 + row_in_tile;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    // ---------------------------------------------------------------- softmax, tile t
+    const int t = warp / 4;
+    const int row_in_tile = (warp % 4) * 32 + lane;
+    const int q_row = m0 + t * BLOCK_M + row_in_tile;
+    const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
+    const uint32_t s_tmem = tmem + lane_addr + S_COL + t * BLOCK_N;
+    const uint32_t o_tmem = tmem + lane_addr + O_COL + t * D;
     const float qk_scale = prm.sm_scale * kLog2e;
+    const int my_blocks = nb[t];
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      const int s = j & 1;
-      if (!mbar_wait(smem_u32(&ss.s_full[s]), (j >> 1) & 1, wc, kSoftS)) { ok = false; break; }
+    for (int j = 0; j < my_blocks && ok; ++j) {
+      if (!mbar_wait(smem_u32(&ss.s_full[t]), j & 1, wc, kSoftS)) { ok = false; break; }
       tc_fence_after();
-      float x[BLOCK_N];
-      {
-        uint32_t r[32];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          tmem_ld_32x32(tmem + lane_addr + (s ? S_COL1 : S_COL0) + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) x[c * 32 + i] = __uint_as_float(r[i]) * qk_scale;
-        }
-      }
       const int n0 = j * BLOCK_N;
-      const bool boundary = (n0 + BLOCK_N > prm.n_ctx) || (prm.causal && n0 + BLOCK_N > m0);
-      if (boundary) {
-#pragma unroll
-        for (int i = 0; i < BLOCK_N; ++i) {
-          const int key = n0 + i;
-          if (key >= prm.n_ctx || (prm.causal && key > q_row)) x[i] = -INFINITY;
-        }
-      }
-      float mx = x[0];
-#pragma unroll
-      for (int i = 1; i < BLOCK_N; ++i) mx = fmaxf(mx, x[i]);
+      const bool boundary = (n0 + BLOCK_N > prm.n_ctx) || (prm.causal && n0 + BLOCK_N > m0 + t * BLOCK_M);
+      const MaskInfo mi{n0, q_row, prm.n_ctx, prm.causal};
+      // pass 1: row max of the raw scores (qk_scale > 0, so the scaled max is max * qk_scale)
+      const float mx = (boundary ? max_pass<true>(s_tmem, mi) : max_pass<false>(s_tmem, mi)) * qk_scale;
       // advance the working max only when it moved far (or on the first block)
       float alpha = 1.f;
       bool rescale = false;
@@ -261,71 +362,40 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         m_used = mx;
         rescale = j > 0;
       }
-      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-      float sum = 0.f;
-      uint32_t packed[BLOCK_N / 2];
-#pragma unroll
-      for (int i = 0; i < BLOCK_N; i += 2) {
-        const float p0 = fast_exp2(x[i] + neg_m);
-        const float p1 = fast_exp2(x[i + 1] + neg_m);
-        sum += p0 + p1;
-        packed[i / 2] = pack2<T>(p0, p1);
-      }
-      l = l * alpha + sum;
-      // P(j) may only replace P(j-1) once the P.V MMA of block j-1 has finished; the
-      // same event makes O safe to rescale.
-      const bool any_rescale = __any_sync(0xffffffffu, rescale);
-      if (j > 0 && (!P_TMEM || any_rescale) &&
-          !mbar_wait(smem_u32(&ss.pv_done), (j - 1) & 1, wc, kSoftPv)) { ok = false; break; }
-      tc_fence_after();
-      if (any_rescale) {
-#pragma unroll
+      if (__any_sync(0xffffffffu, rescale)) {
+        // O_t may only be touched once the P.V MMA of block j-1 has finished
+        if (!mbar_wait(smem_u32(&ss.pv_done[t]), (j - 1) & 1, wc, kSoftPv)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
-          tmem_ld_32x32(tmem + lane_addr + O_COL + c * 32, r);
+          tmem_ld_32x32(o_tmem + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x32(tmem + lane_addr + O_COL + c * 32, r);
+          tmem_st_32x32(o_tmem + c * 32, r);
         }
         tmem_st_wait();
       }
-      if constexpr (P_TMEM) {
-        // P replaces the first 64 columns of the score buffer it was computed from
-        // (two 16-bit values per 32-bit column, even key in the low half).
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = packed[c * 32 + i];
-          tmem_st_32x32(tmem + lane_addr + (s ? S_COL1 : S_COL0) + c * 32, r);
-        }
-        tmem_st_wait();
-      } else {
-      // P tile: K-major, 128-byte swizzle; row r, 16-byte chunk c at (c ^ (r & 7)).
-        uint8_t* prow = p_ptr + row_in_tile * 128;
-        const int sw = row_in_tile & 7;
-#pragma unroll
-        for (int c = 0; c < BLOCK_N / 8; ++c) {
-          uint4 v = make_uint4(packed[c * 4 + 0], packed[c * 4 + 1], packed[c * 4 + 2], packed[c * 4 + 3]);
-          *reinterpret_cast<uint4*>(prow + (c / 8) * (BLOCK_M * 128) + (((c % 8) ^ sw) * 16)) = v;
-        }
-      fence_proxy_async();
-      }
+      // pass 2: exponentials, row sum, 16-bit P over the scores
+      const float sum = boundary ? exp_pass<T, true>(s_tmem, qk_scale, -m_used, mi)
+                                 : exp_pass<T, false>(s_tmem, qk_scale, -m_used, mi);
+      l = l * alpha + sum;
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(smem_u32(&ss.p_full));
+      mbar_arrive(smem_u32(&ss.p_full[t]));
     }
     // ---- epilogue: O / l and the row statistic
-    if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done), (n_blocks - 1) & 1, wc, kSoftFinal);
+    if (ok && my_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done[t]), (my_blocks - 1) & 1, wc, kSoftFinal);
     tc_fence_after();
-    if (ok && n_blocks > 0) {
+    if (ok && my_blocks > 0) {
       const float inv_l = 1.f / l;
       const bool live = q_row < prm.rows;
       T* orow = (T*)prm.o + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem + lane_addr + O_COL + c * 32, r);
+        tmem_ld_32x32(o_tmem + c * 32, r);
         tmem_ld_wait();
         if (live) {
 #pragma unroll
@@ -345,14 +415,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
 }
 
-template <typename T, int D, uint32_t FMT, bool P_TMEM>
-std::string launch_typed_p(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type) {
+template <typename T, int D, uint32_t FMT>
+std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type) {
   CUtensorMap maps[3];
   const void* bases[3] = {p.q, p.k, p.v};
   for (int i = 0; i < 3; ++i) {
@@ -373,28 +443,17 @@ std::string launch_typed_p(const AttnProblem& p, const LaunchCtx& ctx, CUtensorM
   prm.rows = (int)p.rows;
   prm.causal = p.causal;
   // at least 120 KiB so that two CTAs (each wanting all 512 TMEM columns) never share an SM
-  size_t smem = 5 * (BLOCK_M * D * 2) + BLOCK_M * BLOCK_N * 2 + sizeof(Shared) + 1024;
+  size_t smem = (TILES + 4) * (BLOCK_M * D * 2) + sizeof(Shared) + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
-  auto kernel = attn_fwd_tc_kernel<T, D, FMT, P_TMEM>;
+  auto kernel = attn_fwd_tc_kernel<T, D, FMT>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return std::string("attn_fwd: ") + cudaGetErrorString(e);
-  dim3 grid((unsigned)((p.rows + BLOCK_M - 1) / BLOCK_M), (unsigned)p.bh, 1);
+  dim3 grid((unsigned)((p.rows + TILES * BLOCK_M - 1) / (TILES * BLOCK_M)), (unsigned)p.bh, 1);
   kernel<<<grid, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], prm, ctx.status);
   ++*ctx.launches;
   e = cudaGetLastError();
   if (e != cudaSuccess) return std::string("attn_fwd launch failed: ") + cudaGetErrorString(e);
   return std::string();
-}
-
-template <typename T, int D, uint32_t FMT>
-std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type) {
-  // $TMCUDA_ATTN_P=smem keeps P in shared memory (the first, conservative form).
-  static const bool p_smem = [] {
-    const char* e = std::getenv("TMCUDA_ATTN_P");
-    return e && std::string(e) == "smem";
-  }();
-  return p_smem ? launch_typed_p<T, D, FMT, false>(p, ctx, type)
-                : launch_typed_p<T, D, FMT, true>(p, ctx, type);
 }
 
 }  // namespace
