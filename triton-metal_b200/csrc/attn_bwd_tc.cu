@@ -92,6 +92,140 @@ __device__ __forceinline__ void drain(uint32_t bar, uint32_t parity, const WaitC
   }
 }
 
+// ---- element-wise passes over 128-column tiles in TMEM ----------------------------
+// Written as short loops (two 32-column chunks per trip, the next chunk's loads in flight
+// while the current one is processed): these run once per block, and straight-line code for
+// 128 columns does not stay resident in the instruction cache.
+template <typename T> __device__ __forceinline__ void unpack2(uint32_t u, float& lo, float& hi);
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t u, float& lo, float& hi) {
+  lo = __uint_as_float(u << 16);
+  hi = __uint_as_float(u & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void unpack2<__half>(uint32_t u, float& lo, float& hi) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&u));
+  lo = f.x;
+  hi = f.y;
+}
+
+struct KeyMask {
+  int n0, q_row, n_ctx, causal;
+  __device__ __forceinline__ bool masked(int col) const {
+    const int key = n0 + col;
+    return key >= n_ctx || (causal && key > q_row);
+  }
+};
+
+// dq: dS = exp2(S*qk_scale - L) * (dP - Delta), rounded, written over dP.
+template <typename T, bool MASKED>
+__device__ __forceinline__ void ds_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], uint32_t dst,
+                                         float qk_scale, float neg_lse, float delta, int col0,
+                                         const KeyMask& km) {
+  uint32_t packed[16];
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, neg_lse));
+    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_lse));
+    if (MASKED) {
+      if (km.masked(col0 + i)) p0 = 0.f;
+      if (km.masked(col0 + i + 1)) p1 = 0.f;
+    }
+    packed[i / 2] = pack2<T>(p0 * (__uint_as_float(dp[i]) - delta), p1 * (__uint_as_float(dp[i + 1]) - delta));
+  }
+  tmem_st_32x16(dst, packed);
+}
+
+template <typename T, bool MASKED>
+__device__ __forceinline__ void ds_pass(uint32_t s_tmem, uint32_t dp_tmem, float qk_scale, float neg_lse,
+                                        float delta, const KeyMask& km) {
+  uint32_t sa[32], da[32], sb[32], db[32];
+  tmem_ld_32x32(s_tmem, sa);
+  tmem_ld_32x32(dp_tmem, da);
+#pragma unroll 1
+  for (int c = 0; c < 4; c += 2) {
+    tmem_ld_wait();
+    tmem_ld_32x32(s_tmem + (c + 1) * 32, sb);
+    tmem_ld_32x32(dp_tmem + (c + 1) * 32, db);
+    ds_chunk<T, MASKED>(sa, da, dp_tmem + c * 16, qk_scale, neg_lse, delta, c * 32, km);
+    tmem_ld_wait();
+    if (c + 2 < 4) {
+      tmem_ld_32x32(s_tmem + (c + 2) * 32, sa);
+      tmem_ld_32x32(dp_tmem + (c + 2) * 32, da);
+    }
+    ds_chunk<T, MASKED>(sb, db, dp_tmem + (c + 1) * 16, qk_scale, neg_lse, delta, (c + 1) * 32, km);
+  }
+}
+
+// dkdv pass A: P^T = exp2(S^T*qk_scale - L[query]), rounded, written over S^T; the packed
+// values are also kept in registers (`keep`, 16 words per 32 columns) for pass B.
+template <typename T, bool DIAG>
+__device__ __forceinline__ void pt_chunk(const uint32_t (&s)[32], uint32_t dst, float qk_scale,
+                                         const float* lse_s, int col0, int k_minus_q0, uint32_t* keep) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float4 l = *reinterpret_cast<const float4*>(lse_s + col0 + i);
+    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, -l.x));
+    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, -l.y));
+    float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, -l.z));
+    float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, -l.w));
+    if (DIAG) {
+      // key row k attends query q only when k <= q
+      if (k_minus_q0 > col0 + i) p0 = 0.f;
+      if (k_minus_q0 > col0 + i + 1) p1 = 0.f;
+      if (k_minus_q0 > col0 + i + 2) p2 = 0.f;
+      if (k_minus_q0 > col0 + i + 3) p3 = 0.f;
+    }
+    keep[i / 2] = pack2<T>(p0, p1);
+    keep[i / 2 + 1] = pack2<T>(p2, p3);
+  }
+  uint32_t packed[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) packed[i] = keep[i];
+  tmem_st_32x16(dst, packed);
+}
+
+template <typename T, bool DIAG>
+__device__ __forceinline__ void pt_pass(uint32_t st_tmem, float qk_scale, const float* lse_s, int k_minus_q0,
+                                        uint32_t (&keep)[64]) {
+  uint32_t ra[32], rb[32];
+  tmem_ld_32x32(st_tmem, ra);
+#pragma unroll
+  for (int c = 0; c < 4; c += 2) {
+    tmem_ld_wait();
+    tmem_ld_32x32(st_tmem + (c + 1) * 32, rb);
+    pt_chunk<T, DIAG>(ra, st_tmem + c * 16, qk_scale, lse_s, c * 32, k_minus_q0, &keep[c * 16]);
+    tmem_ld_wait();
+    if (c + 2 < 4) tmem_ld_32x32(st_tmem + (c + 2) * 32, ra);
+    pt_chunk<T, DIAG>(rb, st_tmem + (c + 1) * 16, qk_scale, lse_s, (c + 1) * 32, k_minus_q0,
+                      &keep[(c + 1) * 16]);
+  }
+}
+
+// dkdv pass B: dS^T = P^T * (dP^T - Delta[query]) from the register copy of P^T.
+template <typename T>
+__device__ __forceinline__ void dst_pass(uint32_t dpt_tmem, const float* delta_s, const uint32_t (&keep)[64]) {
+  uint32_t da[32], db[32];
+  tmem_ld_32x32(dpt_tmem, da);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t(&cur)[32] = (c & 1) ? db : da;
+    uint32_t(&nxt)[32] = (c & 1) ? da : db;
+    tmem_ld_wait();
+    if (c < 3) tmem_ld_32x32(dpt_tmem + (c + 1) * 32, nxt);
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      const float4 dl = *reinterpret_cast<const float4*>(delta_s + c * 32 + i);
+      float p0, p1, p2, p3;
+      unpack2<T>(keep[c * 16 + i / 2], p0, p1);
+      unpack2<T>(keep[c * 16 + i / 2 + 1], p2, p3);
+      packed[i / 2] = pack2<T>(p0 * (__uint_as_float(cur[i]) - dl.x), p1 * (__uint_as_float(cur[i + 1]) - dl.y));
+      packed[i / 2 + 1] =
+          pack2<T>(p2 * (__uint_as_float(cur[i + 2]) - dl.z), p3 * (__uint_as_float(cur[i + 3]) - dl.w));
+    }
+    tmem_st_32x16(dpt_tmem + c * 16, packed);
+  }
+}
+
 // ===========================================================================
 // dQ
 // ===========================================================================
@@ -229,39 +363,13 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tc_fence_after();
       const int n0 = j * BLK;
       const bool boundary = (n0 + BLK > prm.n_ctx) || (prm.causal && n0 + BLK > m0);
-      float p[BLK];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem + lane_addr + (s ? S_COL1 : S_COL0) + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = fast_exp2(fmaf(__uint_as_float(r[i]), qk_scale, -lse));
-          if (boundary) {
-            const int key = n0 + c * 32 + i;
-            if (key >= prm.n_ctx || (prm.causal && key > q_row)) v = 0.f;
-          }
-          p[c * 32 + i] = v;
-        }
-      }
       if (!mbar_wait(smem_u32(&ss.dp_full), j & 1, wc, 38)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem + lane_addr + DP_COL + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float d0 = p[c * 32 + i] * (__uint_as_float(r[i]) - delta);
-          const float d1 = p[c * 32 + i + 1] * (__uint_as_float(r[i + 1]) - delta);
-          packed[i / 2] = pack2<T>(d0, d1);
-        }
-        // dS overwrites columns of dP that have already been read
-        tmem_st_32x16(tmem + lane_addr + DP_COL + c * 16, packed);
-      }
+      const KeyMask km{n0, q_row, prm.n_ctx, prm.causal};
+      const uint32_t s_tmem = tmem + lane_addr + (s ? S_COL1 : S_COL0);
+      // dS overwrites columns of dP that have already been read
+      if (boundary) ds_pass<T, true>(s_tmem, tmem + lane_addr + DP_COL, qk_scale, -lse, delta, km);
+      else ds_pass<T, false>(s_tmem, tmem + lane_addr + DP_COL, qk_scale, -lse, delta, km);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&ss.ds_full));
@@ -305,8 +413,8 @@ struct SharedDkdv {
   alignas(8) uint64_t kv_full;
   alignas(8) uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
   alignas(8) uint64_t st_full, dpt_full, p_full, ds_full, done;
-  float lse[2][BLK];
-  float delta[2][BLK];
+  alignas(16) float lse[2][BLK];
+  alignas(16) float delta[2][BLK];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -415,6 +523,8 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         tc_fence_after();
         mma_tn<D>(tmem + DV_COL, tmem + ST_COL, do_addr + s * TILE, idesc_tn, t != 0);
         mma_commit(smem_u32(&ss.do_empty[s]));
+        // the next S^T overwrites P^T: MMAs run in issue order, and the element-wise pass
+        // keeps its own (packed) copy of P^T in registers for dS^T
         if (t + 1 < n_iter && !issue_st(t + 1)) { ok = false; break; }
         if (!mbar_wait(smem_u32(&ss.ds_full), t & 1, wc, 57)) { ok = false; break; }
         tc_fence_after();
@@ -431,65 +541,53 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const float qk_scale = prm.sm_scale * kLog2e;
     const float* lse_base = prm.lse + (int64_t)bh * prm.stride_lse;
     const float* delta_base = prm.delta + (int64_t)bh * prm.stride_lse;
-    auto stage_stats = [&](int t) {
-      // this thread fetches the statistics of query (first+t)*128 + row_in_tile;
-      // +inf as L makes exp2(x - L) vanish for queries past the end
+    // Row statistics of the streamed query block go through shared memory (every thread
+    // needs all 128 of them).  The global loads for block t+1 are issued at the top of
+    // iteration t into registers and only stored to shared memory at its end, so their
+    // latency is off the critical path.  +inf as L makes exp2(x - L) vanish for queries
+    // past the end.
+    auto fetch_stats = [&](int t, float& l, float& d) {
       const int q = (first + t) * BLK + row_in_tile;
-      const bool live = q < prm.n_ctx;
-      ss.lse[t & 1][row_in_tile] = live ? lse_base[q] : INFINITY;
-      ss.delta[t & 1][row_in_tile] = live ? delta_base[q] : 0.f;
+      l = INFINITY;
+      d = 0.f;
+      if (q < prm.n_ctx) {
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(l) : "l"(lse_base + q));
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(d) : "l"(delta_base + q));
+      }
     };
-    if (n_iter > 0) stage_stats(0);
+    if (n_iter > 0) {
+      float l, d;
+      fetch_stats(0, l, d);
+      ss.lse[0][row_in_tile] = l;
+      ss.delta[0][row_in_tile] = d;
+    }
     bool ok = true;
     for (int t = 0; t < n_iter && ok; ++t) {
       // all 128 threads: statistics of block t are visible, block t-1 is no longer read
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (t + 1 < n_iter) stage_stats(t + 1);
+      float next_l = INFINITY, next_d = 0.f;
+      if (t + 1 < n_iter) fetch_stats(t + 1, next_l, next_d);
       const float* lse_s = ss.lse[t & 1];
       const float* delta_s = ss.delta[t & 1];
       const int q0 = (first + t) * BLK;
       const bool diagonal = prm.causal && q0 < n0 + BLK;
       if (!mbar_wait(smem_u32(&ss.st_full), t & 1, wc, 58)) { ok = false; break; }
       tc_fence_after();
-      float p[BLK];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem + lane_addr + ST_COL + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = fast_exp2(fmaf(__uint_as_float(r[i]), qk_scale, -lse_s[c * 32 + i]));
-          if (diagonal && k_row > q0 + c * 32 + i) v = 0.f;
-          p[c * 32 + i] = v;
-        }
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) packed[i / 2] = pack2<T>(p[c * 32 + i], p[c * 32 + i + 1]);
-        tmem_st_32x16(tmem + lane_addr + ST_COL + c * 16, packed);
-      }
+      const uint32_t st_tmem = tmem + lane_addr + ST_COL;
+      uint32_t keep[64];
+      if (diagonal) pt_pass<T, true>(st_tmem, qk_scale, lse_s, k_row - q0, keep);
+      else pt_pass<T, false>(st_tmem, qk_scale, lse_s, 0, keep);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&ss.p_full));
       if (!mbar_wait(smem_u32(&ss.dpt_full), t & 1, wc, 60)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem + lane_addr + DPT_COL + c * 32, r);
-        tmem_ld_wait();
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float d0 = p[c * 32 + i] * (__uint_as_float(r[i]) - delta_s[c * 32 + i]);
-          const float d1 = p[c * 32 + i + 1] * (__uint_as_float(r[i + 1]) - delta_s[c * 32 + i + 1]);
-          packed[i / 2] = pack2<T>(d0, d1);
-        }
-        tmem_st_32x16(tmem + lane_addr + DPT_COL + c * 16, packed);
-      }
+      dst_pass<T>(tmem + lane_addr + DPT_COL, delta_s, keep);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&ss.ds_full));
+      ss.lse[(t + 1) & 1][row_in_tile] = next_l;
+      ss.delta[(t + 1) & 1][row_in_tile] = next_d;
     }
     if (ok && n_iter > 0) ok = mbar_wait(smem_u32(&ss.done), 0, wc, 61);
     tc_fence_after();
