@@ -69,6 +69,23 @@ def flops(w):
     return total / 2 if w["causal"] else total
 
 
+def config_of(name):
+    """The `config` object both arms print."""
+    w = WORKLOADS[name]
+    out = {"workload": name}
+    out.update({k: v for k, v in w.items() if k != "kind"})
+    out["sharding"] = "rows of M + all-gather of C" if w["kind"] == "gemm" else "(batch, head)"
+    out["l2"] = "inputs larger than L2, no flush"
+    return out
+
+
+#: dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
+#: ncu captures summarised under profiles/ (same workload sizes as the benchmark).
+NCU_TRAFFIC_BYTES = {
+    "gemm_bf16_8192": 1123.3e6,
+}
+
+
 def shard(total, rank, world):
     """Contiguous block partition of `total` units: (first, count)."""
     base, extra = divmod(total, world)
@@ -101,7 +118,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -504,7 +521,7 @@ def reference_arm(args):
         "impl": "reference", "metric": "bf16_gemm_fa2_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic", "config": {"workload": name, **{k: v for k, v in w.items() if k != "kind"}},
+        "data": "synthetic", "config": config_of(name),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -515,7 +532,7 @@ def reference_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="tmcuda", choices=["tmcuda", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
@@ -555,7 +572,7 @@ def main():
             "bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
             "frac": per_gpu / peak,
             "peak_source": f"{pk['source']} cuBLAS bf16 {'sustained' if long_region else 'burst'}",
-            "traffic": None,
+            "traffic": NCU_TRAFFIC_BYTES.get(name),
             "algorithmic_bytes_per_launch": head["bytes_per_launch"],
         }
         line = {
@@ -563,9 +580,7 @@ def main():
             "n_gpus": dist.world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": name, **{k: v for k, v in w.items() if k != "kind"},
-                       "sharding": "rows of M + all-gather of C" if w["kind"] == "gemm" else "(batch, head)",
-                       "l2": "inputs larger than L2, no flush"},
+            "config": config_of(name),
             "per_gpu_tflops": per_gpu,
             "frac_of_bf16_peak": per_gpu / pk["tf_burst"],
             "roofline": roofline,
