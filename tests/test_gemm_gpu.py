@@ -171,3 +171,53 @@ def test_launch_validation_on_the_device(core):
     finally:
         mm.release()
         a.free()
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 256), (384, 200, 1000), (1024, 512, 4096), (130, 72, 520)])
+def test_fp32_tensor_core_path_is_3xtf32_accurate(shape):
+    """fp32 operands on the tensor cores (split into tf32 hi/lo, three MMAs per K
+    step, K accumulated in chunks): within 1e-5 of a float64 product for every K."""
+    M, N, K = shape
+    a, b = inputs.gemm_uniform(M, N, K, seed=K)
+    c, path = tmtest.run_matmul(a, b, "f32", path=cuda.PATH_TCGEN05)
+    assert path == cuda.PATH_TCGEN05
+    want = a.astype(np.float64) @ b.astype(np.float64)
+    assert ref.relative_error(c, want) <= 1e-5
+    assert ref.relative_error(c, ref.matmul(a, b)) <= 1e-5
+
+
+def test_fp32_tensor_core_path_takes_any_stride():
+    """The operand split rewrites A and B densely, so transposed and padded inputs and a
+    strided C all go through the tensor-core path."""
+    M, N, K = 256, 192, 320
+    a, b = inputs.gemm_normal(M, N, K, seed=4)
+    a_t = np.ascontiguousarray(a.T)                    # stride_am = 1, stride_ak = M
+    b_pad = np.zeros((K, N + 5), dtype=np.float32)
+    b_pad[:, :N] = b
+    strides = (1, M, N + 5, 1, N + 3, 1)
+    ab, bb = tmtest.upload(a_t, "f32"), tmtest.upload(b_pad, "f32")
+    cb = tmtest.empty((M, N + 3), "f32")
+    tmtest.put(cb, np.full((M, N + 3), -9.0, dtype=np.float32))
+    from triton_metal import kernels
+    mm = kernels.Matmul("f32", (128, 128, 32))
+    try:
+        mm.set_path(cuda.PATH_TCGEN05)
+        mm(ab.tm_handle, bb.tm_handle, cb.tm_handle, M, N, K, strides)
+        c = tmtest.fetch(cb)
+        assert mm.last_path() == cuda.PATH_TCGEN05
+        assert ref.relative_error(c[:, :N], ref.matmul(a, b)) <= 1e-5
+        assert np.all(c[:, N:] == -9.0)
+    finally:
+        mm.release()
+        for buf in (ab, bb, cb):
+            buf.free()
+
+
+def test_fp32_large_k_against_float64_rows():
+    M, N, K = 512, 2048, 8192
+    a, b = inputs.gemm_normal(M, N, K, seed=12)
+    c, path = tmtest.run_matmul(a, b, "f32")
+    assert path == cuda.PATH_TCGEN05
+    rows = np.r_[0:16, 250:266, M - 16:M]
+    want = a[rows].astype(np.float64) @ b.astype(np.float64)
+    assert ref.relative_error(c[rows], want) <= 1e-5

@@ -318,7 +318,7 @@ bool gemm_tc_eligible(const GemmProblem& p, std::string* why) {
     if (why) *why = m;
     return false;
   };
-  if (p.elt == Elt::F32) return no("fp32 operands take the generic kernel");
+  if (p.elt == Elt::F32) return no("fp32 operands take the 3xTF32 kernel");
   if (p.sak != 1 || p.sbn != 1 || p.scn != 1) return no("operands are not row-major with unit inner stride");
   if (p.sam % 8 || p.sbk % 8 || p.scm % 8) return no("row strides are not multiples of 16 bytes");
   if (((uintptr_t)p.a | (uintptr_t)p.b | (uintptr_t)p.c) % 16) return no("base pointers are not 16-byte aligned");

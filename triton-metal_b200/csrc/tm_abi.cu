@@ -427,13 +427,14 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
     if (!check_extent(*C, (M - 1) * p.scm + (N - 1) * p.scn, eb, "C", err)) return false;
     prefetch_exposed(d);
     std::string why;
-    bool tc = k.path_option != 1 && gemm_tc_eligible(p, &why);
+    const bool f32 = p.elt == Elt::F32;
+    bool tc = k.path_option != 1 && (f32 ? gemm_tf32_eligible(p, &why) : gemm_tc_eligible(p, &why));
     if (k.path_option == 2 && !tc) {
       err = invalid_argument("the tcgen05 path was required but this launch is not eligible: " + why);
       return false;
     }
     for (int r = 0; r < repeats; ++r) {
-      std::string e = tc ? launch_gemm_tc(p, ctx) : launch_gemm_simt(p, ctx);
+      std::string e = !tc ? launch_gemm_simt(p, ctx) : (f32 ? launch_gemm_tf32(p, ctx) : launch_gemm_tc(p, ctx));
       if (!e.empty()) { err = cuda_error(e); return false; }
     }
     k.last_path = tc ? 2 : 1;

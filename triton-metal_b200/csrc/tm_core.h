@@ -119,6 +119,11 @@ std::string launch_attn_bwd_dkdv_simt(const AttnProblem& p, const LaunchCtx& ctx
 // tcgen05 paths: `eligible` says whether the shape can take the path.
 bool gemm_tc_eligible(const GemmProblem& p, std::string* why);
 std::string launch_gemm_tc(const GemmProblem& p, const LaunchCtx& ctx);
+// fp32 operands: 3xTF32 on the tensor cores, operands split into scratch memory.
+bool gemm_tf32_eligible(const GemmProblem& p, std::string* why);
+std::string launch_gemm_tf32(const GemmProblem& p, const LaunchCtx& ctx);           // library workspace
+size_t gemm_tf32_scratch_bytes(int64_t M, int64_t N, int64_t K);
+std::string run_gemm_tf32(const GemmProblem& p, const LaunchCtx& ctx, void* scratch);  // caller's scratch
 bool attn_fwd_tc_eligible(const AttnProblem& p, std::string* why);
 std::string launch_attn_fwd_tc(const AttnProblem& p, const LaunchCtx& ctx);
 bool attn_bwd_tc_eligible(const AttnProblem& p, std::string* why);
