@@ -146,6 +146,36 @@ int32_t tmx_timer_end(float *elapsed_ms);
 /* Count of kernels this library has launched since load (for launch accounting). */
 int64_t tmx_launch_count(void);
 
+/* fp32 C[M,N] = A[M,K] @ B[K,N] for callers that must not allocate device memory.
+ * No counterpart in the reference.
+ *
+ * The fp32 matmul runs on the tensor cores as 3xTF32, which needs scratch for the split
+ * operands: 8*(M+N)*roundup(K,4) bytes.  tm_launch takes that from a workspace it grows with
+ * cudaMalloc when a larger problem arrives.  That is unusable for a host that has already
+ * given all device memory to its own pool, for a service that may not allocate once it has
+ * started serving, and for any code running where the CUDA runtime refuses allocation.  This
+ * entry point is the same kernel pair with the scratch in a fixed array that is part of the
+ * library image: it calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ *  - a, b, c are fp32 buffer handles (the caller still owns inputs and outputs); strides are
+ *    in elements, any non-negative value; the call waits for the result like tm_launch.
+ *  - Limit: 8*(M+N)*roundup(K,4) must not exceed tmx_matmul_f32_static_capacity() (8 MiB;
+ *    e.g. 512 x 512 x 1024).  Larger problems, and problems below 128 x 64 x 32, are refused
+ *    with -1 and a message; use tm_launch for those.
+ *  - Every GPU that loads the library holds the 8 MiB array until the process exits.
+ *  - The first call on a device looks up the array's device address (one
+ *    cudaGetSymbolAddress with that device current).  Make that first call during start-up,
+ *    before any stream capture is begun.
+ *  - All calls share the one array and it keeps whatever the last call left in it.  Nothing
+ *    needs clearing: each call first rewrites every word its GEMM reads.  Calls are ordered on
+ *    the library's single stream; work that overlaps on the GPU with one of these calls and
+ *    also uses the array (there is none inside this library) would race. */
+int32_t tmx_matmul_f32_static(int64_t a, int64_t b, int64_t c, int64_t M, int64_t N, int64_t K,
+                              int64_t stride_am, int64_t stride_ak, int64_t stride_bk,
+                              int64_t stride_bn, int64_t stride_cm, int64_t stride_cn);
+/* Size in bytes of the fixed scratch array behind tmx_matmul_f32_static. */
+int64_t tmx_matmul_f32_static_capacity(void);
+
 #ifdef __cplusplus
 }
 #endif

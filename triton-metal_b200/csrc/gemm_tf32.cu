@@ -281,6 +281,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
   }
 }
 
+// Fixed scratch for tmx_matmul_f32_static: lives in the library image, so every GPU that
+// loads the library holds these 8 MiB until the process exits.  In host code the name
+// `g_static_scratch` is only a stand-in for the symbol; the device address is obtained
+// with cudaGetSymbolAddress below and that address is what the kernels receive.
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+
 // Workspace the library owns for tm_launch (grown on demand, never shrunk).
 struct Workspace {
   std::mutex lock;
@@ -372,6 +380,43 @@ std::string launch_gemm_tf32(const GemmProblem& p, const LaunchCtx& ctx) {
     g_workspace.bytes = need;
   }
   return run_gemm_tf32(p, ctx, g_workspace.ptr);
+}
+
+}  // namespace tmc
+
+namespace tmc {
+
+size_t gemm_tf32_static_capacity() { return kStaticScratchBytes; }
+
+// The 3xTF32 GEMM with its operand split in the fixed device array instead of an allocated
+// workspace.  The first call on a device resolves the array's device address (with that
+// device current); nothing here allocates or frees device memory.  Every call uses the same
+// array: the split kernels rewrite every word the GEMM will read (including the zero padding
+// of K up to a multiple of 4), so nothing left by an earlier call is ever consumed.
+std::string run_gemm_tf32_static(const GemmProblem& p, const LaunchCtx& ctx, int device) {
+  static std::mutex lock;
+  static void* address[kMaxDevices] = {};
+  if (device < 0 || device >= kMaxDevices) return "device ordinal outside 0..63";
+  const size_t need = gemm_tf32_scratch_bytes(p.M, p.N, p.K);
+  if (need > kStaticScratchBytes) {
+    return "the operand split needs " + std::to_string(need) + " bytes of scratch (8*(M+N)*roundup(K,4)), more than the " +
+           std::to_string(kStaticScratchBytes) + "-byte fixed array; use tm_launch for this size";
+  }
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> guard(lock);
+    if (!address[device]) {
+      void* ptr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+      if (e != cudaSuccess || !ptr) {
+        cudaGetLastError();
+        return std::string("could not resolve the fixed scratch array on this device: ") + cudaGetErrorString(e);
+      }
+      address[device] = ptr;
+    }
+    scratch = address[device];
+  }
+  return run_gemm_tf32(p, ctx, scratch);
 }
 
 }  // namespace tmc

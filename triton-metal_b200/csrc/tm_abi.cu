@@ -915,4 +915,58 @@ int32_t tmx_timer_end(float* elapsed_ms) {
 
 int64_t tmx_launch_count(void) { return g_dev.launches; }
 
+// fp32 C = A @ B with no device allocation anywhere on the path: the scratch for the
+// 3xTF32 operand split is a fixed array inside the library.  Same arithmetic as
+// matmul_kernel launched through tm_launch on fp32 buffers.
+int32_t tmx_matmul_f32_static(int64_t a, int64_t b, int64_t c, int64_t M, int64_t N, int64_t K,
+                              int64_t stride_am, int64_t stride_ak, int64_t stride_bk,
+                              int64_t stride_bn, int64_t stride_cm, int64_t stride_cn) {
+  std::string err;
+  auto A = lookup_as<BufferObj>(a, ObjKind::Buffer, err);
+  auto B = A ? lookup_as<BufferObj>(b, ObjKind::Buffer, err) : nullptr;
+  auto C = B ? lookup_as<BufferObj>(c, ObjKind::Buffer, err) : nullptr;
+  if (!C) { store_error(err); return -1; }
+  if (M <= 0 || N <= 0 || K <= 0 || stride_am < 0 || stride_ak < 0 || stride_bk < 0 || stride_bn < 0 ||
+      stride_cm < 0 || stride_cn < 0) {
+    store_error(invalid_argument("tmx_matmul_f32_static needs positive extents and non-negative strides"));
+    return -1;
+  }
+  GemmProblem p{};
+  p.elt = Elt::F32;
+  p.a = A->ptr; p.b = B->ptr; p.c = C->ptr;
+  p.M = M; p.N = N; p.K = K;
+  p.sam = stride_am; p.sak = stride_ak; p.sbk = stride_bk; p.sbn = stride_bn;
+  p.scm = stride_cm; p.scn = stride_cn;
+  if (!check_extent(*A, (M - 1) * p.sam + (K - 1) * p.sak, 4, "A", err) ||
+      !check_extent(*B, (K - 1) * p.sbk + (N - 1) * p.sbn, 4, "B", err) ||
+      !check_extent(*C, (M - 1) * p.scm + (N - 1) * p.scn, 4, "C", err)) {
+    store_error(err);
+    return -1;
+  }
+  std::string why;
+  if (M < 128 || N < 64 || K < 32) {
+    store_error(invalid_argument("tmx_matmul_f32_static takes problems of at least 128 x 64 x 32"));
+    return -1;
+  }
+  if (!bind_device(err)) { store_error(err); return -1; }
+  if (g_dev.prop.major != 10) {
+    store_error(cuda_error("this device is not sm_100; libtmcuda holds sm_100a code only"));
+    return -1;
+  }
+  Decoded d;
+  d.buffers[(int)Role::A] = A;
+  d.buffers[(int)Role::B] = B;
+  d.buffers[(int)Role::C] = C;
+  prefetch_exposed(d);
+  std::string e = run_gemm_tf32_static(p, launch_ctx(), g_dev.ordinal);
+  if (!e.empty()) {
+    store_error(e.rfind("the operand split needs", 0) == 0 ? invalid_argument(e) : cuda_error(e));
+    return -1;
+  }
+  if (!sync_stream(err)) { store_error(err); return -1; }
+  return 0;
+}
+
+int64_t tmx_matmul_f32_static_capacity(void) { return (int64_t)gemm_tf32_static_capacity(); }
+
 }  // extern "C"

@@ -124,6 +124,8 @@ bool gemm_tf32_eligible(const GemmProblem& p, std::string* why);
 std::string launch_gemm_tf32(const GemmProblem& p, const LaunchCtx& ctx);           // library workspace
 size_t gemm_tf32_scratch_bytes(int64_t M, int64_t N, int64_t K);
 std::string run_gemm_tf32(const GemmProblem& p, const LaunchCtx& ctx, void* scratch);  // caller's scratch
+std::string run_gemm_tf32_static(const GemmProblem& p, const LaunchCtx& ctx, int device);  // fixed device array
+size_t gemm_tf32_static_capacity();
 bool attn_fwd_tc_eligible(const AttnProblem& p, std::string* why);
 std::string launch_attn_fwd_tc(const AttnProblem& p, const LaunchCtx& ctx);
 bool attn_bwd_tc_eligible(const AttnProblem& p, std::string* why);

@@ -27,6 +27,8 @@ EXPORTS = {
     "tmx_timer_begin": (_I32, ()),
     "tmx_timer_end": (_I32, (_F32P,)),
     "tmx_launch_count": (_I64, ()),
+    "tmx_matmul_f32_static": (_I32, (_I64,) * 12),
+    "tmx_matmul_f32_static_capacity": (_I64, ()),
 }
 
 for _symbol, (_ret, _args) in EXPORTS.items():
@@ -106,3 +108,15 @@ def timer_end() -> float:
 
 def launch_count() -> int:
     return _lib.tmx_launch_count()
+
+
+def matmul_f32_static(a, b, c, M, N, K, strides=None) -> None:
+    """fp32 C = A @ B through the entry point that allocates nothing (scratch in a
+    fixed device array; see include/tm.h for the size limit)."""
+    if strides is None:
+        strides = (K, 1, N, 1, N, 1)
+    _ok(_lib.tmx_matmul_f32_static(a, b, c, M, N, K, *strides))
+
+
+def matmul_f32_static_capacity() -> int:
+    return _lib.tmx_matmul_f32_static_capacity()
