@@ -9,13 +9,17 @@
 // directions stay separate kernels, as in the reference, so every gradient is
 // deterministic (no atomics).
 //
-// Both kernels: one CTA per 128 resident rows of one (batch, head); warp 4 issues
-// TMA loads, warp 5 issues tcgen05.mma, warps 0-3 (one thread per resident row =
-// one TMEM lane) do the exponentials and products.  The 16-bit P / dS tiles never
-// touch shared memory: they are written back into the TMEM columns their fp32
-// sources came from and feed the next MMA as TMEM operands.
+// Both kernels: one CTA per 128 resident rows of one (batch, head) (queries for
+// dq, keys for dkdv); the other side streams through in blocks of 128 rows (MMAs
+// with N = 128: narrower score tiles ran the tensor pipe at half rate, measured).
+// Warp 4 issues TMA loads, warp 5 issues tcgen05.mma, and two warpgroups (warps 0-3
+// and 6-9) do the exponentials and products: a thread owns one resident row (its
+// TMEM lane) and one half of the 128 columns of a block, so the TMEM round trips of
+// one group are covered by the arithmetic of the other.  The 16-bit P / dS tiles
+// never touch shared memory: each group writes them back over the fp32 columns it
+// read and they feed the next MMA as TMEM operands.
 //
-// TMEM columns (512):  dq:    S[2] | dP (dS aliases) | dQ
+// TMEM columns (512):  dq:    S[2] (dS aliases) | dP | dQ
 //                      dkdv:  S^T (P^T aliases) | dP^T (dS^T aliases) | dV | dK
 //
 // HBM layout: Q, K, V, dO, dQ, dK, dV [BH, S, D] with D contiguous; L, Delta
@@ -32,7 +36,8 @@ namespace {
 using namespace ptx;
 
 constexpr int BLK = 128;              // rows per tile on both sides
-constexpr int NUM_THREADS = 192;
+constexpr int HALF = 64;              // columns of a block owned by one element-wise group
+constexpr int NUM_THREADS = 320;      // warps 0-3 and 6-9 element-wise, 4 TMA, 5 MMA
 constexpr int TMEM_COLS = 512;
 constexpr float kLog2e = 1.44269504088896340736f;
 
@@ -55,47 +60,6 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
   __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-
-template <int D>
-__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar, int row0,
-                                          int bh) {
-#pragma unroll
-  for (int h = 0; h < D / 64; ++h) tma_load_3d(dst + h * (BLK * 128), map, bar, h * 64, row0, bh);
-}
-
-// S-shaped product: D_tmem[128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles.
-template <int D>
-__device__ __forceinline__ void mma_nt(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc) {
-#pragma unroll
-  for (int kk = 0; kk < D / 16; ++kk) {
-    const uint32_t off = (kk / 4) * (BLK * 128) + (kk % 4) * 32;
-    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + off, 0, 1024), smem_desc_sw128(b_addr + off, 0, 1024),
-               idesc, kk != 0);
-  }
-}
-
-// Accumulating product with a TMEM operand: D_tmem[128 x D] (+)= A_tmem[128 x 128] * B[128 x D],
-// B a row-major (MN-major) tile of 128 rows.
-template <int D>
-__device__ __forceinline__ void mma_tn(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t idesc,
-                                       bool accumulate) {
-#pragma unroll
-  for (int kk = 0; kk < BLK / 16; ++kk)
-    mma_f16_ts(d_tmem, a_tmem + kk * 8, smem_desc_sw128(b_addr + kk * 2048, BLK * 128, 1024), idesc,
-               accumulate || kk != 0);
-}
-
-__device__ __forceinline__ void drain(uint32_t bar, uint32_t parity, const WaitCtx& wc, uint32_t site) {
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) { report_timeout(wc, site, parity); break; }
-  }
-}
-
-// ---- element-wise passes over 128-column tiles in TMEM ----------------------------
-// Written as short loops (two 32-column chunks per trip, the next chunk's loads in flight
-// while the current one is processed): these run once per block, and straight-line code for
-// 128 columns does not stay resident in the instruction cache.
 template <typename T> __device__ __forceinline__ void unpack2(uint32_t u, float& lo, float& hi);
 template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t u, float& lo, float& hi) {
   lo = __uint_as_float(u << 16);
@@ -107,6 +71,44 @@ template <> __device__ __forceinline__ void unpack2<__half>(uint32_t u, float& l
   hi = f.y;
 }
 
+template <int D>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar, int row0,
+                                          int bh) {
+#pragma unroll
+  for (int h = 0; h < D / 64; ++h) tma_load_3d(dst + h * (BLK * 128), map, bar, h * 64, row0, bh);
+}
+
+// D_tmem[128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles.
+template <int D>
+__device__ __forceinline__ void mma_nt(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc) {
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const uint32_t off = (kk / 4) * (BLK * 128) + (kk % 4) * 32;
+    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + off, 0, 1024), smem_desc_sw128(b_addr + off, 0, 1024),
+               idesc, kk != 0);
+  }
+}
+
+// D_tmem[128 x D] (+)= A_tmem[128 x 128] * B[128 x D]; B a row-major (MN-major) tile of
+// 128 rows.  The 16-bit A operand is stored by the two element-wise groups in two pieces:
+// columns 0-63 of the block packed at a_tmem+0..31, columns 64-127 at a_tmem+64..95.
+template <int D>
+__device__ __forceinline__ void mma_tn(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t idesc,
+                                       bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < BLK / 16; ++kk)
+    mma_f16_ts(d_tmem, a_tmem + (kk / 4) * HALF + (kk % 4) * 8,
+               smem_desc_sw128(b_addr + kk * 2048, BLK * 128, 1024), idesc, accumulate || kk != 0);
+}
+
+__device__ __forceinline__ void drain(uint32_t bar, uint32_t parity, const WaitCtx& wc, uint32_t site) {
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kWaitCycles) { report_timeout(wc, site, parity); break; }
+  }
+}
+
+// ---- element-wise passes over one group's 64 columns of a block --------------------
 struct KeyMask {
   int n0, q_row, n_ctx, causal;
   __device__ __forceinline__ bool masked(int col) const {
@@ -115,141 +117,151 @@ struct KeyMask {
   }
 };
 
-// dq: dS = exp2(S*qk_scale - L) * (dP - Delta), rounded, written over dP.
+// dq: dS = exp2(S*qk_scale - L) * (dP - Delta), rounded, written over S.
+// `s_tmem` / `dp_tmem` point at the group's first column; km.n0 is that column's key.
 template <typename T, bool MASKED>
-__device__ __forceinline__ void ds_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], uint32_t dst,
-                                         float qk_scale, float neg_lse, float delta, int col0,
-                                         const KeyMask& km) {
-  uint32_t packed[16];
-#pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, neg_lse));
-    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_lse));
-    if (MASKED) {
-      if (km.masked(col0 + i)) p0 = 0.f;
-      if (km.masked(col0 + i + 1)) p1 = 0.f;
-    }
-    packed[i / 2] = pack2<T>(p0 * (__uint_as_float(dp[i]) - delta), p1 * (__uint_as_float(dp[i + 1]) - delta));
-  }
-  tmem_st_32x16(dst, packed);
-}
-
-template <typename T, bool MASKED>
-__device__ __forceinline__ void ds_pass(uint32_t s_tmem, uint32_t dp_tmem, float qk_scale, float neg_lse,
+__device__ __forceinline__ void ds_half(uint32_t s_tmem, uint32_t dp_tmem, float qk_scale, float neg_lse,
                                         float delta, const KeyMask& km) {
-  uint32_t sa[32], da[32], sb[32], db[32];
-  tmem_ld_32x32(s_tmem, sa);
-  tmem_ld_32x32(dp_tmem, da);
-#pragma unroll 1
-  for (int c = 0; c < 4; c += 2) {
-    tmem_ld_wait();
-    tmem_ld_32x32(s_tmem + (c + 1) * 32, sb);
-    tmem_ld_32x32(dp_tmem + (c + 1) * 32, db);
-    ds_chunk<T, MASKED>(sa, da, dp_tmem + c * 16, qk_scale, neg_lse, delta, c * 32, km);
-    tmem_ld_wait();
-    if (c + 2 < 4) {
-      tmem_ld_32x32(s_tmem + (c + 2) * 32, sa);
-      tmem_ld_32x32(dp_tmem + (c + 2) * 32, da);
+  uint32_t s0[32], d0[32], s1[32], d1[32];
+  tmem_ld_32x32(s_tmem, s0);
+  tmem_ld_32x32(dp_tmem, d0);
+  tmem_ld_32x32(s_tmem + 32, s1);
+  tmem_ld_32x32(dp_tmem + 32, d1);
+  tmem_ld_wait();
+  uint32_t packed[32];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t(&s)[32] = h ? s1 : s0;
+    const uint32_t(&d)[32] = h ? d1 : d0;
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, neg_lse));
+      float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_lse));
+      if (MASKED) {
+        if (km.masked(h * 32 + i)) p0 = 0.f;
+        if (km.masked(h * 32 + i + 1)) p1 = 0.f;
+      }
+      packed[h * 16 + i / 2] =
+          pack2<T>(p0 * (__uint_as_float(d[i]) - delta), p1 * (__uint_as_float(d[i + 1]) - delta));
     }
-    ds_chunk<T, MASKED>(sb, db, dp_tmem + (c + 1) * 16, qk_scale, neg_lse, delta, (c + 1) * 32, km);
   }
+  tmem_st_32x32(s_tmem, packed);
 }
 
-// dkdv pass A: P^T = exp2(S^T*qk_scale - L[query]), rounded, written over S^T; the packed
-// values are also kept in registers (`keep`, 16 words per 32 columns) for pass B.
+// dkdv pass A: P^T = exp2(S^T*qk_scale - L[query]), rounded, written over S^T and kept
+// (packed, 32 words) for pass B.  `k_minus_q0` > column means key row > query: masked.
 template <typename T, bool DIAG>
-__device__ __forceinline__ void pt_chunk(const uint32_t (&s)[32], uint32_t dst, float qk_scale,
-                                         const float* lse_s, int col0, int k_minus_q0, uint32_t* keep) {
+__device__ __forceinline__ void pt_half(uint32_t st_tmem, float qk_scale, const float* lse_s, int k_minus_q0,
+                                        uint32_t (&keep)[32]) {
+  uint32_t s0[32], s1[32];
+  tmem_ld_32x32(st_tmem, s0);
+  tmem_ld_32x32(st_tmem + 32, s1);
+  tmem_ld_wait();
 #pragma unroll
-  for (int i = 0; i < 32; i += 4) {
-    const float4 l = *reinterpret_cast<const float4*>(lse_s + col0 + i);
-    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, -l.x));
-    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, -l.y));
-    float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, -l.z));
-    float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, -l.w));
-    if (DIAG) {
-      // key row k attends query q only when k <= q
-      if (k_minus_q0 > col0 + i) p0 = 0.f;
-      if (k_minus_q0 > col0 + i + 1) p1 = 0.f;
-      if (k_minus_q0 > col0 + i + 2) p2 = 0.f;
-      if (k_minus_q0 > col0 + i + 3) p3 = 0.f;
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t(&s)[32] = h ? s1 : s0;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      const float4 l = *reinterpret_cast<const float4*>(lse_s + h * 32 + i);
+      float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, -l.x));
+      float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, -l.y));
+      float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, -l.z));
+      float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, -l.w));
+      if (DIAG) {
+        const int col = h * 32 + i;
+        if (k_minus_q0 > col) p0 = 0.f;
+        if (k_minus_q0 > col + 1) p1 = 0.f;
+        if (k_minus_q0 > col + 2) p2 = 0.f;
+        if (k_minus_q0 > col + 3) p3 = 0.f;
+      }
+      keep[h * 16 + i / 2] = pack2<T>(p0, p1);
+      keep[h * 16 + i / 2 + 1] = pack2<T>(p2, p3);
     }
-    keep[i / 2] = pack2<T>(p0, p1);
-    keep[i / 2 + 1] = pack2<T>(p2, p3);
   }
-  uint32_t packed[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) packed[i] = keep[i];
-  tmem_st_32x16(dst, packed);
-}
-
-template <typename T, bool DIAG>
-__device__ __forceinline__ void pt_pass(uint32_t st_tmem, float qk_scale, const float* lse_s, int k_minus_q0,
-                                        uint32_t (&keep)[64]) {
-  uint32_t ra[32], rb[32];
-  tmem_ld_32x32(st_tmem, ra);
-#pragma unroll
-  for (int c = 0; c < 4; c += 2) {
-    tmem_ld_wait();
-    tmem_ld_32x32(st_tmem + (c + 1) * 32, rb);
-    pt_chunk<T, DIAG>(ra, st_tmem + c * 16, qk_scale, lse_s, c * 32, k_minus_q0, &keep[c * 16]);
-    tmem_ld_wait();
-    if (c + 2 < 4) tmem_ld_32x32(st_tmem + (c + 2) * 32, ra);
-    pt_chunk<T, DIAG>(rb, st_tmem + (c + 1) * 16, qk_scale, lse_s, (c + 1) * 32, k_minus_q0,
-                      &keep[(c + 1) * 16]);
-  }
+  tmem_st_32x32(st_tmem, keep);
 }
 
 // dkdv pass B: dS^T = P^T * (dP^T - Delta[query]) from the register copy of P^T.
 template <typename T>
-__device__ __forceinline__ void dst_pass(uint32_t dpt_tmem, const float* delta_s, const uint32_t (&keep)[64]) {
-  uint32_t da[32], db[32];
-  tmem_ld_32x32(dpt_tmem, da);
+__device__ __forceinline__ void dst_half(uint32_t dpt_tmem, const float* delta_s, const uint32_t (&keep)[32]) {
+  uint32_t d0[32], d1[32];
+  tmem_ld_32x32(dpt_tmem, d0);
+  tmem_ld_32x32(dpt_tmem + 32, d1);
+  tmem_ld_wait();
+  uint32_t packed[32];
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t(&cur)[32] = (c & 1) ? db : da;
-    uint32_t(&nxt)[32] = (c & 1) ? da : db;
-    tmem_ld_wait();
-    if (c < 3) tmem_ld_32x32(dpt_tmem + (c + 1) * 32, nxt);
-    uint32_t packed[16];
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t(&d)[32] = h ? d1 : d0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
-      const float4 dl = *reinterpret_cast<const float4*>(delta_s + c * 32 + i);
+      const float4 dl = *reinterpret_cast<const float4*>(delta_s + h * 32 + i);
       float p0, p1, p2, p3;
-      unpack2<T>(keep[c * 16 + i / 2], p0, p1);
-      unpack2<T>(keep[c * 16 + i / 2 + 1], p2, p3);
-      packed[i / 2] = pack2<T>(p0 * (__uint_as_float(cur[i]) - dl.x), p1 * (__uint_as_float(cur[i + 1]) - dl.y));
-      packed[i / 2 + 1] =
-          pack2<T>(p2 * (__uint_as_float(cur[i + 2]) - dl.z), p3 * (__uint_as_float(cur[i + 3]) - dl.w));
+      unpack2<T>(keep[h * 16 + i / 2], p0, p1);
+      unpack2<T>(keep[h * 16 + i / 2 + 1], p2, p3);
+      packed[h * 16 + i / 2] =
+          pack2<T>(p0 * (__uint_as_float(d[i]) - dl.x), p1 * (__uint_as_float(d[i + 1]) - dl.y));
+      packed[h * 16 + i / 2 + 1] =
+          pack2<T>(p2 * (__uint_as_float(d[i + 2]) - dl.z), p3 * (__uint_as_float(d[i + 3]) - dl.w));
     }
-    tmem_st_32x16(dpt_tmem + c * 16, packed);
+  }
+  tmem_st_32x32(dpt_tmem, packed);
+}
+
+// Read-out of `COLS` columns of a fp32 accumulator row: scale, round, store.
+template <typename T, int COLS>
+__device__ __forceinline__ void store_rows(uint32_t acc_tmem, T* orow, float scale, bool live) {
+#pragma unroll 1
+  for (int c = 0; c < COLS / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(acc_tmem + c * 32, r);
+    tmem_ld_wait();
+    if (live) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 out;
+        out.x = pack2<T>(__uint_as_float(r[v * 8 + 0]) * scale, __uint_as_float(r[v * 8 + 1]) * scale);
+        out.y = pack2<T>(__uint_as_float(r[v * 8 + 2]) * scale, __uint_as_float(r[v * 8 + 3]) * scale);
+        out.z = pack2<T>(__uint_as_float(r[v * 8 + 4]) * scale, __uint_as_float(r[v * 8 + 5]) * scale);
+        out.w = pack2<T>(__uint_as_float(r[v * 8 + 6]) * scale, __uint_as_float(r[v * 8 + 7]) * scale);
+        *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = out;
+      }
+    }
   }
 }
 
 // ===========================================================================
 // dQ
 // ===========================================================================
+constexpr int K_STAGES = 3, V_STAGES = 2;
+
 struct SharedDq {
   alignas(8) uint64_t qdo_full;
-  alignas(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  alignas(8) uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
   alignas(8) uint64_t s_full[2];
   alignas(8) uint64_t dp_full, ds_full, dq_done;
   uint32_t tmem_base;
   int abort_flag;
 };
 
+// Pipeline of block j (keys j*128 ...):
+//   MMA   S(j) = Q K(j)^T into S[j&1]            (issued two blocks ahead)
+//   MMA   dP(j) = dO V(j)^T into the single dP buffer, as soon as the element-wise pass of
+//         block j-1 has read dP(j-1)
+//   elem  dS(j) written over S[j&1]
+//   MMA   dQ += dS(j) K(j)
+// so the chain from one block's element-wise pass to the next is one MMA (dP) long.
 template <typename T, int D, uint32_t FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                       Params prm, DeviceStatus* status) {
   constexpr int TILE = BLK * D * 2;
-  constexpr int S_COL0 = 0, S_COL1 = 128, DP_COL = 256, DQ_COL = 384;
+  constexpr int S_COL = 0, DP_COL = 256, DQ_COL = 384;     // S[b] at b*128
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t q_addr = smem_u32(smem), do_addr = q_addr + TILE, k_addr = do_addr + TILE,
-                 v_addr = k_addr + 2 * TILE;
-  SharedDq& ss = *reinterpret_cast<SharedDq*>(smem + 6 * TILE);
+                 v_addr = k_addr + K_STAGES * TILE;
+  SharedDq& ss = *reinterpret_cast<SharedDq*>(smem + (2 + K_STAGES + V_STAGES) * TILE);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   WaitCtx wc{&ss.abort_flag, status};
   const int m_tile = prm.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
@@ -261,15 +273,18 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ss.qdo_full), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < K_STAGES; ++s) {
       mbar_init(smem_u32(&ss.k_full[s]), 1);
       mbar_init(smem_u32(&ss.k_empty[s]), 1);
+    }
+    for (int s = 0; s < V_STAGES; ++s) {
       mbar_init(smem_u32(&ss.v_full[s]), 1);
       mbar_init(smem_u32(&ss.v_empty[s]), 1);
-      mbar_init(smem_u32(&ss.s_full[s]), 1);
     }
+    mbar_init(smem_u32(&ss.s_full[0]), 1);
+    mbar_init(smem_u32(&ss.s_full[1]), 1);
     mbar_init(smem_u32(&ss.dp_full), 1);
-    mbar_init(smem_u32(&ss.ds_full), 128);
+    mbar_init(smem_u32(&ss.ds_full), 256);
     mbar_init(smem_u32(&ss.dq_done), 1);
     ss.abort_flag = 0;
     fence_barrier_init();
@@ -292,26 +307,36 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       mbar_expect_tx(smem_u32(&ss.qdo_full), 2 * TILE);
       load_tile<D>(q_addr, &map_q, smem_u32(&ss.qdo_full), m0, bh);
       load_tile<D>(do_addr, &map_do, smem_u32(&ss.qdo_full), m0, bh);
-      int issued = 0;
-      for (int j = 0; j < n_blocks; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&ss.k_empty[s]), ph ^ 1, wc, 31)) break;
+      // K runs up to two blocks ahead of V (its S MMA is issued two blocks early)
+      int k_issued = 0, v_issued = 0;
+      bool ok = true;
+      auto load_k = [&](int j) {
+        const int s = j % K_STAGES;
+        if (!mbar_wait(smem_u32(&ss.k_empty[s]), ((j / K_STAGES) & 1) ^ 1, wc, 31)) return false;
         mbar_expect_tx(smem_u32(&ss.k_full[s]), TILE);
         load_tile<D>(k_addr + s * TILE, &map_k, smem_u32(&ss.k_full[s]), j * BLK, bh);
-        if (!mbar_wait(smem_u32(&ss.v_empty[s]), ph ^ 1, wc, 32)) {
-          drain(smem_u32(&ss.k_full[s]), ph, wc, 39);
-          break;
-        }
+        ++k_issued;
+        return true;
+      };
+      auto load_v = [&](int j) {
+        const int s = j % V_STAGES;
+        if (!mbar_wait(smem_u32(&ss.v_empty[s]), ((j / V_STAGES) & 1) ^ 1, wc, 32)) return false;
         mbar_expect_tx(smem_u32(&ss.v_full[s]), TILE);
         load_tile<D>(v_addr + s * TILE, &map_v, smem_u32(&ss.v_full[s]), j * BLK, bh);
-        ++issued;
+        ++v_issued;
+        return true;
+      };
+      if (n_blocks > 0) ok = load_k(0) && load_v(0);
+      if (ok && n_blocks > 1) ok = load_k(1);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (j + 1 < n_blocks && !load_v(j + 1)) break;
+        if (j + 2 < n_blocks && !load_k(j + 2)) break;
       }
       drain(smem_u32(&ss.qdo_full), 0, wc, 39);
-      for (int j = max(0, issued - 2); j < issued; ++j) {
-        drain(smem_u32(&ss.k_full[j & 1]), (j >> 1) & 1, wc, 39);
-        drain(smem_u32(&ss.v_full[j & 1]), (j >> 1) & 1, wc, 39);
-      }
+      for (int j = max(0, k_issued - K_STAGES); j < k_issued; ++j)
+        drain(smem_u32(&ss.k_full[j % K_STAGES]), (j / K_STAGES) & 1, wc, 39);
+      for (int j = max(0, v_issued - V_STAGES); j < v_issued; ++j)
+        drain(smem_u32(&ss.v_full[j % V_STAGES]), (j / V_STAGES) & 1, wc, 39);
     }
   } else if (warp == 5) {
     if (lane == 0) {
@@ -319,37 +344,41 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       constexpr uint32_t idesc_tn = make_idesc(FMT, BLK, D, 0, 1);
       bool ok = mbar_wait(smem_u32(&ss.qdo_full), 0, wc, 33);
       auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(smem_u32(&ss.k_full[s]), (j >> 1) & 1, wc, 34)) return false;
+        const int s = j % K_STAGES;
+        if (!mbar_wait(smem_u32(&ss.k_full[s]), (j / K_STAGES) & 1, wc, 34)) return false;
         tc_fence_after();
-        mma_nt<D>(tmem + (s ? S_COL1 : S_COL0), q_addr, k_addr + s * TILE, idesc_nt);
-        mma_commit(smem_u32(&ss.s_full[s]));
+        mma_nt<D>(tmem + S_COL + (j & 1) * BLK, q_addr, k_addr + s * TILE, idesc_nt);
+        mma_commit(smem_u32(&ss.s_full[j & 1]));
         return true;
       };
       auto issue_dp = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(smem_u32(&ss.v_full[s]), (j >> 1) & 1, wc, 35)) return false;
+        const int s = j % V_STAGES;
+        if (!mbar_wait(smem_u32(&ss.v_full[s]), (j / V_STAGES) & 1, wc, 35)) return false;
         tc_fence_after();
         mma_nt<D>(tmem + DP_COL, do_addr, v_addr + s * TILE, idesc_nt);
         mma_commit(smem_u32(&ss.v_empty[s]));
         mma_commit(smem_u32(&ss.dp_full));
         return true;
       };
-      if (ok) ok = issue_qk(0) && issue_dp(0);
+      if (ok && n_blocks > 0) ok = issue_qk(0) && issue_dp(0);
+      if (ok && n_blocks > 1) ok = issue_qk(1);
       for (int j = 0; j < n_blocks && ok; ++j) {
-        if (j + 1 < n_blocks && !issue_qk(j + 1)) { ok = false; break; }
         if (!mbar_wait(smem_u32(&ss.ds_full), j & 1, wc, 36)) { ok = false; break; }
         tc_fence_after();
-        mma_tn<D>(tmem + DQ_COL, tmem + DP_COL, k_addr + (j & 1) * TILE, idesc_tn, j != 0);
-        mma_commit(smem_u32(&ss.k_empty[j & 1]));
-        if (j + 1 == n_blocks) mma_commit(smem_u32(&ss.dq_done));
+        // the element-wise pass of block j has read dP(j): the next dP may overwrite it
         if (j + 1 < n_blocks && !issue_dp(j + 1)) { ok = false; break; }
+        mma_tn<D>(tmem + DQ_COL, tmem + S_COL + (j & 1) * BLK, k_addr + (j % K_STAGES) * TILE, idesc_tn, j != 0);
+        mma_commit(smem_u32(&ss.k_empty[j % K_STAGES]));
+        if (j + 1 == n_blocks) mma_commit(smem_u32(&ss.dq_done));
+        // S(j+2) reuses the buffer dS(j) sits in: MMAs run in issue order
+        if (j + 2 < n_blocks && !issue_qk(j + 2)) { ok = false; break; }
       }
     }
   } else {
-    const int row_in_tile = warp * 32 + lane;
+    const int group = warp >= 6 ? 1 : 0;          // owns columns group*64 ... of every block
+    const int row_in_tile = (warp % 4) * 32 + lane;
     const int q_row = m0 + row_in_tile;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
     const float qk_scale = prm.sm_scale * kLog2e;
     float lse = 0.f, delta = 0.f;
     if (q_row < prm.n_ctx) {
@@ -358,44 +387,26 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
     bool ok = true;
     for (int j = 0; j < n_blocks && ok; ++j) {
-      const int s = j & 1;
-      if (!mbar_wait(smem_u32(&ss.s_full[s]), (j >> 1) & 1, wc, 37)) { ok = false; break; }
-      tc_fence_after();
-      const int n0 = j * BLK;
-      const bool boundary = (n0 + BLK > prm.n_ctx) || (prm.causal && n0 + BLK > m0);
+      if (!mbar_wait(smem_u32(&ss.s_full[j & 1]), (j >> 1) & 1, wc, 37)) { ok = false; break; }
       if (!mbar_wait(smem_u32(&ss.dp_full), j & 1, wc, 38)) { ok = false; break; }
       tc_fence_after();
+      const int n0 = j * BLK + group * HALF;
+      const bool boundary = (n0 + HALF > prm.n_ctx) || (prm.causal && n0 + HALF > m0);
       const KeyMask km{n0, q_row, prm.n_ctx, prm.causal};
-      const uint32_t s_tmem = tmem + lane_addr + (s ? S_COL1 : S_COL0);
-      // dS overwrites columns of dP that have already been read
-      if (boundary) ds_pass<T, true>(s_tmem, tmem + lane_addr + DP_COL, qk_scale, -lse, delta, km);
-      else ds_pass<T, false>(s_tmem, tmem + lane_addr + DP_COL, qk_scale, -lse, delta, km);
+      const uint32_t s_tmem = tmem + lane_addr + S_COL + (j & 1) * BLK + group * HALF;
+      const uint32_t dp_tmem = tmem + lane_addr + DP_COL + group * HALF;
+      if (boundary) ds_half<T, true>(s_tmem, dp_tmem, qk_scale, -lse, delta, km);
+      else ds_half<T, false>(s_tmem, dp_tmem, qk_scale, -lse, delta, km);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&ss.ds_full));
     }
-    if (ok) ok = mbar_wait(smem_u32(&ss.dq_done), 0, wc, 40);
+    if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&ss.dq_done), 0, wc, 40);
     tc_fence_after();
-    if (ok) {
-      const bool live = q_row < prm.rows;
-      T* orow = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem + lane_addr + DQ_COL + c * 32, r);
-        tmem_ld_wait();
-        if (live) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 out;
-            out.x = pack2<T>(__uint_as_float(r[v * 8 + 0]) * prm.sm_scale, __uint_as_float(r[v * 8 + 1]) * prm.sm_scale);
-            out.y = pack2<T>(__uint_as_float(r[v * 8 + 2]) * prm.sm_scale, __uint_as_float(r[v * 8 + 3]) * prm.sm_scale);
-            out.z = pack2<T>(__uint_as_float(r[v * 8 + 4]) * prm.sm_scale, __uint_as_float(r[v * 8 + 5]) * prm.sm_scale);
-            out.w = pack2<T>(__uint_as_float(r[v * 8 + 6]) * prm.sm_scale, __uint_as_float(r[v * 8 + 7]) * prm.sm_scale);
-            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = out;
-          }
-        }
-      }
+    if (ok && n_blocks > 0) {
+      // each group stores half of the columns of dQ
+      T* orow = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq + group * (D / 2);
+      store_rows<T, D / 2>(tmem + lane_addr + DQ_COL + group * (D / 2), orow, prm.sm_scale, q_row < prm.rows);
     }
   }
   tc_fence_before();
@@ -449,8 +460,8 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     mbar_init(smem_u32(&ss.st_full), 1);
     mbar_init(smem_u32(&ss.dpt_full), 1);
-    mbar_init(smem_u32(&ss.p_full), 128);
-    mbar_init(smem_u32(&ss.ds_full), 128);
+    mbar_init(smem_u32(&ss.p_full), 256);
+    mbar_init(smem_u32(&ss.ds_full), 256);
     mbar_init(smem_u32(&ss.done), 1);
     ss.abort_flag = 0;
     fence_barrier_init();
@@ -535,91 +546,68 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       }
     }
   } else {
-    const int row_in_tile = warp * 32 + lane;
+    const int group = warp >= 6 ? 1 : 0;          // owns query columns group*64 ... of every block
+    const int row_in_tile = (warp % 4) * 32 + lane;
     const int k_row = n0 + row_in_tile;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
     const float qk_scale = prm.sm_scale * kLog2e;
     const float* lse_base = prm.lse + (int64_t)bh * prm.stride_lse;
     const float* delta_base = prm.delta + (int64_t)bh * prm.stride_lse;
     // Row statistics of the streamed query block go through shared memory (every thread
-    // needs all 128 of them).  The global loads for block t+1 are issued at the top of
-    // iteration t into registers and only stored to shared memory at its end, so their
-    // latency is off the critical path.  +inf as L makes exp2(x - L) vanish for queries
-    // past the end.
-    auto fetch_stats = [&](int t, float& l, float& d) {
+    // needs 64 of them): the threads of group 0 fetch the 128 values of L, those of group 1
+    // the 128 values of Delta.  The global load for block t+1 is issued at the top of
+    // iteration t into a register and stored to shared memory at its end, so its latency is
+    // off the critical path.  +inf as L makes exp2(x - L) vanish for queries past the end.
+    auto fetch_stat = [&](int t) -> float {
       const int q = (first + t) * BLK + row_in_tile;
-      l = INFINITY;
-      d = 0.f;
+      float v = group ? 0.f : INFINITY;
       if (q < prm.n_ctx) {
-        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(l) : "l"(lse_base + q));
-        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(d) : "l"(delta_base + q));
+        const float* src = (group ? delta_base : lse_base) + q;
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(src));
       }
+      return v;
     };
-    if (n_iter > 0) {
-      float l, d;
-      fetch_stats(0, l, d);
-      ss.lse[0][row_in_tile] = l;
-      ss.delta[0][row_in_tile] = d;
-    }
+    auto put_stat = [&](int t, float v) {
+      if (group) ss.delta[t & 1][row_in_tile] = v;
+      else ss.lse[t & 1][row_in_tile] = v;
+    };
+    if (n_iter > 0) put_stat(0, fetch_stat(0));
     bool ok = true;
     for (int t = 0; t < n_iter && ok; ++t) {
-      // all 128 threads: statistics of block t are visible, block t-1 is no longer read
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      float next_l = INFINITY, next_d = 0.f;
-      if (t + 1 < n_iter) fetch_stats(t + 1, next_l, next_d);
-      const float* lse_s = ss.lse[t & 1];
-      const float* delta_s = ss.delta[t & 1];
-      const int q0 = (first + t) * BLK;
+      // all 256 threads: statistics of block t are visible, block t-1 is no longer read
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      float next_stat = 0.f;
+      if (t + 1 < n_iter) next_stat = fetch_stat(t + 1);
+      const float* lse_s = ss.lse[t & 1] + group * HALF;
+      const float* delta_s = ss.delta[t & 1] + group * HALF;
+      const int q0 = (first + t) * BLK + group * HALF;      // first query of this group's columns
       const bool diagonal = prm.causal && q0 < n0 + BLK;
       if (!mbar_wait(smem_u32(&ss.st_full), t & 1, wc, 58)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t st_tmem = tmem + lane_addr + ST_COL;
-      uint32_t keep[64];
-      if (diagonal) pt_pass<T, true>(st_tmem, qk_scale, lse_s, k_row - q0, keep);
-      else pt_pass<T, false>(st_tmem, qk_scale, lse_s, 0, keep);
+      const uint32_t st_tmem = tmem + lane_addr + ST_COL + group * HALF;
+      uint32_t keep[32];
+      if (diagonal) pt_half<T, true>(st_tmem, qk_scale, lse_s, k_row - q0, keep);
+      else pt_half<T, false>(st_tmem, qk_scale, lse_s, 0, keep);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&ss.p_full));
       if (!mbar_wait(smem_u32(&ss.dpt_full), t & 1, wc, 60)) { ok = false; break; }
       tc_fence_after();
-      dst_pass<T>(tmem + lane_addr + DPT_COL, delta_s, keep);
+      dst_half<T>(tmem + lane_addr + DPT_COL + group * HALF, delta_s, keep);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&ss.ds_full));
-      ss.lse[(t + 1) & 1][row_in_tile] = next_l;
-      ss.delta[(t + 1) & 1][row_in_tile] = next_d;
+      if (t + 1 < n_iter) put_stat(t + 1, next_stat);
     }
     if (ok && n_iter > 0) ok = mbar_wait(smem_u32(&ss.done), 0, wc, 61);
     tc_fence_after();
-    const bool live = k_row < prm.rows;
-    T* dk_row = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq;
-    T* dv_row = (T*)prm.out1 + (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq;
     if (ok && n_iter > 0) {
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const float scale = which ? prm.sm_scale : 1.f;
-        T* orow = which ? dk_row : dv_row;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem + lane_addr + (which ? DK_COL : DV_COL) + c * 32, r);
-          tmem_ld_wait();
-          if (live) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 out;
-              out.x = pack2<T>(__uint_as_float(r[v * 8 + 0]) * scale, __uint_as_float(r[v * 8 + 1]) * scale);
-              out.y = pack2<T>(__uint_as_float(r[v * 8 + 2]) * scale, __uint_as_float(r[v * 8 + 3]) * scale);
-              out.z = pack2<T>(__uint_as_float(r[v * 8 + 4]) * scale, __uint_as_float(r[v * 8 + 5]) * scale);
-              out.w = pack2<T>(__uint_as_float(r[v * 8 + 6]) * scale, __uint_as_float(r[v * 8 + 7]) * scale);
-              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = out;
-            }
-          }
-        }
-      }
-    } else if (ok && live) {
-      // no query attends to these keys (cannot happen with n_iter > 0 for live rows)
-      for (int d = 0; d < D; ++d) { dk_row[d] = T(0.f); dv_row[d] = T(0.f); }
+      // group 0 stores dV, group 1 stores dK
+      const bool live = k_row < prm.rows;
+      T* dk_row = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq;
+      T* dv_row = (T*)prm.out1 + (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq;
+      if (group == 0) store_rows<T, D>(tmem + lane_addr + DV_COL, dv_row, 1.f, live);
+      else store_rows<T, D>(tmem + lane_addr + DK_COL, dk_row, prm.sm_scale, live);
     }
   }
   tc_fence_before();
@@ -666,8 +654,9 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   if (!err.empty()) return err;
   Params prm = make_params(p);
   const char* what = dkdv ? "attn_bwd_dkdv" : "attn_bwd_dq";
-  // 6 tiles; never less than 120 KiB so two CTAs (each wanting all of TMEM) do not share an SM
-  size_t smem = 6 * (BLK * D * 2) + (dkdv ? sizeof(SharedDkdv) : sizeof(SharedDq)) + 1024;
+  // never less than 120 KiB so two CTAs (each wanting all of TMEM) do not share an SM
+  size_t smem = (dkdv ? 6 : 2 + K_STAGES + V_STAGES) * (size_t)(BLK * D * 2) +
+                (dkdv ? sizeof(SharedDkdv) : sizeof(SharedDq)) + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
   dim3 grid((unsigned)((p.rows + BLK - 1) / BLK), (unsigned)p.bh, 1);
   cudaError_t e;

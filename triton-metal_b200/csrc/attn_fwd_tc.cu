@@ -64,6 +64,7 @@ struct Params {
   float sm_scale;
   int64_t stride_head, stride_seq, stride_lse;
   int n_ctx, rows, causal;
+  long long* timing;   // optional cycle-count dump for tuning (null in normal use)
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -135,15 +136,17 @@ __device__ __forceinline__ float exp_chunk(const uint32_t (&r)[32], uint32_t dst
   float s0 = 0.f, s1 = 0.f;
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
-    float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), qk_scale, neg_m));
-    float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), qk_scale, neg_m));
-    if (MASKED) {
-      if (mi.masked(col0 + i)) p0 = 0.f;
-      if (mi.masked(col0 + i + 1)) p1 = 0.f;
+    {
+      float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), qk_scale, neg_m));
+      float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), qk_scale, neg_m));
+      if (MASKED) {
+        if (mi.masked(col0 + i)) p0 = 0.f;
+        if (mi.masked(col0 + i + 1)) p1 = 0.f;
+      }
+      s0 += p0;
+      s1 += p1;
+      packed[i / 2] = pack2<T>(p0, p1);
     }
-    s0 += p0;
-    s1 += p1;
-    packed[i / 2] = pack2<T>(p0, p1);
   }
   tmem_st_32x16(dst, packed);
   return s0 + s1;
@@ -346,14 +349,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int my_blocks = nb[t];
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
+    long long tw = 0, tmax = 0, texp = 0, tst = 0, tmark = clock64();
     for (int j = 0; j < my_blocks && ok; ++j) {
       if (!mbar_wait(smem_u32(&ss.s_full[t]), j & 1, wc, kSoftS)) { ok = false; break; }
       tc_fence_after();
+      { const long long now = clock64(); tw += now - tmark; tmark = now; }
       const int n0 = j * BLOCK_N;
       const bool boundary = (n0 + BLOCK_N > prm.n_ctx) || (prm.causal && n0 + BLOCK_N > m0 + t * BLOCK_M);
       const MaskInfo mi{n0, q_row, prm.n_ctx, prm.causal};
       // pass 1: row max of the raw scores (qk_scale > 0, so the scaled max is max * qk_scale)
       const float mx = (boundary ? max_pass<true>(s_tmem, mi) : max_pass<false>(s_tmem, mi)) * qk_scale;
+      { const long long now = clock64(); tmax += now - tmark; tmark = now; }
       // advance the working max only when it moved far (or on the first block)
       float alpha = 1.f;
       bool rescale = false;
@@ -381,9 +387,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       const float sum = boundary ? exp_pass<T, true>(s_tmem, qk_scale, -m_used, mi)
                                  : exp_pass<T, false>(s_tmem, qk_scale, -m_used, mi);
       l = l * alpha + sum;
+      { const long long now = clock64(); texp += now - tmark; tmark = now; }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&ss.p_full[t]));
+      { const long long now = clock64(); tst += now - tmark; tmark = now; }
+    }
+    if (prm.timing && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && lane == 0 && (warp % 4) == 0) {
+      long long* out = prm.timing + t * 8;
+      out[0] = tw; out[1] = tmax; out[2] = texp; out[3] = tst; out[4] = my_blocks;
     }
     // ---- epilogue: O / l and the row statistic
     if (ok && my_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done[t]), (my_blocks - 1) & 1, wc, kSoftFinal);
@@ -442,6 +454,11 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   prm.n_ctx = (int)p.n_ctx;
   prm.rows = (int)p.rows;
   prm.causal = p.causal;
+  static long long* timing_buf = nullptr;
+  if (std::getenv("TMCUDA_FWD_TIMING")) {
+    if (!timing_buf) cudaMallocManaged(&timing_buf, 16 * sizeof(long long));
+    prm.timing = timing_buf;
+  }
   // at least 120 KiB so that two CTAs (each wanting all 512 TMEM columns) never share an SM
   size_t smem = (TILES + 4) * (BLOCK_M * D * 2) + sizeof(Shared) + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
@@ -453,6 +470,13 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   ++*ctx.launches;
   e = cudaGetLastError();
   if (e != cudaSuccess) return std::string("attn_fwd launch failed: ") + cudaGetErrorString(e);
+  if (prm.timing) {
+    cudaStreamSynchronize(ctx.stream);
+    for (int t = 0; t < 2; ++t)
+      fprintf(stderr, "fwd timing tile %d: blocks %lld wait %lld max %lld exp %lld st+arrive %lld (cycles per block)\n", t,
+              timing_buf[t * 8 + 4], timing_buf[t * 8 + 0] / timing_buf[t * 8 + 4], timing_buf[t * 8 + 1] / timing_buf[t * 8 + 4],
+              timing_buf[t * 8 + 2] / timing_buf[t * 8 + 4], timing_buf[t * 8 + 3] / timing_buf[t * 8 + 4]);
+  }
   return std::string();
 }
 
