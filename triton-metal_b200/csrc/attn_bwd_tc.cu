@@ -153,6 +153,10 @@ __device__ __forceinline__ void ds_half(uint32_t s_tmem, uint32_t dp_tmem, float
 template <typename T, bool DIAG>
 __device__ __forceinline__ void pt_half(uint32_t st_tmem, float qk_scale, const float* lse_s, int k_minus_q0,
                                         uint32_t (&keep)[32]) {
+  // the statistics are read into registers before the TMEM loads are issued
+  float4 lv[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) lv[i] = *reinterpret_cast<const float4*>(lse_s + i * 4);
   uint32_t s0[32], s1[32];
   tmem_ld_32x32(st_tmem, s0);
   tmem_ld_32x32(st_tmem + 32, s1);
@@ -162,7 +166,7 @@ __device__ __forceinline__ void pt_half(uint32_t st_tmem, float qk_scale, const 
     const uint32_t(&s)[32] = h ? s1 : s0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
-      const float4 l = *reinterpret_cast<const float4*>(lse_s + h * 32 + i);
+      const float4 l = lv[h * 8 + i / 4];
       float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, -l.x));
       float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, -l.y));
       float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, -l.z));
@@ -184,6 +188,9 @@ __device__ __forceinline__ void pt_half(uint32_t st_tmem, float qk_scale, const 
 // dkdv pass B: dS^T = P^T * (dP^T - Delta[query]) from the register copy of P^T.
 template <typename T>
 __device__ __forceinline__ void dst_half(uint32_t dpt_tmem, const float* delta_s, const uint32_t (&keep)[32]) {
+  float4 dv[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) dv[i] = *reinterpret_cast<const float4*>(delta_s + i * 4);
   uint32_t d0[32], d1[32];
   tmem_ld_32x32(dpt_tmem, d0);
   tmem_ld_32x32(dpt_tmem + 32, d1);
@@ -194,7 +201,7 @@ __device__ __forceinline__ void dst_half(uint32_t dpt_tmem, const float* delta_s
     const uint32_t(&d)[32] = h ? d1 : d0;
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
-      const float4 dl = *reinterpret_cast<const float4*>(delta_s + h * 32 + i);
+      const float4 dl = dv[h * 8 + i / 4];
       float p0, p1, p2, p3;
       unpack2<T>(keep[h * 16 + i / 2], p0, p1);
       unpack2<T>(keep[h * 16 + i / 2 + 1], p2, p3);

@@ -9,18 +9,20 @@
 // One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that take
 // turns on the tensor core, so the exponentials of one tile overlap the MMAs of
 // the other:
-//   warps 0-3 / 4-7  softmax of tile 0 / tile 1, one thread per query row (the row
-//                    is that thread's TMEM lane: row max and row sum need no
-//                    cross-thread traffic).  Two passes over the score tile in
-//                    TMEM: max, then exp2 / sum / round, writing the 16-bit P
-//                    back over the scores it came from.
-//   warp 8           TMA: Q (both tiles) once, then K and V blocks of 128 keys
-//                    into 2-stage rings
-//   warp 9           MMA issuer: S_t = Q_t K^T (128x128xD, operands in shared
-//                    memory), O_t += P_t V (128xDx128, P read from TMEM)
+//   warps 0-15  softmax: tile t = warp / 8; inside a tile warps 0-3 own columns 0-63
+//               of every 128-column score block and warps 4-7 columns 64-127.  A thread
+//               owns one query row (its TMEM lane) and 64 columns: max over them, one
+//               exchange of the half-row maxima through shared memory, then exp2 /
+//               partial sum / round, writing the 16-bit P back over the scores it read.
+//   warp 16     TMA: Q (both tiles) once, then K and V blocks of 128 keys into
+//               2-stage rings
+//   warp 17     MMA issuer: S_t = Q_t K^T (128x128xD, operands in shared memory),
+//               O_t += P_t V (128xDx128, P read from TMEM)
 // The running max used for the exponentials only advances when it grew by more
 // than 8 (log2 units): P stays <= 256 and most iterations skip the O rescale in
-// TMEM; O/l at the end is exact either way.
+// TMEM; O/l at the end is exact either way.  The element-wise code is kept short
+// (64 columns per thread, no full unrolling over the row): straight-line code for a
+// whole row does not stay resident in the instruction cache and ran 1.6x slower.
 //
 // TMEM columns: S_0 | S_1 | O_0 | O_1.
 // HBM layout: Q, K, V, O [BH, S, D] with D contiguous (stride_seq == D),
@@ -40,7 +42,9 @@ using namespace ptx;
 
 constexpr int BLOCK_M = 128, BLOCK_N = 128;
 constexpr int TILES = 2;                       // query tiles per CTA
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 576;                // 16 softmax warps + TMA warp + MMA warp
+constexpr int LOAD_WARP = 16, MMA_WARP = 17;
+constexpr int HALF_N = BLOCK_N / 2;             // columns of a score tile owned by one softmax group
 constexpr int TMEM_COLS = 512;
 constexpr float kLog2e = 1.44269504088896340736f;
 constexpr float kRescaleThreshold = 8.0f;
@@ -54,6 +58,8 @@ struct Shared {
   alignas(8) uint64_t q_full;
   alignas(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   alignas(8) uint64_t s_full[TILES], p_full[TILES], pv_done[TILES];
+  float half_max[TILES][2][2][BLOCK_M];   // [tile][block parity][column half][row]
+  float half_sum[TILES][2][BLOCK_M];      // [tile][column half][row]
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -64,7 +70,6 @@ struct Params {
   float sm_scale;
   int64_t stride_head, stride_seq, stride_lse;
   int n_ctx, rows, causal;
-  long long* timing;   // optional cycle-count dump for tuning (null in normal use)
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -90,45 +95,25 @@ struct MaskInfo {
   }
 };
 
+// Row max of this thread's 64 columns (raw scores).
 template <bool MASKED>
-__device__ __forceinline__ float max_pass(uint32_t s_tmem, const MaskInfo& mi) {
+__device__ __forceinline__ float max_half(uint32_t s_tmem, const MaskInfo& mi) {
   uint32_t ra[32], rb[32];
-  float m0 = -INFINITY, m1 = -INFINITY;
   tmem_ld_32x32(s_tmem, ra);
-#pragma unroll 1
-  for (int c = 0; c < 4; c += 2) {
-    tmem_ld_wait();
-    tmem_ld_32x32(s_tmem + (c + 1) * 32, rb);
+  tmem_ld_32x32(s_tmem + 32, rb);
+  tmem_ld_wait();
+  float m0 = -INFINITY, m1 = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      const float a = __uint_as_float(ra[i]), b = __uint_as_float(ra[i + 1]);
-      if (MASKED) {
-        if (!mi.masked(c * 32 + i)) m0 = fmaxf(m0, a);
-        if (!mi.masked(c * 32 + i + 1)) m1 = fmaxf(m1, b);
-      } else {
-        m0 = fmaxf(m0, a);
-        m1 = fmaxf(m1, b);
-      }
-    }
-    tmem_ld_wait();
-    if (c + 2 < 4) tmem_ld_32x32(s_tmem + (c + 2) * 32, ra);
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      const float a = __uint_as_float(rb[i]), b = __uint_as_float(rb[i + 1]);
-      if (MASKED) {
-        if (!mi.masked((c + 1) * 32 + i)) m0 = fmaxf(m0, a);
-        if (!mi.masked((c + 1) * 32 + i + 1)) m1 = fmaxf(m1, b);
-      } else {
-        m0 = fmaxf(m0, a);
-        m1 = fmaxf(m1, b);
-      }
-    }
+  for (int i = 0; i < 32; ++i) {
+    if (!MASKED || !mi.masked(i)) m0 = fmaxf(m0, __uint_as_float(ra[i]));
+    if (!MASKED || !mi.masked(32 + i)) m1 = fmaxf(m1, __uint_as_float(rb[i]));
   }
   return fmaxf(m0, m1);
 }
 
-// P = exp2(s*qk_scale + neg_m), rounded to T and written back over the scores already
-// read (16 packed columns per 32 score columns); returns the fp32 row sum.
+// P = exp2(s*qk_scale + neg_m) for 32 columns, rounded to T and written to `dst` (16 packed
+// columns); returns the fp32 sum.  (Moving part of the exponentials to a polynomial on the
+// FMA pipe, and taking two at a time in the 16-bit type, were both measured slower here.)
 template <typename T, bool MASKED>
 __device__ __forceinline__ float exp_chunk(const uint32_t (&r)[32], uint32_t dst, float qk_scale,
                                            float neg_m, int col0, const MaskInfo& mi) {
@@ -136,37 +121,31 @@ __device__ __forceinline__ float exp_chunk(const uint32_t (&r)[32], uint32_t dst
   float s0 = 0.f, s1 = 0.f;
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
-    {
-      float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), qk_scale, neg_m));
-      float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), qk_scale, neg_m));
-      if (MASKED) {
-        if (mi.masked(col0 + i)) p0 = 0.f;
-        if (mi.masked(col0 + i + 1)) p1 = 0.f;
-      }
-      s0 += p0;
-      s1 += p1;
-      packed[i / 2] = pack2<T>(p0, p1);
+    const float x0 = fmaf(__uint_as_float(r[i]), qk_scale, neg_m);
+    const float x1 = fmaf(__uint_as_float(r[i + 1]), qk_scale, neg_m);
+    float p0 = fast_exp2(x0);
+    float p1 = fast_exp2(x1);
+    if (MASKED) {
+      if (mi.masked(col0 + i)) p0 = 0.f;
+      if (mi.masked(col0 + i + 1)) p1 = 0.f;
     }
+    s0 += p0;
+    s1 += p1;
+    packed[i / 2] = pack2<T>(p0, p1);
   }
   tmem_st_32x16(dst, packed);
   return s0 + s1;
 }
 
+// Exponentials of this thread's 64 columns; P goes back over the first 32 of them.
 template <typename T, bool MASKED>
-__device__ __forceinline__ float exp_pass(uint32_t s_tmem, float qk_scale, float neg_m,
-                                          const MaskInfo& mi) {
+__device__ __forceinline__ float exp_half(uint32_t s_tmem, float qk_scale, float neg_m, const MaskInfo& mi) {
   uint32_t ra[32], rb[32];
-  float sum = 0.f;
   tmem_ld_32x32(s_tmem, ra);
-#pragma unroll 1
-  for (int c = 0; c < 4; c += 2) {
-    tmem_ld_wait();
-    tmem_ld_32x32(s_tmem + (c + 1) * 32, rb);
-    sum += exp_chunk<T, MASKED>(ra, s_tmem + c * 16, qk_scale, neg_m, c * 32, mi);
-    tmem_ld_wait();
-    if (c + 2 < 4) tmem_ld_32x32(s_tmem + (c + 2) * 32, ra);
-    sum += exp_chunk<T, MASKED>(rb, s_tmem + (c + 1) * 16, qk_scale, neg_m, (c + 1) * 32, mi);
-  }
+  tmem_ld_32x32(s_tmem + 32, rb);
+  tmem_ld_wait();
+  float sum = exp_chunk<T, MASKED>(ra, s_tmem, qk_scale, neg_m, 0, mi);
+  sum += exp_chunk<T, MASKED>(rb, s_tmem + 16, qk_scale, neg_m, 32, mi);
   return sum;
 }
 
@@ -212,13 +191,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     for (int t = 0; t < TILES; ++t) {
       mbar_init(smem_u32(&ss.s_full[t]), 1);
-      mbar_init(smem_u32(&ss.p_full[t]), 128);
+      mbar_init(smem_u32(&ss.p_full[t]), 256);
       mbar_init(smem_u32(&ss.pv_done[t]), 1);
     }
     ss.abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 9) {
+  if (warp == MMA_WARP) {
     tmem_alloc(smem_u32(&ss.tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
@@ -227,7 +206,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem = ss.tmem_base;
 
-  if (warp == 8) {
+  if (warp == LOAD_WARP) {
     // ---------------------------------------------------------------- loads
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
@@ -280,7 +259,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == MMA_WARP) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(FMT, BLOCK_M, BLOCK_N, 0, 0);
@@ -320,9 +299,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const uint32_t vb = v_addr + s * TILE_BYTES;
 #pragma unroll
             for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-              // P: TMEM operand, 16 keys = 8 packed 32-bit columns of the score buffer.
+              // P: TMEM operand, 16 keys = 8 packed 32-bit columns; keys 0-63 sit at the start of
+              // the score buffer, keys 64-127 at its column 64 (one piece per softmax group).
               // V: MN-major, 16 keys = 2048 bytes further, 64-column halves HALF_BYTES apart.
-              mma_f16_ts(tmem + O_COL + t * D, tmem + S_COL + t * BLOCK_N + kk * 8,
+              mma_f16_ts(tmem + O_COL + t * D, tmem + S_COL + t * BLOCK_N + (kk / 4) * HALF_N + (kk % 4) * 8,
                          smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
             }
             mma_commit(smem_u32(&ss.pv_done[t]));
@@ -338,29 +318,37 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax, tile t
-    const int t = warp / 4;
+    // ---------------------------------------------------------------- softmax
+    // Tile t = warp / 8; within a tile, warps 0-3 own columns 0-63 of every score block and
+    // warps 4-7 columns 64-127.  The two threads that share a row exchange their half-row
+    // maxima through shared memory once per block and otherwise work independently (each
+    // keeps a partial row sum; the halves are added at the end).
+    const int t = warp / 8;
+    const int half = (warp / 4) & 1;
     const int row_in_tile = (warp % 4) * 32 + lane;
     const int q_row = m0 + t * BLOCK_M + row_in_tile;
     const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
-    const uint32_t s_tmem = tmem + lane_addr + S_COL + t * BLOCK_N;
-    const uint32_t o_tmem = tmem + lane_addr + O_COL + t * D;
+    const uint32_t s_tmem = tmem + lane_addr + S_COL + t * BLOCK_N + half * HALF_N;
+    const uint32_t o_tmem = tmem + lane_addr + O_COL + t * D + half * (D / 2);
     const float qk_scale = prm.sm_scale * kLog2e;
     const int my_blocks = nb[t];
+    const int pair_barrier = 1 + t;               // named barrier of the tile's 256 threads
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    long long tw = 0, tmax = 0, texp = 0, tst = 0, tmark = clock64();
     for (int j = 0; j < my_blocks && ok; ++j) {
       if (!mbar_wait(smem_u32(&ss.s_full[t]), j & 1, wc, kSoftS)) { ok = false; break; }
       tc_fence_after();
-      { const long long now = clock64(); tw += now - tmark; tmark = now; }
-      const int n0 = j * BLOCK_N;
-      const bool boundary = (n0 + BLOCK_N > prm.n_ctx) || (prm.causal && n0 + BLOCK_N > m0 + t * BLOCK_M);
+      const int n0 = j * BLOCK_N + half * HALF_N;
+      const bool boundary = (n0 + HALF_N > prm.n_ctx) || (prm.causal && n0 + HALF_N > m0 + t * BLOCK_M);
       const MaskInfo mi{n0, q_row, prm.n_ctx, prm.causal};
-      // pass 1: row max of the raw scores (qk_scale > 0, so the scaled max is max * qk_scale)
-      const float mx = (boundary ? max_pass<true>(s_tmem, mi) : max_pass<false>(s_tmem, mi)) * qk_scale;
-      { const long long now = clock64(); tmax += now - tmark; tmark = now; }
-      // advance the working max only when it moved far (or on the first block)
+      // pass 1: max of the raw scores over this half row, then over the whole row
+      // (qk_scale > 0, so the scaled max is max * qk_scale)
+      float mx = boundary ? max_half<true>(s_tmem, mi) : max_half<false>(s_tmem, mi);
+      ss.half_max[t][j & 1][half][row_in_tile] = mx;
+      asm volatile("bar.sync %0, 256;" ::"r"(pair_barrier) : "memory");
+      mx = fmaxf(mx, ss.half_max[t][j & 1][half ^ 1][row_in_tile]) * qk_scale;
+      // advance the working max only when it moved far (or on the first block); both threads
+      // of a row see the same numbers and take the same decision
       float alpha = 1.f;
       bool rescale = false;
       if (mx > m_used + kRescaleThreshold) {
@@ -369,11 +357,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         rescale = j > 0;
       }
       if (__any_sync(0xffffffffu, rescale)) {
-        // O_t may only be touched once the P.V MMA of block j-1 has finished
+        // O_t may only be touched once the P.V MMA of block j-1 has finished; each half
+        // rescales its own D/2 columns of the accumulator
         if (!mbar_wait(smem_u32(&ss.pv_done[t]), (j - 1) & 1, wc, kSoftPv)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < D / 64; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(o_tmem + c * 32, r);
           tmem_ld_wait();
@@ -383,29 +372,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         tmem_st_wait();
       }
-      // pass 2: exponentials, row sum, 16-bit P over the scores
-      const float sum = boundary ? exp_pass<T, true>(s_tmem, qk_scale, -m_used, mi)
-                                 : exp_pass<T, false>(s_tmem, qk_scale, -m_used, mi);
+      // pass 2: exponentials, partial row sum, 16-bit P over the scores already read
+      const float sum = boundary ? exp_half<T, true>(s_tmem, qk_scale, -m_used, mi)
+                                 : exp_half<T, false>(s_tmem, qk_scale, -m_used, mi);
       l = l * alpha + sum;
-      { const long long now = clock64(); texp += now - tmark; tmark = now; }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(smem_u32(&ss.p_full[t]));
-      { const long long now = clock64(); tst += now - tmark; tmark = now; }
     }
-    if (prm.timing && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && lane == 0 && (warp % 4) == 0) {
-      long long* out = prm.timing + t * 8;
-      out[0] = tw; out[1] = tmax; out[2] = texp; out[3] = tst; out[4] = my_blocks;
-    }
-    // ---- epilogue: O / l and the row statistic
+    // ---- epilogue: whole-row sum, O / l and the row statistic
+    ss.half_sum[t][half][row_in_tile] = l;
+    asm volatile("bar.sync %0, 256;" ::"r"(pair_barrier) : "memory");
+    l += ss.half_sum[t][half ^ 1][row_in_tile];
     if (ok && my_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done[t]), (my_blocks - 1) & 1, wc, kSoftFinal);
     tc_fence_after();
     if (ok && my_blocks > 0) {
       const float inv_l = 1.f / l;
       const bool live = q_row < prm.rows;
-      T* orow = (T*)prm.o + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      T* orow = (T*)prm.o + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq + half * (D / 2);
+#pragma unroll 1
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(o_tmem + c * 32, r);
         tmem_ld_wait();
@@ -421,13 +407,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
         }
       }
-      if (live && prm.lse) prm.lse[(int64_t)bh * prm.stride_lse + q_row] = m_used + log2f(l);
+      if (live && half == 0 && prm.lse) prm.lse[(int64_t)bh * prm.stride_lse + q_row] = m_used + log2f(l);
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -454,11 +440,6 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   prm.n_ctx = (int)p.n_ctx;
   prm.rows = (int)p.rows;
   prm.causal = p.causal;
-  static long long* timing_buf = nullptr;
-  if (std::getenv("TMCUDA_FWD_TIMING")) {
-    if (!timing_buf) cudaMallocManaged(&timing_buf, 16 * sizeof(long long));
-    prm.timing = timing_buf;
-  }
   // at least 120 KiB so that two CTAs (each wanting all 512 TMEM columns) never share an SM
   size_t smem = (TILES + 4) * (BLOCK_M * D * 2) + sizeof(Shared) + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
@@ -470,13 +451,6 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   ++*ctx.launches;
   e = cudaGetLastError();
   if (e != cudaSuccess) return std::string("attn_fwd launch failed: ") + cudaGetErrorString(e);
-  if (prm.timing) {
-    cudaStreamSynchronize(ctx.stream);
-    for (int t = 0; t < 2; ++t)
-      fprintf(stderr, "fwd timing tile %d: blocks %lld wait %lld max %lld exp %lld st+arrive %lld (cycles per block)\n", t,
-              timing_buf[t * 8 + 4], timing_buf[t * 8 + 0] / timing_buf[t * 8 + 4], timing_buf[t * 8 + 1] / timing_buf[t * 8 + 4],
-              timing_buf[t * 8 + 2] / timing_buf[t * 8 + 4], timing_buf[t * 8 + 3] / timing_buf[t * 8 + 4]);
-  }
   return std::string();
 }
 

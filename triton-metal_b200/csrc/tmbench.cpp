@@ -1,0 +1,535 @@
+// tmbench: the benchmark CLI of the hot path, over libtmcuda's C ABI only.
+//
+// Same job and flags as the reference's Sources/tmbench/main.swift:62-176 (--sizes,
+// --config, --attn, --attn-bwd, --attn-shapes, --attn-element, --no-verify, --probe,
+// --verbose), the same FLOP accounting (GEMMBenchmark.swift:449-451,
+// AttentionBenchmark.swift:66-68, AttentionBackwardBenchmark.swift:46-49), the same
+// closed-form inputs (GEMMBenchmark.swift:386-387, AttentionBackwardBenchmark.swift:489-491)
+// and the same timing method (dispatches packed to about 25 ms per sample, median of
+// three after a calibration run, best of two passes: GEMMBenchmark.swift:256-277, 414-421).
+// The MPS comparison columns are gone (no Metal here); a "% of peak" column against the
+// dense bf16 tensor-core figure given by --peak takes their place.  Added: --element
+// (f32|f16|bf16 for the GEMM sweep), --causal, --device.
+//
+// Each winning configuration is verified against a CPU reference before it is printed,
+// as the reference does; the CPU code here is a checker, never a fallback.
+
+#include "../../include/tm.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <sstream>
+#include <string>
+#include <vector>
+
+namespace {
+
+std::string last_error() {
+  char* e = tm_last_error();
+  std::string s = e ? e : "unknown";
+  tm_free(e);
+  return s;
+}
+
+[[noreturn]] void die(const std::string& what) {
+  std::fprintf(stderr, "tmbench: %s\n", what.c_str());
+  std::exit(1);
+}
+
+// ---- 16-bit storage helpers (host side, for uploads and verification) -----------
+uint16_t f32_to_bf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+float bf16_to_f32(uint16_t h) {
+  uint32_t u = (uint32_t)h << 16;
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+uint16_t f32_to_f16(float f) {
+  uint32_t x;
+  std::memcpy(&x, &f, 4);
+  const uint32_t sign = (x >> 16) & 0x8000u;
+  int32_t exp = (int32_t)((x >> 23) & 0xFF) - 127 + 15;
+  uint32_t man = x & 0x7FFFFFu;
+  if (exp <= 0) {
+    if (exp < -10) return (uint16_t)sign;
+    man |= 0x800000u;
+    const uint32_t shift = (uint32_t)(14 - exp);
+    uint32_t half = man >> shift;
+    const uint32_t rem = man & ((1u << shift) - 1), mid = 1u << (shift - 1);
+    if (rem > mid || (rem == mid && (half & 1))) half++;
+    return (uint16_t)(sign | half);
+  }
+  if (exp >= 31) return (uint16_t)(sign | 0x7C00u);
+  uint32_t half = ((uint32_t)exp << 10) | (man >> 13);
+  const uint32_t rem = man & 0x1FFFu;
+  if (rem > 0x1000u || (rem == 0x1000u && (half & 1))) half++;
+  return (uint16_t)(sign | half);
+}
+float f16_to_f32(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1F, man = h & 0x3FFu;
+  uint32_t u;
+  if (exp == 0) {
+    if (man == 0) u = sign;
+    else {
+      exp = 127 - 15 + 1;
+      while (!(man & 0x400u)) { man <<= 1; exp--; }
+      u = sign | (exp << 23) | ((man & 0x3FFu) << 13);
+    }
+  } else if (exp == 31) u = sign | 0x7F800000u | (man << 13);
+  else u = sign | ((exp + 127 - 15) << 23) | (man << 13);
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+
+struct Element {
+  std::string name;   // f32 | f16 | bf16
+  int size() const { return name == "f32" ? 4 : 2; }
+  float round(float v) const {
+    if (name == "bf16") return bf16_to_f32(f32_to_bf16(v));
+    if (name == "f16") return f16_to_f32(f32_to_f16(v));
+    return v;
+  }
+  std::vector<uint8_t> encode(const std::vector<float>& v) const {
+    std::vector<uint8_t> out(v.size() * size());
+    for (size_t i = 0; i < v.size(); ++i) {
+      if (name == "f32") std::memcpy(&out[i * 4], &v[i], 4);
+      else {
+        const uint16_t h = name == "bf16" ? f32_to_bf16(v[i]) : f32_to_f16(v[i]);
+        std::memcpy(&out[i * 2], &h, 2);
+      }
+    }
+    return out;
+  }
+  std::vector<float> decode(const std::vector<uint8_t>& raw) const {
+    std::vector<float> out(raw.size() / size());
+    for (size_t i = 0; i < out.size(); ++i) {
+      if (name == "f32") std::memcpy(&out[i], &raw[i * 4], 4);
+      else {
+        uint16_t h;
+        std::memcpy(&h, &raw[i * 2], 2);
+        out[i] = name == "bf16" ? bf16_to_f32(h) : f16_to_f32(h);
+      }
+    }
+    return out;
+  }
+};
+
+// ---- device objects over the ABI ------------------------------------------------
+struct Buffer {
+  int64_t handle = 0;
+  size_t bytes = 0;
+  explicit Buffer(size_t n) : bytes(n) {
+    handle = tm_alloc_buffer((int64_t)std::max<size_t>(n, 1));
+    if (!handle) die("tm_alloc_buffer: " + last_error());
+  }
+  Buffer(const Buffer&) = delete;
+  ~Buffer() { tm_free_buffer(handle); }
+  void write(const std::vector<uint8_t>& data) {
+    if (tm_buffer_write(handle, 0, data.data(), (int64_t)data.size()) != 0) die("tm_buffer_write: " + last_error());
+  }
+  std::vector<uint8_t> read(size_t n) const {
+    std::vector<uint8_t> out(n);
+    if (tm_buffer_read(handle, 0, out.data(), (int64_t)n) != 0) die("tm_buffer_read: " + last_error());
+    return out;
+  }
+};
+
+struct Kernel {
+  int64_t library = 0, handle = 0;
+  Kernel(const std::string& ir, const char* name, bool causal = false) {
+    char* text = tm_emit_msl(ir.c_str(), 4);
+    if (!text) die("tm_emit_msl: " + last_error());
+    library = tm_compile_msl(text);
+    tm_free(text);
+    if (!library) die("tm_compile_msl: " + last_error());
+    handle = tm_load_kernel(library, name);
+    if (!handle) die("tm_load_kernel: " + last_error());
+    if (causal && tmx_kernel_set_option(handle, "causal", 1) != 0) die("causal: " + last_error());
+  }
+  Kernel(const Kernel&) = delete;
+  ~Kernel() {
+    tm_release_kernel(handle);
+    tm_release_library(library);
+  }
+};
+
+struct Launch {
+  int64_t grid[3];
+  std::vector<int32_t> kinds;
+  std::vector<int64_t> values;
+  void buffer(const Buffer& b) { kinds.push_back(0); values.push_back(b.handle); }
+  void i32(int64_t v) { kinds.push_back(1); values.push_back(v); }
+  void f32(float v) {
+    uint32_t bits;
+    std::memcpy(&bits, &v, 4);
+    kinds.push_back(2);
+    values.push_back(bits);
+  }
+};
+
+void run_once(const Kernel& k, const Launch& l) {
+  if (tm_launch(k.handle, l.grid[0], l.grid[1], l.grid[2], 128, l.kinds.data(), l.values.data(),
+                (int32_t)l.kinds.size()) != 0)
+    die("tm_launch: " + last_error());
+}
+
+double time_batch(const std::vector<std::pair<const Kernel*, const Launch*>>& seq, int repeats) {
+  // all launches of `seq`, `repeats` times, between one pair of events per kernel
+  double total = 0;
+  for (auto& kl : seq) {
+    float ms = 0;
+    const Launch& l = *kl.second;
+    if (tmx_launch_timed(kl.first->handle, l.grid[0], l.grid[1], l.grid[2], 128, l.kinds.data(),
+                         l.values.data(), (int32_t)l.kinds.size(), repeats, &ms) != 0)
+      die("tmx_launch_timed: " + last_error());
+    total += ms;
+  }
+  return total / repeats;
+}
+
+// Calibrate, then median of three ~25 ms samples, best of two passes.  Milliseconds per run.
+double measure(const std::vector<std::pair<const Kernel*, const Launch*>>& seq) {
+  const double once = std::max(time_batch(seq, 1), 1e-4);
+  const int repeats = (int)std::min(2000.0, std::max(1.0, std::ceil(25.0 / once)));
+  double best = 1e30;
+  for (int pass = 0; pass < 2; ++pass) {
+    std::vector<double> samples;
+    for (int i = 0; i < 3; ++i) samples.push_back(time_batch(seq, repeats));
+    std::sort(samples.begin(), samples.end());
+    best = std::min(best, samples[1]);
+  }
+  return best;
+}
+
+// ---- signature-level Triton IR for the five entries ---------------------------------
+std::string matmul_ir(int bm, int bn, int bk, const std::string& e) {
+  std::ostringstream o;
+  o << "module {\n  tt.func public @matmul_kernel(%a_ptr: !tt.ptr<" << e << ">, %b_ptr: !tt.ptr<" << e
+    << ">, %c_ptr: !tt.ptr<" << e << ">, %M: i32, %N: i32, %K: i32, %stride_am: i32, %stride_ak: i32, "
+    << "%stride_bk: i32, %stride_bn: i32, %stride_cm: i32, %stride_cn: i32) {\n"
+    << "    %acc = tt.dot %a, %b, %z, inputPrecision = tf32 : tensor<" << bm << "x" << bk << "x" << e
+    << "> * tensor<" << bk << "x" << bn << "x" << e << "> -> tensor<" << bm << "x" << bn << "xf32>\n"
+    << "    tt.return\n  }\n}\n";
+  return o.str();
+}
+
+std::string attn_ir(const std::string& name, const std::string& args, int r0, int d, int r1,
+                    const std::string& e) {
+  std::string a = args;
+  for (size_t p; (p = a.find("{e}")) != std::string::npos;) a.replace(p, 3, e);
+  std::ostringstream o;
+  o << "module {\n  tt.func public @" << name << "(" << a << ") {\n";
+  if (r1 > 0)
+    o << "    %s = tt.dot %x, %y, %z : tensor<" << r0 << "x" << d << "x" << e << "> * tensor<" << d << "x"
+      << r1 << "x" << e << "> -> tensor<" << r0 << "x" << r1 << "xf32>\n";
+  else
+    o << "    %o = tt.load %p : tensor<" << r0 << "x" << d << "x" << e << ">\n";
+  o << "    tt.return\n  }\n}\n";
+  return o.str();
+}
+
+const char* kFwdArgs =
+    "%Q: !tt.ptr<{e}>, %K: !tt.ptr<{e}>, %V: !tt.ptr<{e}>, %O: !tt.ptr<{e}>, %L: !tt.ptr<f32>, "
+    "%sm_scale: f32, %stride_head: i32, %stride_seq: i32, %stride_lse: i32, %N_CTX: i32";
+const char* kPreArgs =
+    "%O: !tt.ptr<{e}>, %DO: !tt.ptr<{e}>, %Delta: !tt.ptr<f32>, %stride_head: i32, %stride_seq: i32, "
+    "%stride_lse: i32, %N_CTX: i32";
+const char* kDqArgs =
+    "%Q: !tt.ptr<{e}>, %K: !tt.ptr<{e}>, %V: !tt.ptr<{e}>, %DO: !tt.ptr<{e}>, %DQ: !tt.ptr<{e}>, "
+    "%L: !tt.ptr<f32>, %D: !tt.ptr<f32>, %sm_scale: f32, %stride_head: i32, %stride_seq: i32, "
+    "%stride_lse: i32, %N_CTX: i32";
+const char* kDkdvArgs =
+    "%Q: !tt.ptr<{e}>, %K: !tt.ptr<{e}>, %V: !tt.ptr<{e}>, %DO: !tt.ptr<{e}>, %DK: !tt.ptr<{e}>, "
+    "%DV: !tt.ptr<{e}>, %L: !tt.ptr<f32>, %D: !tt.ptr<f32>, %sm_scale: f32, %stride_head: i32, "
+    "%stride_seq: i32, %stride_lse: i32, %N_CTX: i32";
+
+std::string pad(const std::string& s, size_t w) { return s.size() >= w ? s : s + std::string(w - s.size(), ' '); }
+std::string fmt(const char* f, double v) {
+  char buf[64];
+  std::snprintf(buf, sizeof buf, f, v);
+  return buf;
+}
+
+struct Options {
+  std::vector<int> sizes{512, 1024, 2048};
+  std::vector<std::string> configs{"128,256,64,4"};
+  std::string element = "f32";
+  bool attention = false, attention_backward = false, verify = true, probe = false, verbose = false;
+  bool causal = false;
+  std::vector<std::vector<int>> shapes{{1, 8, 512, 64}, {1, 8, 1024, 64}, {1, 16, 2048, 64}};
+  std::string attn_element = "f32";
+  double peak_tflops = 0;
+};
+
+std::vector<float> closed_form(size_t n, int modulus, float scale, float shift) {
+  std::vector<float> v(n);
+  for (size_t i = 0; i < n; ++i) v[i] = (float)(i % modulus) * scale - shift;
+  return v;
+}
+std::vector<float> closed_form_tensor(size_t n, int seed) {
+  std::vector<float> v(n);
+  for (size_t i = 0; i < n; ++i) v[i] = (float)(i % seed) / (float)seed - 0.5f;
+  return v;
+}
+
+double max_rel_error(const std::vector<double>& want, const std::vector<float>& got) {
+  // |a-b| / max(1,|b|), the reference's assertClose metric (GPUHarness.swift:129-158)
+  double worst = 0;
+  for (size_t i = 0; i < want.size(); ++i)
+    worst = std::max(worst, std::fabs((double)got[i] - want[i]) / std::max(1.0, std::fabs(want[i])));
+  return worst;
+}
+
+// ---- GEMM sweep --------------------------------------------------------------------
+void run_gemm(const Options& opt) {
+  const Element el{opt.element};
+  std::printf("%s%s%s%s\n", pad("size", 8).c_str(), pad("best config", 25).c_str(),
+              pad("GFLOP/s", 18).c_str(), opt.peak_tflops > 0 ? "% of peak" : "");
+  for (int n : opt.sizes) {
+    std::vector<float> a = closed_form((size_t)n * n, 101, 0.01f, 0.5f);
+    std::vector<float> b = closed_form((size_t)n * n, 97, 0.01f, 0.5f);
+    for (auto& v : a) v = el.round(v);
+    for (auto& v : b) v = el.round(v);
+    Buffer ab((size_t)n * n * el.size()), bb((size_t)n * n * el.size()), cb((size_t)n * n * el.size());
+    ab.write(el.encode(a));
+    bb.write(el.encode(b));
+    double best_ms = 1e30;
+    std::string best_name;
+    for (const std::string& cfg : opt.configs) {
+      int bm = 128, bn = 256, bk = 64, w = 4;
+      std::sscanf(cfg.c_str(), "%d,%d,%d,%d", &bm, &bn, &bk, &w);
+      Kernel k(matmul_ir(bm, bn, bk, el.name), "matmul_kernel");
+      Launch l;
+      l.grid[0] = (n + bm - 1) / bm; l.grid[1] = (n + bn - 1) / bn; l.grid[2] = 1;
+      l.buffer(ab); l.buffer(bb); l.buffer(cb);
+      for (int v : {n, n, n, n, 1, n, 1, n, 1}) l.i32(v);
+      run_once(k, l);
+      const double ms = measure({{&k, &l}});
+      char name[64];
+      std::snprintf(name, sizeof name, "%dx%dx%d w%d", bm, bn, bk, w);
+      if (opt.verbose) std::printf("  %d  %s  %.1f GFLOP/s\n", n, name, 2.0 * n * n * n / ms / 1e6);
+      if (ms < best_ms) { best_ms = ms; best_name = name; }
+    }
+    if (opt.verify) {
+      // CPU reference in double on a band of rows (GEMMBenchmark.swift:325-375 checks the winner)
+      std::vector<float> c = el.decode(cb.read((size_t)n * n * el.size()));
+      const int rows = std::min(n, 16);
+      std::vector<double> want((size_t)rows * n);
+      std::vector<float> got((size_t)rows * n);
+      for (int r = 0; r < rows; ++r) {
+        const int row = (int)((long long)r * (n - 1) / std::max(1, rows - 1));
+        for (int j = 0; j < n; ++j) {
+          double acc = 0;
+          for (int kk = 0; kk < n; ++kk) acc += (double)a[(size_t)row * n + kk] * (double)b[(size_t)kk * n + j];
+          want[(size_t)r * n + j] = acc;
+          got[(size_t)r * n + j] = c[(size_t)row * n + j];
+        }
+      }
+      const double err = max_rel_error(want, got);
+      const double tol = el.name == "f32" ? 1e-4 : 2e-2;   // DotTests.swift tolerances, widened for K = n
+      if (!(err <= tol)) die("GEMM " + std::to_string(n) + " failed verification: error " + std::to_string(err));
+    }
+    const double gflops = 2.0 * n * n * n / best_ms / 1e6;
+    std::printf("%s%s%s%s\n", pad(std::to_string(n), 8).c_str(), pad(best_name, 25).c_str(),
+                pad(fmt("%.1f", gflops), 18).c_str(),
+                opt.peak_tflops > 0 ? fmt("%.0f%%", gflops / 10.0 / opt.peak_tflops).c_str() : "");
+  }
+}
+
+// ---- attention ------------------------------------------------------------------------
+// CPU reference in double for one (batch, head): O, L (log2 units), dQ, dK, dV
+// (the formulas of AttentionBackwardKernel.swift:11-18).
+struct HeadRef {
+  std::vector<double> o, lse, dq, dk, dv;
+};
+
+HeadRef reference_head(const float* q, const float* k, const float* v, const float* d_o, int S, int D,
+                       double scale, bool causal, bool backward) {
+  HeadRef r;
+  r.o.assign((size_t)S * D, 0);
+  r.lse.assign(S, 0);
+  if (backward) { r.dq.assign((size_t)S * D, 0); r.dk.assign((size_t)S * D, 0); r.dv.assign((size_t)S * D, 0); }
+  std::vector<double> p(S), dp(S);
+  for (int i = 0; i < S; ++i) {
+    const int lim = causal ? i + 1 : S;
+    double m = -1e300;
+    for (int j = 0; j < lim; ++j) {
+      double s = 0;
+      for (int d = 0; d < D; ++d) s += (double)q[(size_t)i * D + d] * k[(size_t)j * D + d];
+      p[j] = s * scale;
+      m = std::max(m, p[j]);
+    }
+    double l = 0;
+    for (int j = 0; j < lim; ++j) { p[j] = std::exp(p[j] - m); l += p[j]; }
+    for (int j = 0; j < lim; ++j) p[j] /= l;
+    r.lse[i] = (m + std::log(l)) * 1.4426950408889634;
+    for (int j = 0; j < lim; ++j)
+      for (int d = 0; d < D; ++d) r.o[(size_t)i * D + d] += p[j] * v[(size_t)j * D + d];
+    if (!backward) continue;
+    double delta = 0;
+    for (int j = 0; j < lim; ++j) {
+      double x = 0;
+      for (int d = 0; d < D; ++d) x += (double)d_o[(size_t)i * D + d] * v[(size_t)j * D + d];
+      dp[j] = x;
+      delta += x * p[j];
+    }
+    for (int j = 0; j < lim; ++j) {
+      const double ds = p[j] * (dp[j] - delta);
+      for (int d = 0; d < D; ++d) {
+        r.dq[(size_t)i * D + d] += ds * k[(size_t)j * D + d] * scale;
+        r.dk[(size_t)j * D + d] += ds * q[(size_t)i * D + d] * scale;
+        r.dv[(size_t)j * D + d] += p[j] * d_o[(size_t)i * D + d];
+      }
+    }
+  }
+  return r;
+}
+
+void check(const char* what, const std::vector<double>& want, const std::vector<float>& got, size_t offset,
+           double tol) {
+  std::vector<float> slice(got.begin() + offset, got.begin() + offset + want.size());
+  const double err = max_rel_error(want, slice);
+  if (!(err <= tol)) die(std::string(what) + " failed verification: error " + std::to_string(err));
+}
+
+void run_attention(const Options& opt, bool backward) {
+  const Element el{opt.attn_element};
+  std::printf("%s%s%s%s\n", pad("shape", 26).c_str(), pad("kernel", 16).c_str(), pad("GFLOP/s", 18).c_str(),
+              opt.peak_tflops > 0 ? "% of peak" : "");
+  for (const auto& shp : opt.shapes) {
+    const int B = shp[0], H = shp[1], S = shp[2], D = shp[3], BH = B * H;
+    const size_t n = (size_t)BH * S * D;
+    const float scale = 1.0f / std::sqrt((float)D);
+    // seeds 23 / 29 / 31 / 17 as in AttentionBackwardBenchmark.swift:428-432
+    std::vector<float> q = closed_form_tensor(n, 23), k = closed_form_tensor(n, 29),
+                       v = closed_form_tensor(n, 31), d_o = closed_form_tensor(n, 17);
+    for (auto* t : {&q, &k, &v, &d_o}) for (auto& x : *t) x = el.round(x);
+    Buffer qb(n * el.size()), kb(n * el.size()), vb(n * el.size()), ob(n * el.size()), dob(n * el.size());
+    Buffer dqb(n * el.size()), dkb(n * el.size()), dvb(n * el.size());
+    Buffer lb((size_t)BH * S * 4), deltab((size_t)BH * S * 4);
+    qb.write(el.encode(q)); kb.write(el.encode(k)); vb.write(el.encode(v)); dob.write(el.encode(d_o));
+    const int bm = 128, bn = 128;
+    Kernel fwd(attn_ir("attn_fwd", kFwdArgs, bm, D, bn, el.name), "attn_fwd", opt.causal);
+    Launch lf;
+    lf.grid[0] = (S + bm - 1) / bm; lf.grid[1] = BH; lf.grid[2] = 1;
+    lf.buffer(qb); lf.buffer(kb); lf.buffer(vb); lf.buffer(ob); lf.buffer(lb);
+    lf.f32(scale);
+    for (int x : {S * D, D, S, S}) lf.i32(x);
+    run_once(fwd, lf);
+    const double credit = (opt.causal ? 0.5 : 1.0) * (double)BH * S * (double)S * D;
+    char name[64];
+    std::snprintf(name, sizeof name, "b%d h%d s%d d%d%s", B, H, S, D, opt.causal ? " causal" : "");
+    const double tol = el.name == "f32" ? 2e-5 : 2e-2;
+    HeadRef ref;
+    if (opt.verify)
+      ref = reference_head(q.data(), k.data(), v.data(), d_o.data(), S, D, scale, opt.causal, backward);
+    if (!backward) {
+      const double ms = measure({{&fwd, &lf}});
+      if (opt.verify) check("attn_fwd O", ref.o, el.decode(ob.read(n * el.size())), 0, tol);
+      const double gflops = 4.0 * credit / ms / 1e6;
+      std::printf("%s%s%s%s\n", pad(name, 26).c_str(), pad("attn_fwd", 16).c_str(),
+                  pad(fmt("%.1f", gflops), 18).c_str(),
+                  opt.peak_tflops > 0 ? fmt("%.0f%%", gflops / 10.0 / opt.peak_tflops).c_str() : "");
+      continue;
+    }
+    Kernel pre(attn_ir("attn_bwd_preprocess", kPreArgs, bm, D, 0, el.name), "attn_bwd_preprocess");
+    Kernel dq(attn_ir("attn_bwd_dq", kDqArgs, bm, D, bn, el.name), "attn_bwd_dq", opt.causal);
+    Kernel dkdv(attn_ir("attn_bwd_dkdv", kDkdvArgs, bn, D, bm, el.name), "attn_bwd_dkdv", opt.causal);
+    Launch lp, lq, lk;
+    lp.grid[0] = lq.grid[0] = lk.grid[0] = (S + 127) / 128;
+    lp.grid[1] = lq.grid[1] = lk.grid[1] = BH;
+    lp.grid[2] = lq.grid[2] = lk.grid[2] = 1;
+    lp.buffer(ob); lp.buffer(dob); lp.buffer(deltab);
+    for (int x : {S * D, D, S, S}) lp.i32(x);
+    lq.buffer(qb); lq.buffer(kb); lq.buffer(vb); lq.buffer(dob); lq.buffer(dqb); lq.buffer(lb); lq.buffer(deltab);
+    lq.f32(scale);
+    for (int x : {S * D, D, S, S}) lq.i32(x);
+    lk.buffer(qb); lk.buffer(kb); lk.buffer(vb); lk.buffer(dob); lk.buffer(dkb); lk.buffer(dvb); lk.buffer(lb);
+    lk.buffer(deltab);
+    lk.f32(scale);
+    for (int x : {S * D, D, S, S}) lk.i32(x);
+    run_once(pre, lp); run_once(dq, lq); run_once(dkdv, lk);
+    const double ms = measure({{&pre, &lp}, {&dq, &lq}, {&dkdv, &lk}});
+    if (opt.verify) {
+      check("attn_bwd dQ", ref.dq, el.decode(dqb.read(n * el.size())), 0, tol * 5);
+      check("attn_bwd dK", ref.dk, el.decode(dkb.read(n * el.size())), 0, tol * 5);
+      check("attn_bwd dV", ref.dv, el.decode(dvb.read(n * el.size())), 0, tol * 5);
+    }
+    const double gflops = 10.0 * credit / ms / 1e6;
+    std::printf("%s%s%s%s\n", pad(name, 26).c_str(), pad("attn_bwd (3)", 16).c_str(),
+                pad(fmt("%.1f", gflops), 18).c_str(),
+                opt.peak_tflops > 0 ? fmt("%.0f%%", gflops / 10.0 / opt.peak_tflops).c_str() : "");
+  }
+}
+
+std::vector<std::string> split(const std::string& s, char sep) {
+  std::vector<std::string> out;
+  std::stringstream ss(s);
+  std::string item;
+  while (std::getline(ss, item, sep)) if (!item.empty()) out.push_back(item);
+  return out;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+  Options opt;
+  for (int i = 1; i < argc; ++i) {
+    const std::string a = argv[i];
+    auto next = [&]() -> std::string {
+      if (i + 1 >= argc) die("missing value after " + a);
+      return argv[++i];
+    };
+    if (a == "--sizes") { opt.sizes.clear(); for (auto& s : split(next(), ',')) opt.sizes.push_back(std::atoi(s.c_str())); }
+    else if (a == "--config") { opt.configs = split(next(), ';'); }
+    else if (a == "--element") opt.element = next();
+    else if (a == "--attn") opt.attention = true;
+    else if (a == "--attn-bwd") opt.attention_backward = true;
+    else if (a == "--attn-shapes") {
+      opt.shapes.clear();
+      for (auto& shape : split(next(), ';')) {
+        std::vector<int> dims;
+        for (auto& d : split(shape, ',')) dims.push_back(std::atoi(d.c_str()));
+        if (dims.size() != 4) die("--attn-shapes wants B,H,S,D[;B,H,S,D...]");
+        opt.shapes.push_back(dims);
+      }
+    }
+    else if (a == "--attn-element") opt.attn_element = next();
+    else if (a == "--causal") opt.causal = true;
+    else if (a == "--no-verify") opt.verify = false;
+    else if (a == "--probe") opt.probe = true;
+    else if (a == "--verbose" || a == "-v") opt.verbose = true;
+    else if (a == "--peak") opt.peak_tflops = std::atof(next().c_str());
+    else if (a == "--device") { if (tmx_set_device(std::atoi(next().c_str())) != 0) die(last_error()); }
+    else if (a == "--help" || a == "-h") {
+      std::printf("tmbench [--sizes 512,1024] [--config BM,BN,BK,W[;...]] [--element f32|f16|bf16]\n"
+                  "        [--attn | --attn-bwd] [--attn-shapes B,H,S,D[;...]] [--attn-element f32|f16|bf16]\n"
+                  "        [--causal] [--no-verify] [--probe] [--verbose] [--peak TFLOPS] [--device N]\n");
+      return 0;
+    } else die("unknown argument " + a);
+  }
+  char* name = tm_device_name();
+  std::printf("device: %s\n", name ? name : "none");
+  tm_free(name);
+  if (!tm_is_usable()) {
+    char* why = tm_unusable_reason();
+    std::printf("unusable: %s\n", why ? why : "?");
+    tm_free(why);
+    return opt.probe ? 0 : 1;
+  }
+  if (opt.probe) { std::printf("usable\n"); return 0; }
+  if (opt.attention) run_attention(opt, false);
+  else if (opt.attention_backward) run_attention(opt, true);
+  else run_gemm(opt);
+  return 0;
+}
