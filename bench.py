@@ -214,69 +214,107 @@ def pinned(array_like_bytes):
     return torch.empty(array_like_bytes, dtype=torch.uint8, pin_memory=True)
 
 
+def gemm_chunks(rows_per_rank):
+    """How many row blocks each rank's share of M is cut into so that the all-gather of one
+    block overlaps the GEMM of the next (at least 512 rows per block: a block should still
+    fill the 148 SMs with 128 x 256 tiles)."""
+    return max(1, min(4, rows_per_rank // 512))
+
+
 class GemmJob:
-    """Row block [row0, row0+rows) of C = A @ B on this rank; with more than one
-    rank an all-gather assembles the replicated C."""
+    """C = A @ B with row blocks of M dealt to the ranks block-cyclically: with `chunks`
+    blocks per rank, global block g = c * world + rank belongs to chunk c of `rank`.  Each
+    chunk is one kernel launch; with more than one rank its C block is all-gathered (NCCL,
+    enqueued in order on the library's stream) while the next chunk computes, and chunk c
+    of every rank lands contiguously in the replicated C."""
 
     def __init__(self, w, dist, seed=0):
         from triton_metal.synthetic import gemm_inputs_bf16
-        from triton_metal import _core, kernels
+        from triton_metal import _core, cuda, kernels
         self.w, self.dist, self.core = w, dist, _core
         M, N, K = w["M"], w["N"], w["K"]
-        self.row0, self.rows = shard(M, dist.rank, dist.world)
-        self.a_host, self.b_host = gemm_inputs_bf16(M, N, K, seed, self.row0, self.rows)
-        self.a = _core.alloc_buffer(max(2, self.a_host.nbytes))
+        if M % dist.world:
+            raise SystemExit("M must be a multiple of the number of ranks")
+        self.rows = M // dist.world
+        self.chunks = gemm_chunks(self.rows) if dist.world > 1 else 1
+        self.block = self.rows // self.chunks
+        self.a_host, self.b_host = [], None
+        for c in range(self.chunks):
+            row0 = (c * dist.world + dist.rank) * self.block
+            a, b = gemm_inputs_bf16(M, N, K, seed, row0, self.block)
+            self.a_host.append(a)
+            self.b_host = b
         self.b = _core.alloc_buffer(self.b_host.nbytes)
-        self.c_local = _core.alloc_buffer(max(2, self.rows * N * 2))
-        _core.buffer_write(self.a, 0, self.a_host.ctypes.data, self.a_host.nbytes)
         _core.buffer_write(self.b, 0, self.b_host.ctypes.data, self.b_host.nbytes)
+        self.a, self.c_local = [], []
+        for a in self.a_host:
+            handle = _core.alloc_buffer(a.nbytes)
+            _core.buffer_write(handle, 0, a.ctypes.data, a.nbytes)
+            self.a.append(handle)
+            # C lives in plain device memory: with more than one rank it is handed to NCCL
+            self.c_local.append(cuda.alloc_device_buffer(self.block * N * 2))
         self.kernel = kernels.Matmul("bf16", (128, 256, 64))
-        self.launches_per_step = 1
+        self.launches_per_step = self.chunks
 
     def prepare(self):
+        from triton_metal import cuda
         w = self.w
-        self.args = self.kernel.arguments(self.a, self.b, self.c_local, self.rows, w["N"], w["K"])
+        self.args = [self.kernel.arguments(a, self.b, c, self.block, w["N"], w["K"])
+                     for a, c in zip(self.a, self.c_local)]
         if self.dist.world > 1:
             torch = self.dist.torch
-            self.c_full = self.core.alloc_buffer(w["M"] * w["N"] * 2)
-            self.t_local = torch.as_tensor(
-                DeviceView(self.core.buffer_contents(self.c_local), (self.rows * w["N"],), "<i2"),
-                device="cuda")
-            self.t_full = torch.as_tensor(
-                DeviceView(self.core.buffer_contents(self.c_full), (w["M"] * w["N"],), "<i2"),
-                device="cuda")
+            self.stream = torch.cuda.ExternalStream(cuda.stream_handle())
+            self.c_full = cuda.alloc_device_buffer(w["M"] * w["N"] * 2)
+            full = torch.as_tensor(DeviceView(cuda.device_pointer(self.c_full), (w["M"] * w["N"],), "<i2"),
+                                   device="cuda").view(torch.bfloat16)
+            per_chunk = self.dist.world * self.block * w["N"]
+            self.t_out = [full[c * per_chunk:(c + 1) * per_chunk] for c in range(self.chunks)]
+            self.t_local = [torch.as_tensor(DeviceView(cuda.device_pointer(h), (self.block * w["N"],), "<i2"),
+                                            device="cuda").view(torch.bfloat16) for h in self.c_local]
 
     def step(self):
-        from triton_metal import cuda
-        self.kernel.launch_async(*self.args)
-        if self.dist.world > 1:
-            cuda.synchronize()
-            self.dist.dist.all_gather_into_tensor(self.t_full, self.t_local)
-            self.dist.torch.cuda.synchronize()
+        if self.dist.world == 1:
+            self.kernel.launch_async(*self.args[0])
+            return
+        torch, works = self.dist.torch, []
+        with torch.cuda.stream(self.stream):
+            for c in range(self.chunks):
+                self.kernel.launch_async(*self.args[c])
+                works.append(self.dist.dist.all_gather_into_tensor(self.t_out[c], self.t_local[c],
+                                                                   async_op=True))
+            for work in works:
+                work.wait()      # the library's stream waits; the host does not
 
     def e2e_setup(self):
-        a, b = self.a_host, self.b_host
-        self.pin_a, self.pin_b = pinned(a.nbytes), pinned(b.nbytes)
-        self.pin_a.numpy()[:] = a.reshape(-1).view(np.uint8)
+        b = self.b_host
+        self.pin_a = []
+        for a in self.a_host:
+            p = pinned(a.nbytes)
+            p.numpy()[:] = a.reshape(-1).view(np.uint8)
+            self.pin_a.append(p)
+        self.pin_b = pinned(b.nbytes)
         self.pin_b.numpy()[:] = b.reshape(-1).view(np.uint8)
-        self.pin_c = pinned(self.rows * self.w["N"] * 2)
-        return a.nbytes + b.nbytes, self.rows * self.w["N"] * 2
+        self.pin_c = [pinned(self.block * self.w["N"] * 2) for _ in range(self.chunks)]
+        return sum(a.nbytes for a in self.a_host) + b.nbytes, self.rows * self.w["N"] * 2
 
     def e2e_step(self):
         c = self.core
-        c.buffer_write(self.a, 0, self.pin_a.data_ptr(), self.pin_a.numel())
         c.buffer_write(self.b, 0, self.pin_b.data_ptr(), self.pin_b.numel())
-        self.kernel.launch(*self.args)
-        c.buffer_read(self.c_local, 0, self.pin_c.data_ptr(), self.pin_c.numel())
+        for i in range(self.chunks):
+            c.buffer_write(self.a[i], 0, self.pin_a[i].data_ptr(), self.pin_a[i].numel())
+            self.kernel.launch(*self.args[i])
+            c.buffer_read(self.c_local[i], 0, self.pin_c[i].data_ptr(), self.pin_c[i].numel())
 
-    def sample_output(self, rows):
+    def sample_rows(self, rows):
+        """(A rows as bf16 words, GPU result rows) of the first block, for the checker."""
+        rows = min(rows, self.block)
         got = np.empty((rows, self.w["N"]), dtype=np.uint16)
-        self.core.buffer_read(self.c_local, 0, got.ctypes.data, got.nbytes)
-        return got
+        self.core.buffer_read(self.c_local[0], 0, got.ctypes.data, got.nbytes)
+        return self.a_host[0][:rows], got
 
     def algorithmic_bytes(self):
         w = self.w
-        return 2.0 * (self.rows * w["K"] + w["K"] * w["N"] + self.rows * w["N"])
+        return 2.0 * (self.block * w["K"] + w["K"] * w["N"] + self.block * w["N"])
 
     def path(self):
         return self.kernel.last_path()
@@ -440,11 +478,12 @@ def cpu_baseline(name, job=None, budget_s=12.0):
     cores = os.cpu_count() or 1
     parity = None
     if w["kind"] == "gemm":
-        rows = min(w["M"], 2048) if job is None else min(job.rows, 2048)
+        rows = min(w["M"], 2048) if job is None else min(job.block, 2048)
+        got_bits = None
         if job is None:
             a_bits, b_bits = gemm_inputs_bf16(w["M"], w["N"], w["K"], 0, 0, rows)
         else:
-            a_bits, b_bits = job.a_host[:rows], job.b_host
+            (a_bits, got_bits), b_bits = job.sample_rows(rows), job.b_host
         a, b = from_bf16_bits(a_bits), from_bf16_bits(b_bits)
         want = ref.matmul(a, b)
         best, spent = float("inf"), 0.0
@@ -454,7 +493,7 @@ def cpu_baseline(name, job=None, budget_s=12.0):
             dt = time.perf_counter() - t0
             best, spent = min(best, dt), spent + dt
         if job is not None:
-            parity = ref.relative_error(from_bf16_bits(job.sample_output(rows)), want)
+            parity = ref.relative_error(from_bf16_bits(got_bits), want)
         value = 2.0 * rows * w["N"] * w["K"] / best / 1e12
         return dict(value=value, unit="TFLOP/s", cores=cores, kind="port", parity_error=parity,
                     sample=f"numpy float32 a@b on {rows} of {w['M']} rows of A (bf16-rounded "

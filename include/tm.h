@@ -146,6 +146,16 @@ int32_t tmx_timer_end(float *elapsed_ms);
 /* Count of kernels this library has launched since load (for launch accounting). */
 int64_t tmx_launch_count(void);
 
+/* A buffer of plain device memory (no host pointer: tm_buffer_contents fails on it), for
+ * buffers handed to other device-side libraries such as NCCL.  0 on failure. */
+int64_t tmx_alloc_device_buffer(int64_t nbytes);
+/* The library's stream as a cudaStream_t, for enqueuing other stream-ordered work (an NCCL
+ * collective, a torch op through an external-stream wrapper) in order with the launches.
+ * NULL on failure. */
+void *tmx_stream_handle(void);
+/* The device address of any buffer, for interop with libraries that take raw pointers. */
+void *tmx_buffer_device_pointer(int64_t buffer);
+
 /* fp32 C[M,N] = A[M,K] @ B[K,N] for callers that must not allocate device memory.
  * No counterpart in the reference.
  *

@@ -221,3 +221,29 @@ def test_fp32_large_k_against_float64_rows():
     rows = np.r_[0:16, 250:266, M - 16:M]
     want = a[rows].astype(np.float64) @ b.astype(np.float64)
     assert ref.relative_error(c[rows], want) <= 1e-5
+
+
+def test_device_only_buffers(core):
+    """tmx_alloc_device_buffer: plain device memory that kernels and copies use like any
+    other buffer, but that has no host pointer."""
+    n = 256
+    a, b = inputs.gemm_normal(n, n, n, seed=6)
+    a, b = ref.round_to(a, "bf16"), ref.round_to(b, "bf16")
+    ab, bb = tmtest.upload(a, "bf16"), tmtest.upload(b, "bf16")
+    c = cuda.alloc_device_buffer(n * n * 2)
+    from triton_metal import kernels
+    mm = kernels.Matmul("bf16")
+    try:
+        assert cuda.device_pointer(c) % 256 == 0
+        assert core.buffer_length(c) == n * n * 2
+        with pytest.raises(RuntimeError, match="device-only"):
+            core.buffer_contents(c)
+        mm(ab.tm_handle, bb.tm_handle, c, n, n, n)
+        out = np.empty((n, n), dtype=ref.storage_dtype("bf16"))
+        core.buffer_read(c, 0, out.ctypes.data, out.nbytes)
+        assert ref.relative_error(out.astype(np.float32), ref.matmul(a, b)) <= 2e-2
+    finally:
+        mm.release()
+        core.free_buffer(c)
+        ab.free()
+        bb.free()

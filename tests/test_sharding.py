@@ -31,11 +31,15 @@ def test_shard_partitions_exactly():
 
 
 def test_flop_accounting_matches_the_reference():
+    assert bench.gemm_chunks(4096) == 4 and bench.gemm_chunks(1024) == 2 and bench.gemm_chunks(8192) == 4
     assert bench.flops(bench.WORKLOADS["gemm_bf16_8192"]) == 2 * 8192 ** 3
     fwd = bench.WORKLOADS["attn_fwd_bf16_s4096_full"]
+    assert bench.gemm_chunks(4096) == 4 and bench.gemm_chunks(1024) == 2 and bench.gemm_chunks(8192) == 4
     assert bench.flops(fwd) == 4 * 4096 ** 2 * 128 * 128
+    assert bench.gemm_chunks(4096) == 4 and bench.gemm_chunks(1024) == 2 and bench.gemm_chunks(8192) == 4
     assert bench.flops(bench.WORKLOADS["attn_fwd_bf16_s4096"]) == bench.flops(fwd) / 2
     bwd = bench.WORKLOADS["attn_bwd_bf16_s4096_d128"]
+    assert bench.gemm_chunks(4096) == 4 and bench.gemm_chunks(1024) == 2 and bench.gemm_chunks(8192) == 4
     assert bench.flops(bwd) == 10 * 4096 ** 2 * 128 * 128 / 2
 
 

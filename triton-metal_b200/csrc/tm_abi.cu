@@ -72,6 +72,7 @@ struct BufferObj : Object {
   void* ptr = nullptr;
   int64_t length = 0;
   bool host_exposed = false;   // tm_buffer_contents handed the pointer to the host
+  bool device_only = false;    // plain device memory (tmx_alloc_device_buffer): no host pointer
   BufferObj() : Object(ObjKind::Buffer) {}
   ~BufferObj() override {
     if (ptr) cudaFree(ptr);
@@ -749,6 +750,11 @@ void* tm_buffer_contents(int64_t buffer) {
   std::string err;
   auto b = lookup_as<BufferObj>(buffer, ObjKind::Buffer, err);
   if (!b) { store_error(err); return nullptr; }
+  if (b->device_only) {
+    store_error(invalid_argument("buffer " + std::to_string(buffer) +
+                                 " is device-only memory and has no host-addressable contents"));
+    return nullptr;
+  }
   b->host_exposed = true;
   return b->ptr;
 }
@@ -914,6 +920,48 @@ int32_t tmx_timer_end(float* elapsed_ms) {
 }
 
 int64_t tmx_launch_count(void) { return g_dev.launches; }
+
+// Plain device memory (cudaMalloc), for buffers that are handed to other device-side
+// libraries (NCCL wants ordinary device allocations) and never read through a host pointer.
+int64_t tmx_alloc_device_buffer(int64_t nbytes) {
+  if (nbytes <= 0) {
+    store_error(invalid_argument("buffer length must be positive, got " + std::to_string(nbytes)));
+    return 0;
+  }
+  std::string err;
+  if (!bind_device(err)) { store_error(err); return 0; }
+  auto b = std::make_shared<BufferObj>();
+  cudaError_t e = cudaMalloc(&b->ptr, (size_t)nbytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    b->ptr = nullptr;
+    store_error(cuda_error("could not allocate a " + std::to_string(nbytes) + "-byte device buffer: " +
+                           cudaGetErrorString(e)));
+    return 0;
+  }
+  b->length = nbytes;
+  b->device_only = true;
+  cudaMemsetAsync(b->ptr, 0, (size_t)nbytes, g_dev.stream);
+  cudaStreamSynchronize(g_dev.stream);
+  return g_handles.insert(b);
+}
+
+// The library's CUDA stream (a cudaStream_t), so that other stream-ordered work (an NCCL
+// collective, a torch op) can be enqueued in order with the launches instead of behind a
+// host synchronisation.
+void* tmx_stream_handle(void) {
+  std::string err;
+  if (!bind_device(err)) { store_error(err); return nullptr; }
+  return (void*)g_dev.stream;
+}
+
+// The device address of a buffer (for interop with libraries that take raw pointers).
+void* tmx_buffer_device_pointer(int64_t buffer) {
+  std::string err;
+  auto b = lookup_as<BufferObj>(buffer, ObjKind::Buffer, err);
+  if (!b) { store_error(err); return nullptr; }
+  return b->ptr;
+}
 
 // fp32 C = A @ B with no device allocation anywhere on the path: the scratch for the
 // 3xTF32 operand split is a fixed array inside the library.  Same arithmetic as

@@ -27,6 +27,9 @@ EXPORTS = {
     "tmx_timer_begin": (_I32, ()),
     "tmx_timer_end": (_I32, (_F32P,)),
     "tmx_launch_count": (_I64, ()),
+    "tmx_alloc_device_buffer": (_I64, (_I64,)),
+    "tmx_buffer_device_pointer": (_PTR, (_I64,)),
+    "tmx_stream_handle": (_PTR, ()),
     "tmx_matmul_f32_static": (_I32, (_I64,) * 12),
     "tmx_matmul_f32_static_capacity": (_I64, ()),
 }
@@ -120,3 +123,23 @@ def matmul_f32_static(a, b, c, M, N, K, strides=None) -> None:
 
 def matmul_f32_static_capacity() -> int:
     return _lib.tmx_matmul_f32_static_capacity()
+
+
+def alloc_device_buffer(nbytes: int) -> int:
+    """A buffer of plain device memory (no host pointer); free it with _core.free_buffer."""
+    handle = _lib.tmx_alloc_device_buffer(nbytes)
+    if handle == 0:
+        raise RuntimeError(_core.last_error())
+    return handle
+
+
+def device_pointer(handle: int) -> int:
+    address = _lib.tmx_buffer_device_pointer(handle)
+    if not address:
+        raise RuntimeError(_core.last_error())
+    return address
+
+
+def stream_handle() -> int:
+    """The library's cudaStream_t as an integer (for torch.cuda.ExternalStream)."""
+    return _lib.tmx_stream_handle() or 0
