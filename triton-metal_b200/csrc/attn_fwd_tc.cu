@@ -6,16 +6,18 @@
 // (qk_scale = sm_scale*log2 e), P rounded to the element type before P.V,
 // O = acc / l, and the row statistic L = m + log2(l) in log2 units.
 //
-// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that take
-// turns on the tensor core, so the exponentials of one tile overlap the MMAs of
-// the other:
+// Persistent: one CTA per SM walks a list of query blocks (256 rows of one (batch, head)),
+// balanced under a causal mask by pairing a late block with an early one; the loads and
+// the first score MMAs of the next block run under the output pass of the current one.
+// A query block is two 128-row tiles that take turns on the tensor core, so the
+// exponentials of one tile overlap the MMAs of the other:
 //   warps 0-15  softmax: tile t = warp / 8; inside a tile warps 0-3 own columns 0-63
 //               of every 128-column score block and warps 4-7 columns 64-127.  A thread
 //               owns one query row (its TMEM lane) and 64 columns: max over them, one
 //               exchange of the half-row maxima through shared memory, then exp2 /
 //               partial sum / round, writing the 16-bit P back over the scores it read.
-//   warp 16     TMA: Q (both tiles) once, then K and V blocks of 128 keys into
-//               2-stage rings
+//   warp 16     TMA: Q (both tiles) once per query block, then K and V blocks of 128
+//               keys into 2-stage rings
 //   warp 17     MMA issuer: S_t = Q_t K^T (128x128xD, operands in shared memory),
 //               O_t += P_t V (128xDx128, P read from TMEM)
 // The running max used for the exponentials only advances when it grew by more
@@ -50,12 +52,12 @@ constexpr float kLog2e = 1.44269504088896340736f;
 constexpr float kRescaleThreshold = 8.0f;
 
 enum Site : uint32_t {
-  kLoadKEmpty = 11, kLoadVEmpty = 12, kMmaQ = 13, kMmaK = 14, kMmaV = 15, kMmaP = 16,
+  kLoadQEmpty = 10, kLoadKEmpty = 11, kLoadVEmpty = 12, kMmaQ = 13, kMmaK = 14, kMmaV = 15, kMmaP = 16,
   kSoftS = 17, kSoftPv = 18, kSoftFinal = 19, kDrainLoad = 20
 };
 
 struct Shared {
-  alignas(8) uint64_t q_full;
+  alignas(8) uint64_t q_full, q_empty;
   alignas(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   alignas(8) uint64_t s_full[TILES], p_full[TILES], pv_done[TILES];
   float half_max[TILES][2][2][BLOCK_M];   // [tile][block parity][column half][row]
@@ -151,10 +153,35 @@ __device__ __forceinline__ float exp_half(uint32_t s_tmem, float qk_scale, float
   return sum;
 }
 
+// ---- persistent schedule -------------------------------------------------------------
+// A CTA walks work units u = blockIdx.x, blockIdx.x + gridDim.x, ...  A unit is one (batch,
+// head) and one or two 256-row query blocks.  Under a causal mask block i walks i+1 key
+// blocks of 256, so a unit pairs block k with block n-1-k: every unit then costs the same
+// and the CTAs finish together.  Units of one head are adjacent, so the CTAs that run side
+// by side share that head's K and V in L2.
+struct Schedule {
+  int blocks;          // 256-row query blocks per head
+  int units_per_head;
+  int total_units;
+  int causal;
+  __device__ __forceinline__ int subs(int u) const {
+    if (!causal) return 1;
+    const int k = u % units_per_head;
+    return (blocks - 1 - k != k) ? 2 : 1;
+  }
+  __device__ __forceinline__ int head(int u) const { return u / units_per_head; }
+  // heavy block first
+  __device__ __forceinline__ int block(int u, int sub) const {
+    const int k = u % units_per_head;
+    if (!causal) return k;
+    return sub == 0 ? blocks - 1 - k : k;
+  }
+};
+
 template <typename T, int D, uint32_t FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, Params prm, DeviceStatus* status) {
+                   const __grid_constant__ CUtensorMap map_v, Params prm, Schedule sch, DeviceStatus* status) {
   constexpr int HALVES = D / 64;                        // 64-column swizzle atoms per row
   constexpr int TILE_BYTES = BLOCK_M * D * 2;           // one 128-row tile of Q, K or V
   constexpr int HALF_BYTES = BLOCK_M * 128;             // one [128 x 64] swizzled box
@@ -169,22 +196,17 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   WaitCtx wc{&ss.abort_flag, status};
 
-  // heavy (late) query tiles first under a causal mask
-  const int m_pair = prm.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-  const int bh = blockIdx.y;
-  const int m0 = m_pair * (TILES * BLOCK_M);
-  // key blocks each tile walks: everything, or up to its own diagonal
-  int nb[TILES];
-#pragma unroll
-  for (int t = 0; t < TILES; ++t) {
+  // key blocks tile t of the query block starting at row m0 walks: everything, or up to
+  // its own diagonal
+  auto key_blocks = [&](int m0, int t) {
     int key_end = prm.n_ctx;
     if (prm.causal) key_end = min(prm.n_ctx, m0 + (t + 1) * BLOCK_M);
-    nb[t] = (key_end + BLOCK_N - 1) / BLOCK_N;
-  }
-  const int nb_max = nb[TILES - 1];                     // later rows see at least as many keys
+    return (key_end + BLOCK_N - 1) / BLOCK_N;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ss.q_full), 1);
+    mbar_init(smem_u32(&ss.q_empty), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&ss.k_full[s]), 1);
       mbar_init(smem_u32(&ss.k_empty[s]), 1);
@@ -208,68 +230,71 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem = ss.tmem_base;
 
+  // All three roles walk the same sequence of query blocks.  Barrier phases follow running
+  // counters that never reset: `item` counts query blocks, `g` key blocks through the K/V
+  // rings, `c` score blocks of one tile.
   if (warp == LOAD_WARP) {
     // ---------------------------------------------------------------- loads
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
-      mbar_expect_tx(smem_u32(&ss.q_full), TILES * TILE_BYTES);
+      uint32_t item = 0, g = 0, q_loads = 0, k_loads = 0, v_loads = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
+        const int bh = sch.head(u);
+        for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
+          const int m0 = sch.block(u, sub) * (TILES * BLOCK_M);
+          const int nb_max = key_blocks(m0, TILES - 1);
+          // Q is single-buffered: the previous block's last score MMA must have retired
+          if (!mbar_wait(smem_u32(&ss.q_empty), (item & 1) ^ 1, wc, kLoadQEmpty)) { ok = false; break; }
+          mbar_expect_tx(smem_u32(&ss.q_full), TILES * TILE_BYTES);
 #pragma unroll
-      for (int t = 0; t < TILES; ++t)
+          for (int t = 0; t < TILES; ++t)
 #pragma unroll
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_3d(q_addr + t * TILE_BYTES + h * HALF_BYTES, &map_q, smem_u32(&ss.q_full), h * 64,
-                      m0 + t * BLOCK_M, bh);
-      int issued = 0;
-      for (int j = 0; j < nb_max; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&ss.k_empty[s]), ph ^ 1, wc, kLoadKEmpty)) break;
-        mbar_expect_tx(smem_u32(&ss.k_full[s]), TILE_BYTES);
+            for (int h = 0; h < HALVES; ++h)
+              tma_load_3d(q_addr + t * TILE_BYTES + h * HALF_BYTES, &map_q, smem_u32(&ss.q_full), h * 64,
+                          m0 + t * BLOCK_M, bh);
+          q_loads = item + 1;
+          for (int j = 0; j < nb_max; ++j, ++g) {
+            const int s = g & 1;
+            const uint32_t ph = (g >> 1) & 1;
+            if (!mbar_wait(smem_u32(&ss.k_empty[s]), ph ^ 1, wc, kLoadKEmpty)) { ok = false; break; }
+            mbar_expect_tx(smem_u32(&ss.k_full[s]), TILE_BYTES);
 #pragma unroll
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_3d(k_addr + s * TILE_BYTES + h * HALF_BYTES, &map_k, smem_u32(&ss.k_full[s]), h * 64,
-                      j * BLOCK_N, bh);
-        if (!mbar_wait(smem_u32(&ss.v_empty[s]), ph ^ 1, wc, kLoadVEmpty)) {
-          const long long t1 = clock64();
-          while (!mbar_try_wait(smem_u32(&ss.k_full[s]), ph)) {
-            if (clock64() - t1 > kWaitCycles) { report_timeout(wc, kDrainLoad, j + 1); break; }
+            for (int h = 0; h < HALVES; ++h)
+              tma_load_3d(k_addr + s * TILE_BYTES + h * HALF_BYTES, &map_k, smem_u32(&ss.k_full[s]), h * 64,
+                          j * BLOCK_N, bh);
+            k_loads = g + 1;
+            if (!mbar_wait(smem_u32(&ss.v_empty[s]), ph ^ 1, wc, kLoadVEmpty)) { ok = false; break; }
+            mbar_expect_tx(smem_u32(&ss.v_full[s]), TILE_BYTES);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+              tma_load_3d(v_addr + s * TILE_BYTES + h * HALF_BYTES, &map_v, smem_u32(&ss.v_full[s]), h * 64,
+                          j * BLOCK_N, bh);
+            v_loads = g + 1;
           }
-          break;
         }
-        mbar_expect_tx(smem_u32(&ss.v_full[s]), TILE_BYTES);
-#pragma unroll
-        for (int h = 0; h < HALVES; ++h)
-          tma_load_3d(v_addr + s * TILE_BYTES + h * HALF_BYTES, &map_v, smem_u32(&ss.v_full[s]), h * 64,
-                      j * BLOCK_N, bh);
-        ++issued;
       }
       // every copy started here must have landed before the CTA exits
-      {
+      auto drain = [&](uint64_t* bar, uint32_t parity, uint32_t info) {
         const long long t0 = clock64();
-        while (!mbar_try_wait(smem_u32(&ss.q_full), 0)) {
-          if (clock64() - t0 > kWaitCycles) { report_timeout(wc, kDrainLoad, 0); break; }
+        while (!mbar_try_wait(smem_u32(bar), parity)) {
+          if (clock64() - t0 > kWaitCycles) { report_timeout(wc, kDrainLoad, info); break; }
         }
-        for (int j = max(0, issued - 2); j < issued; ++j) {
-          const int s = j & 1;
-          const uint32_t ph = (j >> 1) & 1;
-          const long long t1 = clock64();
-          while (!(mbar_try_wait(smem_u32(&ss.k_full[s]), ph) && mbar_try_wait(smem_u32(&ss.v_full[s]), ph))) {
-            if (clock64() - t1 > kWaitCycles) { report_timeout(wc, kDrainLoad, j + 1); break; }
-          }
-        }
-      }
+      };
+      if (q_loads) drain(&ss.q_full, (q_loads - 1) & 1, 0);
+      for (uint32_t n = k_loads > 2 ? k_loads - 2 : 0; n < k_loads; ++n) drain(&ss.k_full[n & 1], (n >> 1) & 1, 1);
+      for (uint32_t n = v_loads > 2 ? v_loads - 2 : 0; n < v_loads; ++n) drain(&ss.v_full[n & 1], (n >> 1) & 1, 2);
     }
   } else if (warp == MMA_WARP) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(FMT, BLOCK_M, BLOCK_N, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc(FMT, BLOCK_M, D, 0, 1);
-      bool ok = mbar_wait(smem_u32(&ss.q_full), 0, wc, kMmaQ);
-      // S_t(j) = Q_t K(j)^T.  The caller has made sure K(j) has landed.
-      auto issue_qk = [&](int t, int j) {
-        const uint32_t kb = k_addr + (j & 1) * TILE_BYTES;
+      // S_t = Q_t K^T with K in ring stage `stage`.  The caller has made sure K has landed.
+      auto issue_qk = [&](int t, int stage) {
+        const uint32_t kb = k_addr + stage * TILE_BYTES;
         const uint32_t qb = q_addr + t * TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -279,44 +304,63 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         mma_commit(smem_u32(&ss.s_full[t]));
       };
-      if (ok) ok = mbar_wait(smem_u32(&ss.k_full[0]), 0, wc, kMmaK);
-      if (ok) {
-        tc_fence_after();
+      uint32_t item = 0, g = 0, c[TILES] = {0, 0};
+      bool ok = true;
+      for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
+        for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
+          const int m0 = sch.block(u, sub) * (TILES * BLOCK_M);
+          int nb[TILES];
 #pragma unroll
-        for (int t = 0; t < TILES; ++t) issue_qk(t, 0);
-        mma_commit(smem_u32(&ss.k_empty[0]));      // K(0) is free once both S(0) retire
-      }
-      for (int j = 0; j < nb_max && ok; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(smem_u32(&ss.v_full[s]), (j >> 1) & 1, wc, kMmaV)) { ok = false; break; }
-        if (j + 1 < nb_max && !mbar_wait(smem_u32(&ss.k_full[s ^ 1]), ((j + 1) >> 1) & 1, wc, kMmaK)) {
-          ok = false;
-          break;
-        }
+          for (int t = 0; t < TILES; ++t) nb[t] = key_blocks(m0, t);
+          const int nb_max = nb[TILES - 1];               // later rows see at least as many keys
+          if (!mbar_wait(smem_u32(&ss.q_full), item & 1, wc, kMmaQ)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&ss.k_full[g & 1]), (g >> 1) & 1, wc, kMmaK)) { ok = false; break; }
+          tc_fence_after();
+          // The first scores of this query block go over the last P of the previous one, and
+          // its first P.V starts a fresh O: MMAs run in issue order, and the softmax threads
+          // hand over P(0) only after they have read the previous O out of TMEM.
 #pragma unroll
-        for (int t = 0; t < TILES; ++t) {
-          if (j < nb[t]) {
-            if (!mbar_wait(smem_u32(&ss.p_full[t]), j & 1, wc, kMmaP)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t vb = v_addr + s * TILE_BYTES;
-#pragma unroll
-            for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-              // P: TMEM operand, 16 keys = 8 packed 32-bit columns; keys 0-63 sit at the start of
-              // the score buffer, keys 64-127 at its column 64 (one piece per softmax group).
-              // V: MN-major, 16 keys = 2048 bytes further, 64-column halves HALF_BYTES apart.
-              mma_f16_ts(tmem + O_COL + t * D, tmem + S_COL + t * BLOCK_N + (kk / 4) * HALF_N + (kk % 4) * 8,
-                         smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
+          for (int t = 0; t < TILES; ++t) issue_qk(t, g & 1);
+          mma_commit(smem_u32(&ss.k_empty[g & 1]));      // K(0) is free once both S(0) retire
+          if (nb_max == 1) mma_commit(smem_u32(&ss.q_empty));
+          for (int j = 0; j < nb_max && ok; ++j, ++g) {
+            const int s = g & 1;
+            if (!mbar_wait(smem_u32(&ss.v_full[s]), (g >> 1) & 1, wc, kMmaV)) { ok = false; break; }
+            if (j + 1 < nb_max && !mbar_wait(smem_u32(&ss.k_full[s ^ 1]), ((g + 1) >> 1) & 1, wc, kMmaK)) {
+              ok = false;
+              break;
             }
-            mma_commit(smem_u32(&ss.pv_done[t]));
+#pragma unroll
+            for (int t = 0; t < TILES; ++t) {
+              if (j < nb[t]) {
+                if (!mbar_wait(smem_u32(&ss.p_full[t]), c[t] & 1, wc, kMmaP)) { ok = false; break; }
+                ++c[t];
+                tc_fence_after();
+                const uint32_t vb = v_addr + s * TILE_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
+                  // P: TMEM operand, 16 keys = 8 packed 32-bit columns; keys 0-63 sit at the start
+                  // of the score buffer, keys 64-127 at its column 64 (one piece per softmax group).
+                  // V: MN-major, 16 keys = 2048 bytes further, 64-column halves HALF_BYTES apart.
+                  mma_f16_ts(tmem + O_COL + t * D,
+                             tmem + S_COL + t * BLOCK_N + (kk / 4) * HALF_N + (kk % 4) * 8,
+                             smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
+                }
+                mma_commit(smem_u32(&ss.pv_done[t]));
+              }
+              // V(j) has been read by both tiles: release it as early as possible
+              if (t == TILES - 1) mma_commit(smem_u32(&ss.v_empty[s]));
+              // the next scores of this tile overwrite its P: MMAs run in issue order
+              if (j + 1 < nb[t]) issue_qk(t, s ^ 1);
+              if (t == TILES - 1 && j + 1 < nb_max) {
+                // the last tile always walks every block: K(j+1) is free once its S retires,
+                // and after the last block's scores so is Q
+                mma_commit(smem_u32(&ss.k_empty[s ^ 1]));
+                if (j + 2 == nb_max) mma_commit(smem_u32(&ss.q_empty));
+              }
+            }
           }
-          // V(j) has been read by both tiles: release it as early as possible
-          if (t == TILES - 1) mma_commit(smem_u32(&ss.v_empty[s]));
-          // the next scores of this tile overwrite its P: MMAs run in issue order
-          if (j + 1 < nb[t]) issue_qk(t, j + 1);
-          // the last tile always walks every block: K(j+1) is free once its S retires
-          if (t == TILES - 1 && j + 1 < nb_max) mma_commit(smem_u32(&ss.k_empty[s ^ 1]));
         }
-        if (!ok) break;
       }
     }
   } else {
@@ -328,88 +372,95 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int t = warp / 8;
     const int half = (warp / 4) & 1;
     const int row_in_tile = (warp % 4) * 32 + lane;
-    const int q_row = m0 + t * BLOCK_M + row_in_tile;
     const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
     const uint32_t s_tmem = tmem + lane_addr + S_COL + t * BLOCK_N + half * HALF_N;
     const uint32_t o_tmem = tmem + lane_addr + O_COL + t * D + half * (D / 2);
     const float qk_scale = prm.sm_scale * kLog2e;
-    const int my_blocks = nb[t];
     const int pair_barrier = 1 + t;               // named barrier of the tile's 256 threads
-    float m_used = -INFINITY, l = 0.f;
+    uint32_t c = 0;                               // score blocks this tile has consumed
     bool ok = true;
-    for (int j = 0; j < my_blocks && ok; ++j) {
-      if (!mbar_wait(smem_u32(&ss.s_full[t]), j & 1, wc, kSoftS)) { ok = false; break; }
-      tc_fence_after();
-      const int n0 = j * BLOCK_N + half * HALF_N;
-      const bool boundary = (n0 + HALF_N > prm.n_ctx) || (prm.causal && n0 + HALF_N > m0 + t * BLOCK_M);
-      const MaskInfo mi{n0, q_row, prm.n_ctx, prm.causal};
-      // pass 1: max of the raw scores over this half row, then over the whole row
-      // (qk_scale > 0, so the scaled max is max * qk_scale)
-      float mx = boundary ? max_half<true>(s_tmem, mi) : max_half<false>(s_tmem, mi);
-      ss.half_max[t][j & 1][half][row_in_tile] = mx;
-      asm volatile("bar.sync %0, 256;" ::"r"(pair_barrier) : "memory");
-      mx = fmaxf(mx, ss.half_max[t][j & 1][half ^ 1][row_in_tile]) * qk_scale;
-      // advance the working max only when it moved far (or on the first block); both threads
-      // of a row see the same numbers and take the same decision
-      float alpha = 1.f;
-      bool rescale = false;
-      if (mx > m_used + kRescaleThreshold) {
-        alpha = fast_exp2(m_used - mx);      // 0 on the first block (m_used = -inf)
-        m_used = mx;
-        rescale = j > 0;
-      }
-      if (__any_sync(0xffffffffu, rescale)) {
-        // O_t may only be touched once the P.V MMA of block j-1 has finished; each half
-        // rescales its own D/2 columns of the accumulator
-        if (!mbar_wait(smem_u32(&ss.pv_done[t]), (j - 1) & 1, wc, kSoftPv)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < D / 64; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(o_tmem + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x32(o_tmem + c * 32, r);
-        }
-        tmem_st_wait();
-      }
-      // pass 2: exponentials, partial row sum, 16-bit P over the scores already read
-      const float sum = boundary ? exp_half<T, true>(s_tmem, qk_scale, -m_used, mi)
-                                 : exp_half<T, false>(s_tmem, qk_scale, -m_used, mi);
-      l = l * alpha + sum;
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&ss.p_full[t]));
-    }
-    // ---- epilogue: whole-row sum, O / l and the row statistic
-    ss.half_sum[t][half][row_in_tile] = l;
-    asm volatile("bar.sync %0, 256;" ::"r"(pair_barrier) : "memory");
-    l += ss.half_sum[t][half ^ 1][row_in_tile];
-    if (ok && my_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done[t]), (my_blocks - 1) & 1, wc, kSoftFinal);
-    tc_fence_after();
-    if (ok && my_blocks > 0) {
-      const float inv_l = 1.f / l;
-      const bool live = q_row < prm.rows;
-      T* orow = (T*)prm.o + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq + half * (D / 2);
-#pragma unroll 1
-      for (int c = 0; c < D / 64; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(o_tmem + c * 32, r);
-        tmem_ld_wait();
-        if (live) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 out;
-            out.x = pack2<T>(__uint_as_float(r[v * 8 + 0]) * inv_l, __uint_as_float(r[v * 8 + 1]) * inv_l);
-            out.y = pack2<T>(__uint_as_float(r[v * 8 + 2]) * inv_l, __uint_as_float(r[v * 8 + 3]) * inv_l);
-            out.z = pack2<T>(__uint_as_float(r[v * 8 + 4]) * inv_l, __uint_as_float(r[v * 8 + 5]) * inv_l);
-            out.w = pack2<T>(__uint_as_float(r[v * 8 + 6]) * inv_l, __uint_as_float(r[v * 8 + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = out;
+    for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
+      const int bh = sch.head(u);
+      for (int sub = 0; sub < sch.subs(u) && ok; ++sub) {
+        const int m0 = sch.block(u, sub) * (TILES * BLOCK_M);
+        const int q_row = m0 + t * BLOCK_M + row_in_tile;
+        const int my_blocks = key_blocks(m0, t);
+        float m_used = -INFINITY, l = 0.f;
+        for (int j = 0; j < my_blocks && ok; ++j, ++c) {
+          if (!mbar_wait(smem_u32(&ss.s_full[t]), c & 1, wc, kSoftS)) { ok = false; break; }
+          tc_fence_after();
+          const int n0 = j * BLOCK_N + half * HALF_N;
+          const bool boundary = (n0 + HALF_N > prm.n_ctx) || (prm.causal && n0 + HALF_N > m0 + t * BLOCK_M);
+          const MaskInfo mi{n0, q_row, prm.n_ctx, prm.causal};
+          // pass 1: max of the raw scores over this half row, then over the whole row
+          // (qk_scale > 0, so the scaled max is max * qk_scale)
+          float mx = boundary ? max_half<true>(s_tmem, mi) : max_half<false>(s_tmem, mi);
+          ss.half_max[t][c & 1][half][row_in_tile] = mx;
+          asm volatile("bar.sync %0, 256;" ::"r"(pair_barrier) : "memory");
+          mx = fmaxf(mx, ss.half_max[t][c & 1][half ^ 1][row_in_tile]) * qk_scale;
+          // advance the working max only when it moved far (or on the first block); both
+          // threads of a row see the same numbers and take the same decision
+          float alpha = 1.f;
+          bool rescale = false;
+          if (mx > m_used + kRescaleThreshold) {
+            alpha = fast_exp2(m_used - mx);      // 0 on the first block (m_used = -inf)
+            m_used = mx;
+            rescale = j > 0;
           }
+          if (__any_sync(0xffffffffu, rescale)) {
+            // O_t may only be touched once the P.V MMA of block j-1 has finished; each half
+            // rescales its own D/2 columns of the accumulator
+            if (!mbar_wait(smem_u32(&ss.pv_done[t]), (c - 1) & 1, wc, kSoftPv)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll 1
+            for (int cc = 0; cc < D / 64; ++cc) {
+              uint32_t r[32];
+              tmem_ld_32x32(o_tmem + cc * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32(o_tmem + cc * 32, r);
+            }
+            tmem_st_wait();
+          }
+          // pass 2: exponentials, partial row sum, 16-bit P over the scores already read
+          const float sum = boundary ? exp_half<T, true>(s_tmem, qk_scale, -m_used, mi)
+                                     : exp_half<T, false>(s_tmem, qk_scale, -m_used, mi);
+          l = l * alpha + sum;
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(smem_u32(&ss.p_full[t]));
+        }
+        // ---- whole-row sum, O / l and the row statistic of this query block
+        ss.half_sum[t][half][row_in_tile] = l;
+        asm volatile("bar.sync %0, 256;" ::"r"(pair_barrier) : "memory");
+        l += ss.half_sum[t][half ^ 1][row_in_tile];
+        if (ok && my_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done[t]), (c - 1) & 1, wc, kSoftFinal);
+        tc_fence_after();
+        if (ok && my_blocks > 0) {
+          const float inv_l = 1.f / l;
+          const bool live = q_row < prm.rows;
+          T* orow = (T*)prm.o + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq + half * (D / 2);
+#pragma unroll 1
+          for (int cc = 0; cc < D / 64; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(o_tmem + cc * 32, r);
+            tmem_ld_wait();
+            if (live) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 out;
+                out.x = pack2<T>(__uint_as_float(r[v * 8 + 0]) * inv_l, __uint_as_float(r[v * 8 + 1]) * inv_l);
+                out.y = pack2<T>(__uint_as_float(r[v * 8 + 2]) * inv_l, __uint_as_float(r[v * 8 + 3]) * inv_l);
+                out.z = pack2<T>(__uint_as_float(r[v * 8 + 4]) * inv_l, __uint_as_float(r[v * 8 + 5]) * inv_l);
+                out.w = pack2<T>(__uint_as_float(r[v * 8 + 6]) * inv_l, __uint_as_float(r[v * 8 + 7]) * inv_l);
+                *reinterpret_cast<uint4*>(orow + cc * 32 + v * 8) = out;
+              }
+            }
+          }
+          if (live && half == 0 && prm.lse) prm.lse[(int64_t)bh * prm.stride_lse + q_row] = m_used + log2f(l);
         }
       }
-      if (live && half == 0 && prm.lse) prm.lse[(int64_t)bh * prm.stride_lse + q_row] = m_used + log2f(l);
     }
   }
 
@@ -448,8 +499,13 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   auto kernel = attn_fwd_tc_kernel<T, D, FMT>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return std::string("attn_fwd: ") + cudaGetErrorString(e);
-  dim3 grid((unsigned)((p.rows + TILES * BLOCK_M - 1) / (TILES * BLOCK_M)), (unsigned)p.bh, 1);
-  kernel<<<grid, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], prm, ctx.status);
+  Schedule sch{};
+  sch.blocks = (int)((p.rows + TILES * BLOCK_M - 1) / (TILES * BLOCK_M));
+  sch.causal = p.causal;
+  sch.units_per_head = p.causal ? (sch.blocks + 1) / 2 : sch.blocks;
+  sch.total_units = sch.units_per_head * (int)p.bh;
+  const int grid = sch.total_units < ctx.sm_count ? sch.total_units : ctx.sm_count;
+  kernel<<<grid, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], prm, sch, ctx.status);
   ++*ctx.launches;
   e = cudaGetLastError();
   if (e != cudaSuccess) return std::string("attn_fwd launch failed: ") + cudaGetErrorString(e);
@@ -471,7 +527,8 @@ bool attn_fwd_tc_eligible(const AttnProblem& p, std::string* why) {
   if (((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.v | (uintptr_t)p.out0) % 16)
     return no("base pointers are not 16-byte aligned");
   if (p.n_ctx < 128) return no("sequence shorter than one 128-row tile");
-  if (p.n_ctx > 0x7fffffff / 256 || p.bh > 65535) return no("extent out of range");
+  if (p.n_ctx > 0x7fffffff / 256 || p.bh > 65535 || (p.rows / 256 + 1) * p.bh > 0x7fffffff)
+    return no("extent out of range");
   if (!(p.sm_scale > 0.f)) return no("softmax scale is not positive");
   return true;
 }
