@@ -12,15 +12,21 @@
 // Both kernels: one CTA per 128 resident rows of one (batch, head) (queries for
 // dq, keys for dkdv); the other side streams through in blocks of 128 rows (MMAs
 // with N = 128: narrower score tiles ran the tensor pipe at half rate, measured).
-// Warp 4 issues TMA loads, warp 5 issues tcgen05.mma, and two warpgroups (warps 0-3
-// and 6-9) do the exponentials and products: a thread owns one resident row (its
-// TMEM lane) and one half of the 128 columns of a block, so the TMEM round trips of
-// one group are covered by the arithmetic of the other.  The 16-bit P / dS tiles
-// never touch shared memory: each group writes them back over the fp32 columns it
-// read and they feed the next MMA as TMEM operands.
+// Warp 16 issues TMA loads, warp 17 issues every tcgen05.mma, and four warpgroups (warps
+// 0-15) do the exponentials and products: a thread owns one resident row (its TMEM lane)
+// and one quarter of the 128 columns of a block, so the TMEM round trips of one group are
+// covered by the arithmetic of the others.  The element-wise warps copy a fresh score (or
+// dP) tile into registers and release its TMEM columns at once, so that the next MMA into
+// those columns does not wait for the exponentials.  dS (and P in dq) go back into TMEM over
+// the fp32 columns they were computed from and feed the next MMA as TMEM operands; P^T in
+// dkdv goes through shared memory (see there).  Measured on a B200, per SM: a tcgen05.mma
+// costs the issuing thread about 55 cycles whatever its size (a 128 x 128 x 16 one occupies
+// the tensor pipe for 64, so one issuer just keeps up and N = 64 runs at half rate), a
+// tcgen05.commit or a completed barrier wait about 50; two issuing warps interleave their
+// MMAs and were slower; ex2.approx runs at 16 per cycle.
 //
 // TMEM columns (512):  dq:    S[2] (dS aliases) | dP | dQ
-//                      dkdv:  S^T (P^T aliases) | dP^T (dS^T aliases) | dV | dK
+//                      dkdv:  S^T | dP^T (dS^T aliases) | dV | dK
 //
 // HBM layout: Q, K, V, dO, dQ, dK, dV [BH, S, D] with D contiguous; L, Delta
 // [BH, S] fp32.
@@ -36,8 +42,11 @@ namespace {
 using namespace ptx;
 
 constexpr int BLK = 128;              // rows per tile on both sides
-constexpr int HALF = 64;              // columns of a block owned by one element-wise group
-constexpr int NUM_THREADS = 320;      // warps 0-3 and 6-9 element-wise, 4 TMA, 5 MMA
+constexpr int GROUPS = 4;             // element-wise groups (four warps each)
+constexpr int GCOLS = BLK / GROUPS;   // columns of a block owned by one group
+constexpr int EW_THREADS = GROUPS * 128;
+constexpr int LOAD_WARP = 16, MMA_WARP = 17;
+constexpr int NUM_THREADS = 576;      // warps 0-15 element-wise, 16 TMA, 17 MMA
 constexpr int TMEM_COLS = 512;
 constexpr float kLog2e = 1.44269504088896340736f;
 
@@ -80,26 +89,38 @@ __device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, 
 
 // D_tmem[128 x 128] = A[128 x D] * B[128 x D]^T, both K-major tiles.
 template <int D>
-__device__ __forceinline__ void mma_nt(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr, uint32_t idesc) {
+__device__ __forceinline__ void mma_nt(uint32_t d_tmem, SmemDesc a, SmemDesc b, uint32_t idesc) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     const uint32_t off = (kk / 4) * (BLK * 128) + (kk % 4) * 32;
-    mma_f16_ss(d_tmem, smem_desc_sw128(a_addr + off, 0, 1024), smem_desc_sw128(b_addr + off, 0, 1024),
-               idesc, kk != 0);
+    mma_f16_ss(d_tmem, a.at(off), b.at(off), idesc, kk != 0);
   }
 }
 
 // D_tmem[128 x D] (+)= A_tmem[128 x 128] * B[128 x D]; B a row-major (MN-major) tile of
-// 128 rows.  The 16-bit A operand is stored by the two element-wise groups in two pieces:
-// columns 0-63 of the block packed at a_tmem+0..31, columns 64-127 at a_tmem+64..95.
+// 128 rows.  The 16-bit A operand is stored by the element-wise groups in pieces: group g
+// packs its 32 columns of the block into the 16 words at a_tmem + 32 g.
 template <int D>
-__device__ __forceinline__ void mma_tn(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t idesc,
+__device__ __forceinline__ void mma_tn(uint32_t d_tmem, uint32_t a_tmem, SmemDesc b, uint32_t idesc,
                                        bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < BLK / 16; ++kk)
-    mma_f16_ts(d_tmem, a_tmem + (kk / 4) * HALF + (kk % 4) * 8,
-               smem_desc_sw128(b_addr + kk * 2048, BLK * 128, 1024), idesc, accumulate || kk != 0);
+    mma_f16_ts(d_tmem, a_tmem + (kk / 2) * GCOLS + (kk % 2) * 8, b.at(kk * 2048), idesc, accumulate || kk != 0);
 }
+
+// D_tmem[128 x D] (+)= A[128 x 128] * B[128 x D]: A a K-major 128 x 128 tile in shared memory
+// (two 64-column atoms), B a row-major (MN-major) tile of 128 rows.
+template <int D>
+__device__ __forceinline__ void mma_sn(uint32_t d_tmem, SmemDesc a, SmemDesc b, uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < BLK / 16; ++kk)
+    mma_f16_ss(d_tmem, a.at((kk / 4) * (BLK * 128) + (kk % 4) * 32), b.at(kk * 2048), idesc, accumulate || kk != 0);
+}
+
+// Descriptors of a K-major tile (operand of mma_nt) and of a row-major tile used as the
+// MN-major B operand of mma_tn, built once per kernel; `advanced` selects a ring stage.
+__device__ __forceinline__ SmemDesc kmajor(uint32_t addr) { return make_desc_sw128(addr, 0, 1024); }
+__device__ __forceinline__ SmemDesc mnmajor(uint32_t addr) { return make_desc_sw128(addr, BLK * 128, 1024); }
 
 __device__ __forceinline__ void drain(uint32_t bar, uint32_t parity, const WaitCtx& wc, uint32_t site) {
   const long long t0 = clock64();
@@ -108,7 +129,10 @@ __device__ __forceinline__ void drain(uint32_t bar, uint32_t parity, const WaitC
   }
 }
 
-// ---- element-wise passes over one group's 64 columns of a block --------------------
+// ---- element-wise passes over one group's 32 columns of a block --------------------
+// Sixteen warps share the work so that four are resident on every scheduler: the passes are
+// chains of TMEM round trips and special-function latency, and with two warps per scheduler
+// (64 columns per thread) they, not the tensor pipe, set the time of an iteration.
 struct KeyMask {
   int n0, q_row, n_ctx, causal;
   __device__ __forceinline__ bool masked(int col) const {
@@ -117,101 +141,68 @@ struct KeyMask {
   }
 };
 
-// dq: dS = exp2(S*qk_scale - L) * (dP - Delta), rounded, written over S.
-// `s_tmem` / `dp_tmem` point at the group's first column; km.n0 is that column's key.
+// dq: dS = exp2(S*qk_scale - L) * (dP - Delta), rounded, written over S, from the register
+// copies `s` and `d` of the group's 32 columns of S and dP; km.n0 is the first column's key.
 template <typename T, bool MASKED>
-__device__ __forceinline__ void ds_half(uint32_t s_tmem, uint32_t dp_tmem, float qk_scale, float neg_lse,
-                                        float delta, const KeyMask& km) {
-  uint32_t s0[32], d0[32], s1[32], d1[32];
-  tmem_ld_32x32(s_tmem, s0);
-  tmem_ld_32x32(dp_tmem, d0);
-  tmem_ld_32x32(s_tmem + 32, s1);
-  tmem_ld_32x32(dp_tmem + 32, d1);
-  tmem_ld_wait();
-  uint32_t packed[32];
+__device__ __forceinline__ void ds_part(uint32_t s_tmem, const uint32_t (&s)[32], const uint32_t (&d)[32],
+                                        float qk_scale, float neg_lse, float delta, const KeyMask& km) {
+  uint32_t packed[16];
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const uint32_t(&s)[32] = h ? s1 : s0;
-    const uint32_t(&d)[32] = h ? d1 : d0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, neg_lse));
-      float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_lse));
-      if (MASKED) {
-        if (km.masked(h * 32 + i)) p0 = 0.f;
-        if (km.masked(h * 32 + i + 1)) p1 = 0.f;
-      }
-      packed[h * 16 + i / 2] =
-          pack2<T>(p0 * (__uint_as_float(d[i]) - delta), p1 * (__uint_as_float(d[i + 1]) - delta));
+  for (int i = 0; i < 32; i += 2) {
+    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, neg_lse));
+    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_lse));
+    if (MASKED) {
+      if (km.masked(i)) p0 = 0.f;
+      if (km.masked(i + 1)) p1 = 0.f;
     }
+    packed[i / 2] = pack2<T>(p0 * (__uint_as_float(d[i]) - delta), p1 * (__uint_as_float(d[i + 1]) - delta));
   }
-  tmem_st_32x32(s_tmem, packed);
+  tmem_st_32x16(s_tmem, packed);
 }
 
-// dkdv pass A: P^T = exp2(S^T*qk_scale - L[query]), rounded, written over S^T and kept
-// (packed, 32 words) for pass B.  `k_minus_q0` > column means key row > query: masked.
+// dkdv pass A: P^T = exp2(S^T*qk_scale - L[query]) from the register copy `s` of the group's
+// 32 columns, rounded and packed (16 words).  `k_minus_q0` > column means key row > query: masked.
 template <typename T, bool DIAG>
-__device__ __forceinline__ void pt_half(uint32_t st_tmem, float qk_scale, const float* lse_s, int k_minus_q0,
-                                        uint32_t (&keep)[32]) {
-  // the statistics are read into registers before the TMEM loads are issued
-  float4 lv[16];
+__device__ __forceinline__ void pt_part(const uint32_t (&s)[32], float qk_scale, const float* lse_s,
+                                        int k_minus_q0, uint32_t (&keep)[16]) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) lv[i] = *reinterpret_cast<const float4*>(lse_s + i * 4);
-  uint32_t s0[32], s1[32];
-  tmem_ld_32x32(st_tmem, s0);
-  tmem_ld_32x32(st_tmem + 32, s1);
-  tmem_ld_wait();
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const uint32_t(&s)[32] = h ? s1 : s0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-      const float4 l = lv[h * 8 + i / 4];
-      float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, -l.x));
-      float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, -l.y));
-      float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, -l.z));
-      float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, -l.w));
-      if (DIAG) {
-        const int col = h * 32 + i;
-        if (k_minus_q0 > col) p0 = 0.f;
-        if (k_minus_q0 > col + 1) p1 = 0.f;
-        if (k_minus_q0 > col + 2) p2 = 0.f;
-        if (k_minus_q0 > col + 3) p3 = 0.f;
-      }
-      keep[h * 16 + i / 2] = pack2<T>(p0, p1);
-      keep[h * 16 + i / 2 + 1] = pack2<T>(p2, p3);
+  for (int i = 0; i < 32; i += 4) {
+    const float4 l = *reinterpret_cast<const float4*>(lse_s + i);
+    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, -l.x));
+    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, -l.y));
+    float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, -l.z));
+    float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, -l.w));
+    if (DIAG) {
+      if (k_minus_q0 > i) p0 = 0.f;
+      if (k_minus_q0 > i + 1) p1 = 0.f;
+      if (k_minus_q0 > i + 2) p2 = 0.f;
+      if (k_minus_q0 > i + 3) p3 = 0.f;
     }
+    keep[i / 2] = pack2<T>(p0, p1);
+    keep[i / 2 + 1] = pack2<T>(p2, p3);
   }
-  tmem_st_32x32(st_tmem, keep);
 }
 
 // dkdv pass B: dS^T = P^T * (dP^T - Delta[query]) from the register copy of P^T.
 template <typename T>
-__device__ __forceinline__ void dst_half(uint32_t dpt_tmem, const float* delta_s, const uint32_t (&keep)[32]) {
-  float4 dv[16];
+__device__ __forceinline__ void dst_part(uint32_t dpt_tmem, const float* delta_s, const uint32_t (&keep)[16]) {
+  float4 dv[8];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) dv[i] = *reinterpret_cast<const float4*>(delta_s + i * 4);
-  uint32_t d0[32], d1[32];
-  tmem_ld_32x32(dpt_tmem, d0);
-  tmem_ld_32x32(dpt_tmem + 32, d1);
+  for (int i = 0; i < 8; ++i) dv[i] = *reinterpret_cast<const float4*>(delta_s + i * 4);
+  uint32_t d[32];
+  tmem_ld_32x32(dpt_tmem, d);
   tmem_ld_wait();
-  uint32_t packed[32];
+  uint32_t packed[16];
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const uint32_t(&d)[32] = h ? d1 : d0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-      const float4 dl = dv[h * 8 + i / 4];
-      float p0, p1, p2, p3;
-      unpack2<T>(keep[h * 16 + i / 2], p0, p1);
-      unpack2<T>(keep[h * 16 + i / 2 + 1], p2, p3);
-      packed[h * 16 + i / 2] =
-          pack2<T>(p0 * (__uint_as_float(d[i]) - dl.x), p1 * (__uint_as_float(d[i + 1]) - dl.y));
-      packed[h * 16 + i / 2 + 1] =
-          pack2<T>(p2 * (__uint_as_float(d[i + 2]) - dl.z), p3 * (__uint_as_float(d[i + 3]) - dl.w));
-    }
+  for (int i = 0; i < 32; i += 4) {
+    const float4 dl = dv[i / 4];
+    float p0, p1, p2, p3;
+    unpack2<T>(keep[i / 2], p0, p1);
+    unpack2<T>(keep[i / 2 + 1], p2, p3);
+    packed[i / 2] = pack2<T>(p0 * (__uint_as_float(d[i]) - dl.x), p1 * (__uint_as_float(d[i + 1]) - dl.y));
+    packed[i / 2 + 1] = pack2<T>(p2 * (__uint_as_float(d[i + 2]) - dl.z), p3 * (__uint_as_float(d[i + 3]) - dl.w));
   }
-  tmem_st_32x32(dpt_tmem, packed);
+  tmem_st_32x16(dpt_tmem, packed);
 }
 
 // Read-out of `COLS` columns of a fp32 accumulator row: scale, round, store.
@@ -245,15 +236,15 @@ struct SharedDq {
   alignas(8) uint64_t qdo_full;
   alignas(8) uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
   alignas(8) uint64_t s_full[2];
-  alignas(8) uint64_t dp_full, ds_full, dq_done;
+  alignas(8) uint64_t dp_full, dp_read, ds_full, dq_done;
   uint32_t tmem_base;
   int abort_flag;
 };
 
 // Pipeline of block j (keys j*128 ...):
 //   MMA   S(j) = Q K(j)^T into S[j&1]            (issued two blocks ahead)
-//   MMA   dP(j) = dO V(j)^T into the single dP buffer, as soon as the element-wise pass of
-//         block j-1 has read dP(j-1)
+//   MMA   dP(j) = dO V(j)^T into the single dP buffer, as soon as the element-wise warps have
+//         loaded dP(j-1) into registers (they signal that before they start computing)
 //   elem  dS(j) written over S[j&1]
 //   MMA   dQ += dS(j) K(j)
 // so the chain from one block's element-wise pass to the next is one MMA (dP) long.
@@ -291,12 +282,13 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     mbar_init(smem_u32(&ss.s_full[0]), 1);
     mbar_init(smem_u32(&ss.s_full[1]), 1);
     mbar_init(smem_u32(&ss.dp_full), 1);
-    mbar_init(smem_u32(&ss.ds_full), 256);
+    mbar_init(smem_u32(&ss.dp_read), EW_THREADS / 32);
+    mbar_init(smem_u32(&ss.ds_full), EW_THREADS / 32);
     mbar_init(smem_u32(&ss.dq_done), 1);
     ss.abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     tmem_alloc(smem_u32(&ss.tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
@@ -305,7 +297,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   tc_fence_after();
   const uint32_t tmem = ss.tmem_base;
 
-  if (warp == 4) {
+  if (warp == LOAD_WARP) {
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_k);
@@ -345,16 +337,21 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int j = max(0, v_issued - V_STAGES); j < v_issued; ++j)
         drain(smem_u32(&ss.v_full[j % V_STAGES]), (j / V_STAGES) & 1, wc, 39);
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
+    // One thread issues every MMA.  A tcgen05.mma costs its issuer about 55 cycles whatever
+    // its size (measured; a 128 x 128 x 16 one occupies the pipe for 64), a commit or a
+    // barrier wait about 50 more, so this loop is kept to the minimum of both.
     if (lane == 0) {
       constexpr uint32_t idesc_nt = make_idesc(FMT, BLK, BLK, 0, 0);
       constexpr uint32_t idesc_tn = make_idesc(FMT, BLK, D, 0, 1);
+      const SmemDesc q_km = kmajor(q_addr), do_km = kmajor(do_addr), k_km = kmajor(k_addr), v_km = kmajor(v_addr);
+      const SmemDesc k_mn = mnmajor(k_addr);
       bool ok = mbar_wait(smem_u32(&ss.qdo_full), 0, wc, 33);
       auto issue_qk = [&](int j) -> bool {
         const int s = j % K_STAGES;
         if (!mbar_wait(smem_u32(&ss.k_full[s]), (j / K_STAGES) & 1, wc, 34)) return false;
         tc_fence_after();
-        mma_nt<D>(tmem + S_COL + (j & 1) * BLK, q_addr, k_addr + s * TILE, idesc_nt);
+        mma_nt<D>(tmem + S_COL + (j & 1) * BLK, q_km, k_km.advanced(s * TILE), idesc_nt);
         mma_commit(smem_u32(&ss.s_full[j & 1]));
         return true;
       };
@@ -362,7 +359,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int s = j % V_STAGES;
         if (!mbar_wait(smem_u32(&ss.v_full[s]), (j / V_STAGES) & 1, wc, 35)) return false;
         tc_fence_after();
-        mma_nt<D>(tmem + DP_COL, do_addr, v_addr + s * TILE, idesc_nt);
+        mma_nt<D>(tmem + DP_COL, do_km, v_km.advanced(s * TILE), idesc_nt);
         mma_commit(smem_u32(&ss.v_empty[s]));
         mma_commit(smem_u32(&ss.dp_full));
         return true;
@@ -370,11 +367,15 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (ok && n_blocks > 0) ok = issue_qk(0) && issue_dp(0);
       if (ok && n_blocks > 1) ok = issue_qk(1);
       for (int j = 0; j < n_blocks && ok; ++j) {
+        if (j + 1 < n_blocks) {
+          // the element-wise warps have dP(j) in registers: the next dP may overwrite it while
+          // they are still working on block j
+          if (!mbar_wait(smem_u32(&ss.dp_read), j & 1, wc, 41)) { ok = false; break; }
+          if (!issue_dp(j + 1)) { ok = false; break; }
+        }
         if (!mbar_wait(smem_u32(&ss.ds_full), j & 1, wc, 36)) { ok = false; break; }
         tc_fence_after();
-        // the element-wise pass of block j has read dP(j): the next dP may overwrite it
-        if (j + 1 < n_blocks && !issue_dp(j + 1)) { ok = false; break; }
-        mma_tn<D>(tmem + DQ_COL, tmem + S_COL + (j & 1) * BLK, k_addr + (j % K_STAGES) * TILE, idesc_tn, j != 0);
+        mma_tn<D>(tmem + DQ_COL, tmem + S_COL + (j & 1) * BLK, k_mn.advanced((j % K_STAGES) * TILE), idesc_tn, j != 0);
         mma_commit(smem_u32(&ss.k_empty[j % K_STAGES]));
         if (j + 1 == n_blocks) mma_commit(smem_u32(&ss.dq_done));
         // S(j+2) reuses the buffer dS(j) sits in: MMAs run in issue order
@@ -382,7 +383,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
     }
   } else {
-    const int group = warp >= 6 ? 1 : 0;          // owns columns group*64 ... of every block
+    const int group = warp / 4;                   // owns columns group*32 ... of every block
     const int row_in_tile = (warp % 4) * 32 + lane;
     const int q_row = m0 + row_in_tile;
     const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
@@ -397,28 +398,40 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (!mbar_wait(smem_u32(&ss.s_full[j & 1]), (j >> 1) & 1, wc, 37)) { ok = false; break; }
       if (!mbar_wait(smem_u32(&ss.dp_full), j & 1, wc, 38)) { ok = false; break; }
       tc_fence_after();
-      const int n0 = j * BLK + group * HALF;
-      const bool boundary = (n0 + HALF > prm.n_ctx) || (prm.causal && n0 + HALF > m0);
+      const int n0 = j * BLK + group * GCOLS;
+      const bool boundary = (n0 + GCOLS > prm.n_ctx) || (prm.causal && n0 + GCOLS > m0);
       const KeyMask km{n0, q_row, prm.n_ctx, prm.causal};
-      const uint32_t s_tmem = tmem + lane_addr + S_COL + (j & 1) * BLK + group * HALF;
-      const uint32_t dp_tmem = tmem + lane_addr + DP_COL + group * HALF;
-      if (boundary) ds_half<T, true>(s_tmem, dp_tmem, qk_scale, -lse, delta, km);
-      else ds_half<T, false>(s_tmem, dp_tmem, qk_scale, -lse, delta, km);
+      const uint32_t s_tmem = tmem + lane_addr + S_COL + (j & 1) * BLK + group * GCOLS;
+      const uint32_t dp_tmem = tmem + lane_addr + DP_COL + group * GCOLS;
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(dp_tmem, dv);
+      tmem_ld_32x32(s_tmem, sv);
+      tmem_ld_wait();
+      // dP(j) is in registers: let the next dP start
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ss.dp_read));
+      if (boundary) ds_part<T, true>(s_tmem, sv, dv, qk_scale, -lse, delta, km);
+      else ds_part<T, false>(s_tmem, sv, dv, qk_scale, -lse, delta, km);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(smem_u32(&ss.ds_full));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ss.ds_full));   // one arrival per warp
     }
     if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&ss.dq_done), 0, wc, 40);
     tc_fence_after();
     if (ok && n_blocks > 0) {
-      // each group stores half of the columns of dQ
-      T* orow = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq + group * (D / 2);
-      store_rows<T, D / 2>(tmem + lane_addr + DQ_COL + group * (D / 2), orow, prm.sm_scale, q_row < prm.rows);
+      // the groups share the columns of dQ, 32 at a time
+      constexpr int SC = 32;
+      if (group * SC < D) {
+        T* orow = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq + group * SC;
+        store_rows<T, SC>(tmem + lane_addr + DQ_COL + group * SC, orow, prm.sm_scale, q_row < prm.rows);
+      }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -429,14 +442,27 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // ===========================================================================
 struct SharedDkdv {
   alignas(8) uint64_t kv_full;
-  alignas(8) uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
-  alignas(8) uint64_t st_full, dpt_full, p_full, ds_full, done;
+  alignas(8) uint64_t qdo_full[2], qdo_empty[2];
+  alignas(8) uint64_t st_full, s_read, p_full, p_empty, dpt_full, ds_full, done;
   alignas(16) float lse[2][BLK];
   alignas(16) float delta[2][BLK];
   uint32_t tmem_base;
   int abort_flag;
 };
 
+constexpr int P_TILE = BLK * BLK * 2;     // the 16-bit P^T tile in shared memory
+
+// Pipeline of streamed query block t (S^T single-buffered in TMEM, all 512 columns taken):
+//   MMA   S^T(t) = K Q(t)^T                     as soon as the element-wise warps hold S^T(t-1)
+//                                               in registers (they signal that before computing)
+//   elem  P^T(t) = exp2(...) -> shared memory   (K-major, 128-byte swizzle, like a loaded tile)
+//   MMA   dV += P^T(t) dO(t)                    both operands from shared memory
+//   MMA   dP^T(t) = V dO(t)^T                   issued one block ahead
+//   elem  dS^T(t) = P^T (dP^T - Delta)          written over dP^T in TMEM
+//   MMA   dK += dS^T(t) Q(t)                    A operand from TMEM
+// P^T goes through shared memory because in TMEM it can only sit on top of S^T, and then
+// S^T(t+1) has to wait for dV(t), which has to wait for the whole exponential pass: that chain
+// (about 3500 cycles a block, measured) and not the 2048 cycles of tensor work set the pace.
 template <typename T, int D, uint32_t FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -444,11 +470,12 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         Params prm, DeviceStatus* status) {
   constexpr int TILE = BLK * D * 2;
   constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  // layout: K | V | Q0 Q1 | dO0 dO1 | P^T | barriers and row statistics
   const uint32_t k_addr = smem_u32(smem), v_addr = k_addr + TILE, q_addr = v_addr + TILE,
-                 do_addr = q_addr + 2 * TILE;
-  SharedDkdv& ss = *reinterpret_cast<SharedDkdv*>(smem + 6 * TILE);
+                 do_addr = q_addr + 2 * TILE, p_addr = do_addr + 2 * TILE;
+  SharedDkdv& ss = *reinterpret_cast<SharedDkdv*>(smem + 6 * TILE + P_TILE);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   WaitCtx wc{&ss.abort_flag, status};
   const int bh = blockIdx.y;
@@ -457,23 +484,32 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int first = prm.causal ? n0 / BLK : 0;            // earlier queries never see these keys
   const int n_iter = total_q_blocks - first;
 
+  // the swizzled tiles need the 1024-byte alignment asked for above
+  if (k_addr & 1023u) {
+    if (threadIdx.x == 0) {
+      ss.abort_flag = 0;
+      report_timeout(wc, 62, k_addr);
+    }
+    return;
+  }
+
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ss.kv_full), 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&ss.q_full[s]), 1);
-      mbar_init(smem_u32(&ss.q_empty[s]), 1);
-      mbar_init(smem_u32(&ss.do_full[s]), 1);
-      mbar_init(smem_u32(&ss.do_empty[s]), 1);
+      mbar_init(smem_u32(&ss.qdo_full[s]), 1);
+      mbar_init(smem_u32(&ss.qdo_empty[s]), 1);
     }
     mbar_init(smem_u32(&ss.st_full), 1);
+    mbar_init(smem_u32(&ss.s_read), EW_THREADS / 32);
+    mbar_init(smem_u32(&ss.p_full), EW_THREADS / 32);
+    mbar_init(smem_u32(&ss.p_empty), 1);
     mbar_init(smem_u32(&ss.dpt_full), 1);
-    mbar_init(smem_u32(&ss.p_full), 256);
-    mbar_init(smem_u32(&ss.ds_full), 256);
+    mbar_init(smem_u32(&ss.ds_full), EW_THREADS / 32);
     mbar_init(smem_u32(&ss.done), 1);
     ss.abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     tmem_alloc(smem_u32(&ss.tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
@@ -482,7 +518,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   tc_fence_after();
   const uint32_t tmem = ss.tmem_base;
 
-  if (warp == 4) {
+  if (warp == LOAD_WARP) {
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_k);
@@ -496,130 +532,149 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int s = t & 1;
         const uint32_t ph = (t >> 1) & 1;
         const int row0 = (first + t) * BLK;
-        if (!mbar_wait(smem_u32(&ss.q_empty[s]), ph ^ 1, wc, 51)) break;
-        mbar_expect_tx(smem_u32(&ss.q_full[s]), TILE);
-        load_tile<D>(q_addr + s * TILE, &map_q, smem_u32(&ss.q_full[s]), row0, bh);
-        if (!mbar_wait(smem_u32(&ss.do_empty[s]), ph ^ 1, wc, 52)) {
-          drain(smem_u32(&ss.q_full[s]), ph, wc, 59);
-          break;
-        }
-        mbar_expect_tx(smem_u32(&ss.do_full[s]), TILE);
-        load_tile<D>(do_addr + s * TILE, &map_do, smem_u32(&ss.do_full[s]), row0, bh);
+        // Q(t) and dO(t) travel together: one barrier to fill, one to release
+        if (!mbar_wait(smem_u32(&ss.qdo_empty[s]), ph ^ 1, wc, 51)) break;
+        mbar_expect_tx(smem_u32(&ss.qdo_full[s]), 2 * TILE);
+        load_tile<D>(q_addr + s * TILE, &map_q, smem_u32(&ss.qdo_full[s]), row0, bh);
+        load_tile<D>(do_addr + s * TILE, &map_do, smem_u32(&ss.qdo_full[s]), row0, bh);
         ++issued;
       }
       drain(smem_u32(&ss.kv_full), 0, wc, 59);
-      for (int t = max(0, issued - 2); t < issued; ++t) {
-        drain(smem_u32(&ss.q_full[t & 1]), (t >> 1) & 1, wc, 59);
-        drain(smem_u32(&ss.do_full[t & 1]), (t >> 1) & 1, wc, 59);
-      }
+      for (int t = max(0, issued - 2); t < issued; ++t) drain(smem_u32(&ss.qdo_full[t & 1]), (t >> 1) & 1, wc, 59);
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
+    // One thread issues every MMA.  A tcgen05.mma costs its issuer about 55 cycles whatever
+    // its size (measured; a 128 x 128 x 16 one occupies the pipe for 64), a commit or a
+    // barrier wait about 50 more: four waits and four commits per block, no more.
     if (lane == 0) {
       constexpr uint32_t idesc_nt = make_idesc(FMT, BLK, BLK, 0, 0);
       constexpr uint32_t idesc_tn = make_idesc(FMT, BLK, D, 0, 1);
+      const SmemDesc k_km = kmajor(k_addr), v_km = kmajor(v_addr), q_km = kmajor(q_addr), do_km = kmajor(do_addr);
+      const SmemDesc q_mn = mnmajor(q_addr), do_mn = mnmajor(do_addr), p_km = kmajor(p_addr);
       bool ok = mbar_wait(smem_u32(&ss.kv_full), 0, wc, 53);
-      auto issue_st = [&](int t) -> bool {
-        const int s = t & 1;
-        if (!mbar_wait(smem_u32(&ss.q_full[s]), (t >> 1) & 1, wc, 54)) return false;
+      if (ok && n_iter > 0) ok = mbar_wait(smem_u32(&ss.qdo_full[0]), 0, wc, 54);
+      if (ok && n_iter > 0) {
         tc_fence_after();
-        mma_nt<D>(tmem + ST_COL, k_addr, q_addr + s * TILE, idesc_nt);
+        mma_nt<D>(tmem + ST_COL, k_km, q_km, idesc_nt);
         mma_commit(smem_u32(&ss.st_full));
-        return true;
-      };
-      auto issue_dpt = [&](int t) -> bool {
-        const int s = t & 1;
-        if (!mbar_wait(smem_u32(&ss.do_full[s]), (t >> 1) & 1, wc, 55)) return false;
-        tc_fence_after();
-        mma_nt<D>(tmem + DPT_COL, v_addr, do_addr + s * TILE, idesc_nt);
+        mma_nt<D>(tmem + DPT_COL, v_km, do_km, idesc_nt);
         mma_commit(smem_u32(&ss.dpt_full));
-        return true;
-      };
-      if (ok && n_iter > 0) ok = issue_st(0) && issue_dpt(0);
+      }
       for (int t = 0; t < n_iter && ok; ++t) {
         const int s = t & 1;
+        const bool more = t + 1 < n_iter;
+        if (more) {
+          // S^T(t) is in registers and Q(t+1) has landed: the next scores can go
+          if (!mbar_wait(smem_u32(&ss.s_read), t & 1, wc, 63)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&ss.qdo_full[s ^ 1]), ((t + 1) >> 1) & 1, wc, 54)) { ok = false; break; }
+          tc_fence_after();
+          mma_nt<D>(tmem + ST_COL, k_km, q_km.advanced((s ^ 1) * TILE), idesc_nt);
+          mma_commit(smem_u32(&ss.st_full));
+        }
         if (!mbar_wait(smem_u32(&ss.p_full), t & 1, wc, 56)) { ok = false; break; }
         tc_fence_after();
-        mma_tn<D>(tmem + DV_COL, tmem + ST_COL, do_addr + s * TILE, idesc_tn, t != 0);
-        mma_commit(smem_u32(&ss.do_empty[s]));
-        // the next S^T overwrites P^T: MMAs run in issue order, and the element-wise pass
-        // keeps its own (packed) copy of P^T in registers for dS^T
-        if (t + 1 < n_iter && !issue_st(t + 1)) { ok = false; break; }
+        mma_sn<D>(tmem + DV_COL, p_km, do_mn.advanced(s * TILE), idesc_tn, t != 0);
+        mma_commit(smem_u32(&ss.p_empty));
         if (!mbar_wait(smem_u32(&ss.ds_full), t & 1, wc, 57)) { ok = false; break; }
         tc_fence_after();
-        mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_addr + s * TILE, idesc_tn, t != 0);
-        mma_commit(smem_u32(&ss.q_empty[s]));
-        if (t + 1 == n_iter) mma_commit(smem_u32(&ss.done));
-        if (t + 1 < n_iter && !issue_dpt(t + 1)) { ok = false; break; }
+        mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_mn.advanced(s * TILE), idesc_tn, t != 0);
+        mma_commit(smem_u32(&ss.qdo_empty[s]));        // last use of Q(t) and dO(t)
+        if (more) {
+          mma_nt<D>(tmem + DPT_COL, v_km, do_km.advanced((s ^ 1) * TILE), idesc_nt);
+          mma_commit(smem_u32(&ss.dpt_full));
+        } else {
+          mma_commit(smem_u32(&ss.done));
+        }
       }
     }
-  } else {
-    const int group = warp >= 6 ? 1 : 0;          // owns query columns group*64 ... of every block
+  } else if (warp < EW_THREADS / 32) {
+    const int group = warp / 4;                   // owns query columns group*32 ... of every block
     const int row_in_tile = (warp % 4) * 32 + lane;
     const int k_row = n0 + row_in_tile;
     const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
     const float qk_scale = prm.sm_scale * kLog2e;
     const float* lse_base = prm.lse + (int64_t)bh * prm.stride_lse;
     const float* delta_base = prm.delta + (int64_t)bh * prm.stride_lse;
+    // This thread's 64 bytes of a P^T row in the K-major, 128-byte-swizzled tile: 64-query
+    // atoms 16 KiB apart, rows of 128 bytes, 16-byte chunks XORed with the row (mod 8).
+    const uint32_t p_row = p_addr + (group / 2) * (BLK * 128) + row_in_tile * 128;
+    const uint32_t p_chunk0 = (group % 2) * 4, p_xor = row_in_tile & 7;
     // Row statistics of the streamed query block go through shared memory (every thread
-    // needs 64 of them): the threads of group 0 fetch the 128 values of L, those of group 1
+    // needs 32 of each): the threads of group 0 fetch the 128 values of L, those of group 1
     // the 128 values of Delta.  The global load for block t+1 is issued at the top of
     // iteration t into a register and stored to shared memory at its end, so its latency is
     // off the critical path.  +inf as L makes exp2(x - L) vanish for queries past the end.
     auto fetch_stat = [&](int t) -> float {
       const int q = (first + t) * BLK + row_in_tile;
       float v = group ? 0.f : INFINITY;
-      if (q < prm.n_ctx) {
+      if (group < 2 && q < prm.n_ctx) {
         const float* src = (group ? delta_base : lse_base) + q;
         asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(src));
       }
       return v;
     };
     auto put_stat = [&](int t, float v) {
-      if (group) ss.delta[t & 1][row_in_tile] = v;
-      else ss.lse[t & 1][row_in_tile] = v;
+      if (group == 1) ss.delta[t & 1][row_in_tile] = v;
+      else if (group == 0) ss.lse[t & 1][row_in_tile] = v;
     };
     if (n_iter > 0) put_stat(0, fetch_stat(0));
     bool ok = true;
     for (int t = 0; t < n_iter && ok; ++t) {
-      // all 256 threads: statistics of block t are visible, block t-1 is no longer read
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      // all element-wise threads: statistics of block t are visible, block t-1 is no longer read
+      asm volatile("bar.sync 1, %0;" ::"n"(EW_THREADS) : "memory");
       float next_stat = 0.f;
       if (t + 1 < n_iter) next_stat = fetch_stat(t + 1);
-      const float* lse_s = ss.lse[t & 1] + group * HALF;
-      const float* delta_s = ss.delta[t & 1] + group * HALF;
-      const int q0 = (first + t) * BLK + group * HALF;      // first query of this group's columns
+      const float* lse_s = ss.lse[t & 1] + group * GCOLS;
+      const float* delta_s = ss.delta[t & 1] + group * GCOLS;
+      const int q0 = (first + t) * BLK + group * GCOLS;     // first query of this group's columns
       const bool diagonal = prm.causal && q0 < n0 + BLK;
       if (!mbar_wait(smem_u32(&ss.st_full), t & 1, wc, 58)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t st_tmem = tmem + lane_addr + ST_COL + group * HALF;
-      uint32_t keep[32];
-      if (diagonal) pt_half<T, true>(st_tmem, qk_scale, lse_s, k_row - q0, keep);
-      else pt_half<T, false>(st_tmem, qk_scale, lse_s, 0, keep);
-      tmem_st_wait();
+      uint32_t sv[32];
+      tmem_ld_32x32(tmem + lane_addr + ST_COL + group * GCOLS, sv);
+      tmem_ld_wait();
+      // S^T(t) is in registers: the next scores may overwrite it
       tc_fence_before();
-      mbar_arrive(smem_u32(&ss.p_full));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ss.s_read));
+      uint32_t keep[16];
+      if (diagonal) pt_part<T, true>(sv, qk_scale, lse_s, k_row - q0, keep);
+      else pt_part<T, false>(sv, qk_scale, lse_s, 0, keep);
+      // dV(t-1) must have read the previous P^T before it is replaced
+      if (t > 0 && !mbar_wait(smem_u32(&ss.p_empty), (t - 1) & 1, wc, 64)) { ok = false; break; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t dst = p_row + (((p_chunk0 + i) ^ p_xor) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(keep[4 * i]), "r"(keep[4 * i + 1]),
+                     "r"(keep[4 * i + 2]), "r"(keep[4 * i + 3])
+                     : "memory");
+      }
+      fence_proxy_async();          // the tensor core reads shared memory through the async proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ss.p_full));
       if (!mbar_wait(smem_u32(&ss.dpt_full), t & 1, wc, 60)) { ok = false; break; }
       tc_fence_after();
-      dst_half<T>(tmem + lane_addr + DPT_COL + group * HALF, delta_s, keep);
+      dst_part<T>(tmem + lane_addr + DPT_COL + group * GCOLS, delta_s, keep);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(smem_u32(&ss.ds_full));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ss.ds_full));   // one arrival per warp
       if (t + 1 < n_iter) put_stat(t + 1, next_stat);
     }
     if (ok && n_iter > 0) ok = mbar_wait(smem_u32(&ss.done), 0, wc, 61);
     tc_fence_after();
     if (ok && n_iter > 0) {
-      // group 0 stores dV, group 1 stores dK
+      // groups 0 and 1 store the halves of dV, groups 2 and 3 those of dK
       const bool live = k_row < prm.rows;
-      T* dk_row = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq;
-      T* dv_row = (T*)prm.out1 + (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq;
-      if (group == 0) store_rows<T, D>(tmem + lane_addr + DV_COL, dv_row, 1.f, live);
-      else store_rows<T, D>(tmem + lane_addr + DK_COL, dk_row, prm.sm_scale, live);
+      const int c0 = (group & 1) * (D / 2);
+      const int64_t row_off = (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq + c0;
+      if (group < 2) store_rows<T, D / 2>(tmem + lane_addr + DV_COL + c0, (T*)prm.out1 + row_off, 1.f, live);
+      else store_rows<T, D / 2>(tmem + lane_addr + DK_COL + c0, (T*)prm.out0 + row_off, prm.sm_scale, live);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -662,8 +717,10 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   Params prm = make_params(p);
   const char* what = dkdv ? "attn_bwd_dkdv" : "attn_bwd_dq";
   // never less than 120 KiB so two CTAs (each wanting all of TMEM) do not share an SM
-  size_t smem = (dkdv ? 6 : 2 + K_STAGES + V_STAGES) * (size_t)(BLK * D * 2) +
-                (dkdv ? sizeof(SharedDkdv) : sizeof(SharedDq)) + 1024;
+  // dkdv: six operand tiles and the P^T tile, on a 1024-byte aligned base (no slack: 227 KiB
+  // is the limit at D = 128); dq: its tiles plus slack for rounding the base up
+  size_t smem = dkdv ? 6 * (size_t)(BLK * D * 2) + P_TILE + sizeof(SharedDkdv)
+                     : (2 + K_STAGES + V_STAGES) * (size_t)(BLK * D * 2) + sizeof(SharedDq) + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
   dim3 grid((unsigned)((p.rows + BLK - 1) / BLK), (unsigned)p.bh, 1);
   cudaError_t e;

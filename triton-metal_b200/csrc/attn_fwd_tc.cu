@@ -215,7 +215,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     for (int t = 0; t < TILES; ++t) {
       mbar_init(smem_u32(&ss.s_full[t]), 1);
-      mbar_init(smem_u32(&ss.p_full[t]), 256);
+      mbar_init(smem_u32(&ss.p_full[t]), 8);
       mbar_init(smem_u32(&ss.pv_done[t]), 1);
     }
     ss.abort_flag = 0;
@@ -293,14 +293,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       constexpr uint32_t idesc_qk = make_idesc(FMT, BLOCK_M, BLOCK_N, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc(FMT, BLOCK_M, D, 0, 1);
       // S_t = Q_t K^T with K in ring stage `stage`.  The caller has made sure K has landed.
+      // operand descriptors are built once; per instruction only the address field moves
+      const SmemDesc q_desc = make_desc_sw128(q_addr, 0, 1024), k_desc = make_desc_sw128(k_addr, 0, 1024);
+      const SmemDesc v_desc = make_desc_sw128(v_addr, HALF_BYTES, 1024);
       auto issue_qk = [&](int t, int stage) {
-        const uint32_t kb = k_addr + stage * TILE_BYTES;
-        const uint32_t qb = q_addr + t * TILE_BYTES;
+        const SmemDesc kb = k_desc.advanced(stage * TILE_BYTES);
+        const SmemDesc qb = q_desc.advanced(t * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
-          mma_f16_ss(tmem + S_COL + t * BLOCK_N, smem_desc_sw128(qb + off, 0, 1024),
-                     smem_desc_sw128(kb + off, 0, 1024), idesc_qk, kk != 0);
+          mma_f16_ss(tmem + S_COL + t * BLOCK_N, qb.at(off), kb.at(off), idesc_qk, kk != 0);
         }
         mma_commit(smem_u32(&ss.s_full[t]));
       };
@@ -336,7 +338,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (!mbar_wait(smem_u32(&ss.p_full[t]), c[t] & 1, wc, kMmaP)) { ok = false; break; }
                 ++c[t];
                 tc_fence_after();
-                const uint32_t vb = v_addr + s * TILE_BYTES;
+                const SmemDesc vb = v_desc.advanced(s * TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
                   // P: TMEM operand, 16 keys = 8 packed 32-bit columns; keys 0-63 sit at the start
@@ -344,7 +346,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                   // V: MN-major, 16 keys = 2048 bytes further, 64-column halves HALF_BYTES apart.
                   mma_f16_ts(tmem + O_COL + t * D,
                              tmem + S_COL + t * BLOCK_N + (kk / 4) * HALF_N + (kk % 4) * 8,
-                             smem_desc_sw128(vb + kk * 2048, HALF_BYTES, 1024), idesc_pv, (j | kk) != 0);
+                             vb.at(kk * 2048), idesc_pv, (j | kk) != 0);
                 }
                 mma_commit(smem_u32(&ss.pv_done[t]));
               }
@@ -429,7 +431,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           l = l * alpha + sum;
           tmem_st_wait();
           tc_fence_before();
-          mbar_arrive(smem_u32(&ss.p_full[t]));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ss.p_full[t]));   // one arrival per warp
         }
         // ---- whole-row sum, O / l and the row statistic of this query block
         ss.half_sum[t][half][row_in_tile] = l;

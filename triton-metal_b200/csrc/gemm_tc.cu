@@ -199,6 +199,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(FMT, BM, BN, 0, 1);
+      const SmemDesc a_base = make_desc_sw128(smem_base, 0, 1024);
+      const SmemDesc b_base = make_desc_sw128(smem_base + A_BYTES, B_BOX_BYTES, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -212,15 +214,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(smem_u32(&ss.full[stage]), phase, wc, kMmaFull)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_base + stage * STAGE_BYTES;
-          const uint32_t b_addr = a_addr + A_BYTES;
+          const SmemDesc a_desc = a_base.advanced(stage * STAGE_BYTES);
+          const SmemDesc b_desc = b_base.advanced(stage * STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // A: K-major, 16 elements = 32 bytes further along the 128-byte row.
             // B: MN-major, 16 K rows = 2048 bytes further; 64-column blocks 8 KiB apart.
-            const uint64_t a_desc = smem_desc_sw128(a_addr + k * 32, 0, 1024);
-            const uint64_t b_desc = smem_desc_sw128(b_addr + k * 2048, B_BOX_BYTES, 1024);
-            mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+            mma_f16_ss(d_tmem, a_desc.at(k * 32), b_desc.at(k * 2048), idesc, (kb | k) != 0);
           }
           mma_commit(smem_u32(&ss.empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }

@@ -182,6 +182,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
       constexpr uint32_t idesc = make_idesc(2, BM, BN, 0, 0);     // tf32, both operands K-major
       int stage = 0;
       uint32_t phase = 0;
+      const SmemDesc stage_base = make_desc_sw128(smem_base, 0, 1024);
       int local = 0;                       // chunks issued so far (selects the accumulator)
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -195,15 +196,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
           for (int kb = kb0; kb < kb_end; ++kb) {
             if (!mbar_wait(smem_u32(&ss.full[stage]), phase, wc, 72)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t ahi = smem_base + stage * STAGE_BYTES, alo = ahi + A_BYTES;
-            const uint32_t bhi = ahi + 2 * A_BYTES, blo = bhi + B_BYTES;
+            // operands of a stage: A hi | A lo | B hi | B lo
+            const SmemDesc ahi = stage_base.advanced(stage * STAGE_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / 8; ++k) {
               // 8 fp32 = 32 bytes further along the 128-byte row, for every operand
-              const uint64_t d_ahi = smem_desc_sw128(ahi + k * 32, 0, 1024);
-              const uint64_t d_alo = smem_desc_sw128(alo + k * 32, 0, 1024);
-              const uint64_t d_bhi = smem_desc_sw128(bhi + k * 32, 0, 1024);
-              const uint64_t d_blo = smem_desc_sw128(blo + k * 32, 0, 1024);
+              const uint64_t d_ahi = ahi.at(k * 32);
+              const uint64_t d_alo = ahi.at(A_BYTES + k * 32);
+              const uint64_t d_bhi = ahi.at(2 * A_BYTES + k * 32);
+              const uint64_t d_blo = ahi.at(2 * A_BYTES + B_BYTES + k * 32);
               mma_tf32_ss(d_tmem, d_alo, d_bhi, idesc, (kb != kb0) || k != 0);
               mma_tf32_ss(d_tmem, d_ahi, d_blo, idesc, 1);
               mma_tf32_ss(d_tmem, d_ahi, d_bhi, idesc, 1);

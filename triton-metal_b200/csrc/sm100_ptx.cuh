@@ -142,6 +142,29 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo,
   return d;
 }
 
+// The same descriptor as its two 32-bit words.  The thread that issues the MMAs builds one
+// per operand outside its loops and then only steps the address field (low word, units of
+// 16 bytes): one add per instruction.  Building a descriptor from a byte address inside the
+// loop costs about a dozen dependent integer operations, and the single issuing thread pays
+// full dependent-issue latency for each of them - measured, that alone held the tensor pipe
+// to half rate in the attention kernels.  Valid while every address stays below 256 KiB.
+struct SmemDesc {
+  uint32_t lo, hi;
+  // descriptor of the tile `bytes` further on in shared memory
+  __device__ __forceinline__ uint64_t at(uint32_t bytes) const {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo + (bytes >> 4)), "r"(hi));
+    return d;
+  }
+  __device__ __forceinline__ SmemDesc advanced(uint32_t bytes) const { return SmemDesc{lo + (bytes >> 4), hi}; }
+};
+__device__ __forceinline__ SmemDesc make_desc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  SmemDesc d;
+  d.lo = ((addr & 0x3FFFFu) >> 4) | (((lbo >> 4) & 0x3FFFu) << 16);
+  d.hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+  return d;
+}
+
 // Instruction descriptor for kind::f16 / kind::tf32 with fp32 accumulation.
 //   fmt: 0 f16, 1 bf16, 2 tf32;  *_mn_major: 1 when the operand is MN-major.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t m, uint32_t n,
