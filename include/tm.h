@@ -3,7 +3,9 @@
  *
  * libtmcuda is a CUDA (sm_100a) implementation of the two hot kernels of
  * triton-metal - the tl.dot matmul and FlashAttention-2 forward/backward -
- * behind that project's handle-based `tm_*` C ABI.  The 23 `tm_*` functions
+ * behind that project's handle-based `tm_*` C ABI (plus the five one-dimensional
+ * kernels that project's own ABI tests launch: copy_kernel, add_kernel, mul_kernel,
+ * scale_bias_kernel, softmax_kernel).  The 23 `tm_*` functions
  * below have the signatures the reference's ctypes shim binds
  * (python/triton_metal/_core.py:70-100); each comment names the reference
  * export it replaces.  Everything prefixed `tmx_` is additive: the reference
@@ -49,7 +51,8 @@ char *tm_device_name(void);
 /* Scan the tt.func signature (and the first tt.dot / rank-2 tensor type) of
  * `ttir` and return a kernel descriptor text - not MSL, and not a compiler:
  * the kernels are precompiled sm_100a functions selected by entry name and
- * element type.  `num_simdgroups` is accepted for signature compatibility and
+ * element type (for the one-dimensional kernels BLOCK is the extent of the first
+ * tt.make_range, and a body that is not the named computation is refused).  `num_simdgroups` is accepted for signature compatibility and
  * only echoed into threads_per_threadgroup.  NULL on failure.
  * Replaces tm_emit_msl, Compiler.swift:192-210. */
 char *tm_emit_msl(const char *ttir, int32_t num_simdgroups);

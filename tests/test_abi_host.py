@@ -63,9 +63,40 @@ def test_parse_and_unsupported_op_errors(core):
 
 
 def test_other_kernels_are_refused_by_name(core):
-    ir = "module {\n  tt.func public @add_kernel(%a: !tt.ptr<f32>, %n: i32) {\n    tt.return\n  }\n}"
-    with pytest.raises(RuntimeError, match="kernel 'add_kernel'.*no sm_100a implementation"):
+    ir = "module {\n  tt.func public @iadd_kernel(%a: !tt.ptr<i32>, %n: i32) {\n    tt.return\n  }\n}"
+    with pytest.raises(RuntimeError, match="kernel 'iadd_kernel'.*no sm_100a implementation"):
         core.emit_msl(ir)
+
+
+def test_one_dimensional_kernels_scan(core):
+    """kernel_info of the kernels the reference's ABI tests launch: name, BLOCK from
+    tt.make_range, threads = 32 * num_warps (CABITests.swift:49-56,
+    test_plugin_shape.py:148-155, :228)."""
+    cases = [("copy", 256, "copy_kernel", ["pointer", "pointer", "scalar"]),
+             ("add", 1024, "add_kernel", ["pointer"] * 3 + ["scalar"]),
+             ("mul", 128, "mul_kernel", ["pointer"] * 3 + ["scalar"]),
+             ("scale_bias", 64, "scale_bias_kernel", ["pointer", "pointer", "scalar", "scalar", "scalar"])]
+    for kind, block, name, arg_kinds in cases:
+        info = json.loads(core.kernel_info(kernels.elementwise_ir(kind, block), 4))["kernels"][0]
+        assert (info["name"], info["block_size"], info["block_shape"]) == (name, block, [block])
+        assert info["threads_per_threadgroup"] == 128
+        assert [a["kind"] for a in info["args"]] == arg_kinds
+    info = json.loads(core.kernel_info(kernels.elementwise_ir("scale_bias", 64), 4))["kernels"][0]
+    assert [a["dtype"] for a in info["args"]] == ["f32", "f32", "f32", "f32", "i32"]
+    info = json.loads(core.kernel_info(kernels.softmax_ir(128), 2))["kernels"][0]
+    assert (info["name"], info["block_size"], info["threads_per_threadgroup"]) == ("softmax_kernel", 128, 64)
+
+
+def test_a_same_named_kernel_with_another_body_is_refused(core):
+    """The precompiled kernels are selected by name; a body that computes something else
+    must not be replaced silently."""
+    ir = kernels.elementwise_ir("add", 1024).replace("arith.addf", "arith.subf")
+    with pytest.raises(RuntimeError, match="body of 'add_kernel'"):
+        core.emit_msl(ir)
+    with pytest.raises(RuntimeError, match="takes 4 arguments"):
+        core.emit_msl(kernels.elementwise_ir("add", 1024).replace(", %arg3: i32", ""))
+    with pytest.raises(RuntimeError, match="f32 only"):
+        core.emit_msl(kernels.elementwise_ir("copy", 256).replace("f32", "bf16"))
 
 
 def test_f64_arguments_are_refused(core):

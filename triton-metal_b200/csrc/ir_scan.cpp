@@ -16,6 +16,7 @@
 
 #include <cctype>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <set>
@@ -30,6 +31,11 @@ const char* kernel_entry_name(KernelId id) {
     case KernelId::AttnBwdPreprocess: return "attn_bwd_preprocess";
     case KernelId::AttnBwdDq: return "attn_bwd_dq";
     case KernelId::AttnBwdDkdv: return "attn_bwd_dkdv";
+    case KernelId::VecCopy: return "copy_kernel";
+    case KernelId::VecAdd: return "add_kernel";
+    case KernelId::VecMul: return "mul_kernel";
+    case KernelId::ScaleBias: return "scale_bias_kernel";
+    case KernelId::Softmax: return "softmax_kernel";
     default: return "?";
   }
 }
@@ -157,6 +163,27 @@ bool assign_positional(KernelDesc& d, std::string& err) {
       set({Role::Q, Role::Kt, Role::V, Role::DO, Role::DK, Role::DV, Role::L, Role::Delta,
            Role::SmScale, Role::StrideHead, Role::StrideSeq, Role::StrideLse, Role::NCtx});
       return true;
+    // The one-dimensional kernels are matched by position only: pointers first, then scalars.
+    case KernelId::VecCopy:
+      if (a.size() != 3) return fail("takes 3 arguments (in, out, n), found " + std::to_string(a.size()));
+      set({Role::In0, Role::Out, Role::Count});
+      return true;
+    case KernelId::VecAdd:
+    case KernelId::VecMul:
+      if (a.size() != 4) return fail("takes 4 arguments (a, b, out, n), found " + std::to_string(a.size()));
+      set({Role::In0, Role::In1, Role::Out, Role::Count});
+      return true;
+    case KernelId::ScaleBias:
+      if (a.size() != 5)
+        return fail("takes 5 arguments (in, out, scale, bias, n), found " + std::to_string(a.size()));
+      set({Role::In0, Role::Out, Role::Scale, Role::Bias, Role::Count});
+      return true;
+    case KernelId::Softmax:
+      if (a.size() != 5)
+        return fail("takes 5 arguments (in, out, in_row_stride, out_row_stride, n_cols), found " +
+                    std::to_string(a.size()));
+      set({Role::In0, Role::Out, Role::StrideIn, Role::StrideOut, Role::NCols});
+      return true;
     default:
       return fail("is not a known entry");
   }
@@ -164,7 +191,7 @@ bool assign_positional(KernelDesc& d, std::string& err) {
 
 bool assign_roles(KernelDesc& d, std::string& err) {
   // By name when every argument has a recognisable role name, else by position.
-  bool all_named = !d.args.empty();
+  bool all_named = !d.args.empty() && !is_rowwise(d.id);
   std::set<int> seen;
   for (auto& a : d.args) {
     Role r = role_from_name(d.id, a.name);
@@ -214,7 +241,7 @@ bool assign_roles(KernelDesc& d, std::string& err) {
     switch (a.role) {
       case Role::A: case Role::B: case Role::C: case Role::Q: case Role::Kt: case Role::V:
       case Role::O: case Role::DO: case Role::DQ: case Role::DK: case Role::DV: case Role::L:
-      case Role::Delta:
+      case Role::Delta: case Role::In0: case Role::In1: case Role::Out:
         want_ptr = true; break;
       default: break;
     }
@@ -228,7 +255,7 @@ bool assign_roles(KernelDesc& d, std::string& err) {
       err = "unsupported type '" + a.dtype + "' at line 0, col 0";
       return false;
     }
-    if (a.role == Role::SmScale && a.dtype != "f32") {
+    if ((a.role == Role::SmScale || a.role == Role::Scale || a.role == Role::Bias) && a.dtype != "f32") {
       err = "unsupported type '" + a.dtype + "' at line 0, col 0";
       return false;
     }
@@ -333,8 +360,9 @@ bool scan_module(const std::string& ttir, int num_simdgroups, std::vector<Kernel
     }
     if (!known) {
       error = "unimplemented: kernel '" + name + "' at " + loc_str(loc_of(ttir, header)) +
-              " has no sm_100a implementation in libtmcuda (available: attn_bwd_dkdv, attn_bwd_dq, "
-              "attn_bwd_preprocess, attn_fwd, matmul_kernel)";
+              " has no sm_100a implementation in libtmcuda (available: add_kernel, attn_bwd_dkdv, "
+              "attn_bwd_dq, attn_bwd_preprocess, attn_fwd, copy_kernel, matmul_kernel, mul_kernel, "
+              "scale_bias_kernel, softmax_kernel)";
       return false;
     }
     auto pieces = split_top(ttir.substr(open + 1, close - open - 1), open + 1);
@@ -392,6 +420,47 @@ bool scan_module(const std::string& ttir, int num_simdgroups, std::vector<Kernel
     size_t next_func = ttir.find("tt.func", close);
     std::string body = ttir.substr(close, next_func == std::string::npos ? std::string::npos
                                                                          : next_func - close);
+    if (is_rowwise(d.id)) {
+      // BLOCK is the extent of the first tt.make_range; the body must hold the operations the
+      // precompiled kernel of that name performs (a same-named kernel doing something else is
+      // refused rather than silently replaced).
+      if (d.elt != Elt::F32) {
+        error = "unsupported type '" + e0 + "' at " + loc_str(loc_of(ttir, header)) + ": " +
+                kernel_entry_name(d.id) + " is precompiled for f32 only";
+        return false;
+      }
+      size_t mr = body.find("tt.make_range");
+      size_t endk = mr == std::string::npos ? mr : body.find("end = ", mr);
+      int block = endk == std::string::npos ? 0 : std::atoi(body.c_str() + endk + 6);
+      if (block <= 0 || block > 65536) {
+        error = "lowering error at " + loc_str(loc_of(ttir, header)) + ": " + kernel_entry_name(d.id) +
+                " needs a tt.make_range {end = BLOCK} with 0 < BLOCK <= 65536";
+        return false;
+      }
+      auto has_op = [&](const char* op) { return body.find(op) != std::string::npos; };
+      bool ok_body = has_op("tt.load") && has_op("tt.store");
+      switch (d.id) {
+        case KernelId::VecCopy: ok_body = ok_body && !has_op("arith.addf") && !has_op("arith.mulf"); break;
+        case KernelId::VecAdd: ok_body = ok_body && has_op("arith.addf") && !has_op("arith.mulf"); break;
+        case KernelId::VecMul: ok_body = ok_body && has_op("arith.mulf") && !has_op("arith.addf"); break;
+        case KernelId::ScaleBias: ok_body = ok_body && has_op("arith.mulf") && has_op("arith.addf"); break;
+        case KernelId::Softmax:
+          ok_body = ok_body && has_op("tt.reduce") && has_op("math.exp") && has_op("arith.divf") &&
+                    has_op("arith.maxnumf");
+          break;
+        default: break;
+      }
+      if (!ok_body) {
+        error = "unimplemented: the body of '" + name + "' at " + loc_str(loc_of(ttir, header)) +
+                " is not the computation libtmcuda's precompiled " + kernel_entry_name(d.id) + " performs";
+        return false;
+      }
+      d.block_m = block;
+      d.threads = std::min(1024, std::max(32, num_simdgroups <= 0 ? 32 : num_simdgroups * 32));
+      out.push_back(d);
+      pos = close;
+      continue;
+    }
     size_t dot = body.find("tt.dot");
     int r0 = 0, r1 = 0;
     std::string te;
@@ -500,7 +569,7 @@ bool parse_descriptor(const std::string& text, std::vector<KernelDesc>& out, std
       std::string kind;
       int role = 0;
       ls >> a.index >> kind >> a.dtype >> role >> a.name;
-      if (ls.fail() || (kind != "pointer" && kind != "scalar") || role < 0 || role > (int)Role::NCtx)
+      if (ls.fail() || (kind != "pointer" && kind != "scalar") || role < 0 || role > (int)Role::Last)
         return bad(t);
       a.is_pointer = kind == "pointer";
       a.role = (Role)role;
@@ -532,6 +601,10 @@ std::string kernel_info_json(const std::vector<KernelDesc>& kernels) {
       case KernelId::Matmul: shape = {k.block_m, k.block_n}; break;
       case KernelId::AttnBwdPreprocess: shape = {k.block_m, k.head_dim}; break;
       case KernelId::AttnBwdDkdv: shape = {k.block_n, k.block_m}; break;
+      case KernelId::VecCopy: case KernelId::VecAdd: case KernelId::VecMul: case KernelId::ScaleBias:
+      case KernelId::Softmax:
+        shape = {k.block_m};
+        break;
       default: shape = {k.block_m, k.block_n}; break;
     }
     long long size = 1;

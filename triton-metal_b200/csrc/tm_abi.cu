@@ -265,6 +265,7 @@ bool sync_stream(std::string& err) {
 struct Decoded {
   std::map<int, std::shared_ptr<BufferObj>> buffers;   // by Role
   std::map<int, int64_t> ints;
+  std::map<int, float> floats;
   float sm_scale = 0.f;
 };
 
@@ -313,6 +314,7 @@ bool decode_args(KernelObj& k, const int32_t* kinds, const int64_t* values, int3
       float f;
       std::memcpy(&f, &bits, 4);
       if (a.role == Role::SmScale) out.sm_scale = f;
+      out.floats[(int)a.role] = f;
     } else {
       if (kinds[i] != 1 && kinds[i] != 3) {
         err = invalid_argument("argument " + std::to_string(i) + " of " +
@@ -399,6 +401,47 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
     }
     return true;
   };
+
+  if (is_rowwise(desc.id)) {
+    // ---- one-dimensional kernels: program p covers [p*BLOCK, (p+1)*BLOCK) (rows for softmax) ----
+    RowProblem p{};
+    p.id = desc.id;
+    BufferObj *in0 = buf(Role::In0), *in1 = buf(Role::In1), *outb = buf(Role::Out);
+    p.in0 = (const float*)in0->ptr;
+    p.in1 = in1 ? (const float*)in1->ptr : nullptr;
+    p.out = (float*)outb->ptr;
+    auto f = [&](Role r) {
+      auto it = d.floats.find((int)r);
+      return it == d.floats.end() ? 0.f : it->second;
+    };
+    p.scale = f(Role::Scale);
+    p.bias = f(Role::Bias);
+    const int64_t block = desc.block_m;
+    if (desc.id == KernelId::Softmax) {
+      p.rows = gx;
+      p.cols = std::min<int64_t>(get_int(d, Role::NCols, 0), block);
+      p.stride_in = get_int(d, Role::StrideIn, 0);
+      p.stride_out = get_int(d, Role::StrideOut, 0);
+      if (!nonneg(p.stride_in, "the input row stride") || !nonneg(p.stride_out, "the output row stride"))
+        return false;
+      if (p.cols <= 0) return true;
+      if (!check_extent(*in0, (p.rows - 1) * p.stride_in + p.cols - 1, 4, "the input", err)) return false;
+      if (!check_extent(*outb, (p.rows - 1) * p.stride_out + p.cols - 1, 4, "the output", err)) return false;
+    } else {
+      p.limit = std::min<int64_t>(get_int(d, Role::Count, 0), gx * block);
+      if (p.limit <= 0) return true;
+      if (!check_extent(*in0, p.limit - 1, 4, "the first input", err)) return false;
+      if (in1 && !check_extent(*in1, p.limit - 1, 4, "the second input", err)) return false;
+      if (!check_extent(*outb, p.limit - 1, 4, "the output", err)) return false;
+    }
+    prefetch_exposed(d);
+    for (int r = 0; r < repeats; ++r) {
+      std::string e = launch_rowwise(p, ctx);
+      if (!e.empty()) { err = cuda_error(e); return false; }
+    }
+    k.last_path = 1;
+    return true;
+  }
 
   if (desc.id == KernelId::Matmul) {
     GemmProblem p{};
@@ -823,7 +866,7 @@ int32_t tmx_kernel_set_option(int64_t kernel, const char* name, int64_t value) {
   if (!name) { store_error(invalid_argument("tmx_kernel_set_option received a NULL name")); return -1; }
   std::string n(name);
   if (n == "causal") {
-    if (k->desc.id == KernelId::Matmul || k->desc.id == KernelId::AttnBwdPreprocess) {
+    if (k->desc.id == KernelId::Matmul || k->desc.id == KernelId::AttnBwdPreprocess || is_rowwise(k->desc.id)) {
       store_error(invalid_argument(std::string("option 'causal' does not apply to ") +
                                    kernel_entry_name(k->desc.id)));
       return -1;

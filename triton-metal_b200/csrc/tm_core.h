@@ -25,8 +25,16 @@ enum class KernelId : int {
   AttnBwdPreprocess = 2,
   AttnBwdDq = 3,
   AttnBwdDkdv = 4,
-  Count = 5
+  // The one-dimensional kernels the reference's own ABI tests launch
+  // (Tests/TritonMetalCoreTests/Fixtures.swift, python/tests/test_plugin_shape.py).
+  VecCopy = 5,       // copy_kernel(in, out, n)
+  VecAdd = 6,        // add_kernel(a, b, out, n)
+  VecMul = 7,        // mul_kernel(a, b, out, n)
+  ScaleBias = 8,     // scale_bias_kernel(in, out, scale, bias, n)
+  Softmax = 9,       // softmax_kernel(in, out, in_row_stride, out_row_stride, n_cols)
+  Count = 10
 };
+inline bool is_rowwise(KernelId id) { return (int)id >= (int)KernelId::VecCopy; }
 
 const char* kernel_entry_name(KernelId id);
 
@@ -36,7 +44,10 @@ enum class Role : int {
   // matmul_kernel
   A, B, C, M, N, K, StrideAm, StrideAk, StrideBk, StrideBn, StrideCm, StrideCn,
   // attention kernels
-  Q, Kt, V, O, DO, DQ, DK, DV, L, Delta, SmScale, StrideHead, StrideSeq, StrideLse, NCtx
+  Q, Kt, V, O, DO, DQ, DK, DV, L, Delta, SmScale, StrideHead, StrideSeq, StrideLse, NCtx,
+  // one-dimensional kernels
+  In0, In1, Out, Count, Scale, Bias, StrideIn, StrideOut, NCols,
+  Last = NCols
 };
 
 struct ArgInfo {
@@ -93,6 +104,16 @@ struct AttnProblem {
   int causal;
 };
 
+// One launch of a one-dimensional kernel: `limit` elements (already clamped by the grid) for
+// the element-wise kernels; `rows` rows of `cols` columns (already clamped by BLOCK) for softmax.
+struct RowProblem {
+  KernelId id;
+  const float* in0; const float* in1; float* out;
+  int64_t limit;
+  float scale, bias;
+  int64_t rows, cols, stride_in, stride_out;
+};
+
 // Device status word: non-zero after a bounded wait inside a kernel gave up.
 struct DeviceStatus {
   unsigned int code;      // 0 ok
@@ -131,6 +152,8 @@ std::string launch_attn_fwd_tc(const AttnProblem& p, const LaunchCtx& ctx);
 bool attn_bwd_tc_eligible(const AttnProblem& p, std::string* why);
 std::string launch_attn_bwd_dq_tc(const AttnProblem& p, const LaunchCtx& ctx);
 std::string launch_attn_bwd_dkdv_tc(const AttnProblem& p, const LaunchCtx& ctx);
+
+std::string launch_rowwise(const RowProblem& p, const LaunchCtx& ctx);
 
 std::string launch_probe(const LaunchCtx& ctx, int* out_host);
 

@@ -9,7 +9,8 @@
 // three after a calibration run, best of two passes: GEMMBenchmark.swift:256-277, 414-421).
 // The MPS comparison columns are gone (no Metal here); a "% of peak" column against the
 // dense bf16 tensor-core figure given by --peak takes their place.  Added: --element
-// (f32|f16|bf16 for the GEMM sweep), --causal, --device.
+// (f32|f16|bf16 for the GEMM sweep), --causal, --device, and --stream (the one-dimensional
+// kernels of the reference's ABI tests, in GB/s of algorithmic traffic).
 //
 // Each winning configuration is verified against a CPU reference before it is printed,
 // as the reference does; the CPU code here is a checker, never a fallback.
@@ -269,6 +270,9 @@ struct Options {
   std::vector<std::vector<int>> shapes{{1, 8, 512, 64}, {1, 8, 1024, 64}, {1, 16, 2048, 64}};
   std::string attn_element = "f32";
   double peak_tflops = 0;
+  bool stream = false;                    // --stream: the one-dimensional kernels, in GB/s
+  size_t stream_n = (size_t)1 << 27;
+  double peak_gbs = 0;
 };
 
 std::vector<float> closed_form(size_t n, int modulus, float scale, float shift) {
@@ -472,6 +476,97 @@ void run_attention(const Options& opt, bool backward) {
   }
 }
 
+// ---- the one-dimensional kernels (HBM-bound): GB/s of algorithmic traffic -----------------
+std::string index_lines(int block, const char* count) {
+  char b[1024];
+  std::snprintf(b, sizeof b,
+                "    %%block = arith.constant %d : i32\n    %%pid = tt.get_program_id x : i32\n"
+                "    %%first = arith.muli %%pid, %%block : i32\n"
+                "    %%lane = tt.make_range {end = %d : i32, start = 0 : i32} : tensor<%dxi32>\n"
+                "    %%firsts = tt.splat %%first : i32 -> tensor<%dxi32>\n"
+                "    %%index = arith.addi %%firsts, %%lane : tensor<%dxi32>\n"
+                "    %%counts = tt.splat %s : i32 -> tensor<%dxi32>\n"
+                "    %%mask = arith.cmpi slt, %%index, %%counts : tensor<%dxi32>\n",
+                block, block, block, block, block, count, block, block);
+  return b;
+}
+std::string load_lines(int block, const char* v, const char* ptr) {
+  char b[1024];
+  std::snprintf(b, sizeof b,
+                "    %%%s_base = tt.splat %s : !tt.ptr<f32> -> tensor<%dx!tt.ptr<f32>>\n"
+                "    %%%s_ptr = tt.addptr %%%s_base, %%index : tensor<%dx!tt.ptr<f32>>, tensor<%dxi32>\n"
+                "    %%%s = tt.load %%%s_ptr, %%mask : tensor<%dx!tt.ptr<f32>>\n",
+                v, ptr, block, v, v, block, block, v, v, block);
+  return b;
+}
+std::string store_lines(int block, const char* v, const char* ptr) {
+  char b[1024];
+  std::snprintf(b, sizeof b,
+                "    %%out_base = tt.splat %s : !tt.ptr<f32> -> tensor<%dx!tt.ptr<f32>>\n"
+                "    %%out_ptr = tt.addptr %%out_base, %%index : tensor<%dx!tt.ptr<f32>>, tensor<%dxi32>\n"
+                "    tt.store %%out_ptr, %%%s, %%mask : tensor<%dx!tt.ptr<f32>>\n    tt.return\n",
+                ptr, block, block, block, v, block);
+  return b;
+}
+std::string vector_ir(const std::string& kind, int block) {
+  const std::string t = "tensor<" + std::to_string(block) + "xf32>";
+  std::string head, body;
+  if (kind == "copy") {
+    head = "@copy_kernel(%arg0: !tt.ptr<f32>, %arg1: !tt.ptr<f32>, %arg2: i32)";
+    body = index_lines(block, "%arg2") + load_lines(block, "x", "%arg0") + store_lines(block, "x", "%arg1");
+  } else if (kind == "add" || kind == "mul") {
+    head = "@" + kind + "_kernel(%arg0: !tt.ptr<f32>, %arg1: !tt.ptr<f32>, %arg2: !tt.ptr<f32>, %arg3: i32)";
+    body = index_lines(block, "%arg3") + load_lines(block, "x", "%arg0") + load_lines(block, "y", "%arg1") +
+           "    %r = arith." + kind + "f %x, %y : " + t + "\n" + store_lines(block, "r", "%arg2");
+  } else {
+    head = "@scale_bias_kernel(%arg0: !tt.ptr<f32>, %arg1: !tt.ptr<f32>, %arg2: f32, %arg3: f32, %arg4: i32)";
+    body = index_lines(block, "%arg4") + load_lines(block, "x", "%arg0") + "    %scales = tt.splat %arg2 : f32 -> " + t +
+           "\n    %scaled = arith.mulf %x, %scales : " + t + "\n    %biases = tt.splat %arg3 : f32 -> " + t +
+           "\n    %r = arith.addf %scaled, %biases : " + t + "\n" + store_lines(block, "r", "%arg1");
+  }
+  return "module {\n  tt.func public " + head + " {\n" + body + "  }\n}\n";
+}
+
+void run_stream(const Options& opt) {
+  const size_t n = opt.stream_n;
+  const int block = 1024;
+  std::vector<float> a = closed_form(n, 251, 1.f / 64, -1.5f), b = closed_form(n, 127, 1.f / 32, 0.25f);
+  auto bytes_of = [](const std::vector<float>& v) {
+    std::vector<uint8_t> o(v.size() * 4);
+    std::memcpy(o.data(), v.data(), o.size());
+    return o;
+  };
+  Buffer ba(n * 4), bb(n * 4), bo(n * 4);
+  ba.write(bytes_of(a));
+  bb.write(bytes_of(b));
+  std::printf("%-18s %12s %10s %10s %s\n", "kernel", "elements", "ms", "GB/s", opt.peak_gbs > 0 ? "of peak" : "");
+  for (const char* kind : {"copy", "add", "mul", "scale_bias"}) {
+    const std::string k = kind;
+    const std::string name = k + "_kernel";
+    Kernel kernel(vector_ir(k, block), name.c_str());
+    Launch l{{(int64_t)((n + block - 1) / block), 1, 1}, {}, {}};
+    const bool two = k == "add" || k == "mul";
+    l.buffer(ba);
+    if (two) l.buffer(bb);
+    l.buffer(bo);
+    if (k == "scale_bias") { l.f32(2.5f); l.f32(-1.75f); }
+    l.i32((int64_t)n);
+    run_once(kernel, l);
+    if (opt.verify) {
+      std::vector<uint8_t> raw = bo.read(n * 4);
+      const float* got = reinterpret_cast<const float*>(raw.data());
+      for (size_t i = 0; i < n; i += 997) {
+        float want = k == "copy" ? a[i] : k == "add" ? a[i] + b[i] : k == "mul" ? a[i] * b[i] : a[i] * 2.5f + -1.75f;
+        if (got[i] != want) die(name + ": element " + std::to_string(i) + " differs");
+      }
+    }
+    const double ms = measure({{&kernel, &l}});
+    const double gbs = (two ? 12.0 : 8.0) * n / (ms * 1e-3) / 1e9;
+    std::printf("%-18s %12zu %10.4f %10.1f %s\n", name.c_str(), n, ms, gbs,
+                opt.peak_gbs > 0 ? fmt("%.2f", gbs / opt.peak_gbs).c_str() : "");
+  }
+}
+
 std::vector<std::string> split(const std::string& s, char sep) {
   std::vector<std::string> out;
   std::stringstream ss(s);
@@ -510,11 +605,15 @@ int main(int argc, char** argv) {
     else if (a == "--probe") opt.probe = true;
     else if (a == "--verbose" || a == "-v") opt.verbose = true;
     else if (a == "--peak") opt.peak_tflops = std::atof(next().c_str());
+    else if (a == "--stream") opt.stream = true;
+    else if (a == "--stream-n") opt.stream_n = (size_t)std::atoll(next().c_str());
+    else if (a == "--peak-gbs") opt.peak_gbs = std::atof(next().c_str());
     else if (a == "--device") { if (tmx_set_device(std::atoi(next().c_str())) != 0) die(last_error()); }
     else if (a == "--help" || a == "-h") {
       std::printf("tmbench [--sizes 512,1024] [--config BM,BN,BK,W[;...]] [--element f32|f16|bf16]\n"
                   "        [--attn | --attn-bwd] [--attn-shapes B,H,S,D[;...]] [--attn-element f32|f16|bf16]\n"
-                  "        [--causal] [--no-verify] [--probe] [--verbose] [--peak TFLOPS] [--device N]\n");
+                  "        [--causal] [--no-verify] [--probe] [--verbose] [--peak TFLOPS] [--device N]\n"
+                  "        [--stream [--stream-n ELEMENTS] [--peak-gbs GBS]]\n");
       return 0;
     } else die("unknown argument " + a);
   }
@@ -528,7 +627,8 @@ int main(int argc, char** argv) {
     return opt.probe ? 0 : 1;
   }
   if (opt.probe) { std::printf("usable\n"); return 0; }
-  if (opt.attention) run_attention(opt, false);
+  if (opt.stream) run_stream(opt);
+  else if (opt.attention) run_attention(opt, false);
   else if (opt.attention_backward) run_attention(opt, true);
   else run_gemm(opt);
   return 0;

@@ -1,4 +1,5 @@
-"""The five hot kernels as callables over the `tm_*` ABI.
+"""The hot kernels (and the small kernels of the reference's ABI tests) as callables over
+the `tm_*` ABI.
 
 The reference reaches its kernels by handing Triton IR to `tm_emit_msl`
 (Sources/TritonMetalBench/{GEMMKernel,AttentionKernel,AttentionBackwardKernel}.swift
@@ -73,6 +74,103 @@ def attn_bwd_dkdv_ir(block_m=128, block_n=128, head_dim=128, element="f32", caus
             "%sm_scale: f32, %stride_head: i32, %stride_seq: i32, %stride_lse: i32, %N_CTX: i32")
     return _attn_ir("attn_bwd_dkdv", args, (block_n, head_dim), (head_dim, block_m),
                     (block_n, block_m), element, causal)
+
+
+# ---- the one-dimensional kernels of the reference's ABI tests -------------------------
+# (Tests/TritonMetalCoreTests/Fixtures.swift, python/tests/test_plugin_shape.py).  Full
+# programs, not signature stubs: libtmcuda checks that the body holds the operations its
+# precompiled kernel of that name performs.
+
+def _masked_index(block, count):
+    """pid*BLOCK + arange(BLOCK) and its `< n` mask, as SSA lines."""
+    return f"""    %block = arith.constant {block} : i32
+    %pid = tt.get_program_id x : i32
+    %first = arith.muli %pid, %block : i32
+    %lane = tt.make_range {{end = {block} : i32, start = 0 : i32}} : tensor<{block}xi32>
+    %firsts = tt.splat %first : i32 -> tensor<{block}xi32>
+    %index = arith.addi %firsts, %lane : tensor<{block}xi32>
+    %counts = tt.splat {count} : i32 -> tensor<{block}xi32>
+    %mask = arith.cmpi slt, %index, %counts : tensor<{block}xi32>
+"""
+
+
+def _load(block, value, pointer):
+    return f"""    %{value}_base = tt.splat {pointer} : !tt.ptr<f32> -> tensor<{block}x!tt.ptr<f32>>
+    %{value}_ptr = tt.addptr %{value}_base, %index : tensor<{block}x!tt.ptr<f32>>, tensor<{block}xi32>
+    %{value} = tt.load %{value}_ptr, %mask : tensor<{block}x!tt.ptr<f32>>
+"""
+
+
+def _store(block, value, pointer):
+    return f"""    %out_base = tt.splat {pointer} : !tt.ptr<f32> -> tensor<{block}x!tt.ptr<f32>>
+    %out_ptr = tt.addptr %out_base, %index : tensor<{block}x!tt.ptr<f32>>, tensor<{block}xi32>
+    tt.store %out_ptr, %{value}, %mask : tensor<{block}x!tt.ptr<f32>>
+    tt.return
+"""
+
+
+def elementwise_ir(kind, block):
+    """copy: out = in; add / mul: out = a (+|*) b; scale_bias: out = in * scale + bias."""
+    if kind == "copy":
+        head = "@copy_kernel(%arg0: !tt.ptr<f32>, %arg1: !tt.ptr<f32>, %arg2: i32)"
+        body = _masked_index(block, "%arg2") + _load(block, "x", "%arg0") + _store(block, "x", "%arg1")
+    elif kind in ("add", "mul"):
+        head = (f"@{kind}_kernel(%arg0: !tt.ptr<f32>, %arg1: !tt.ptr<f32>, %arg2: !tt.ptr<f32>, "
+                "%arg3: i32)")
+        body = (_masked_index(block, "%arg3") + _load(block, "x", "%arg0") + _load(block, "y", "%arg1")
+                + f"    %r = arith.{kind}f %x, %y : tensor<{block}xf32>\n" + _store(block, "r", "%arg2"))
+    elif kind == "scale_bias":
+        head = ("@scale_bias_kernel(%arg0: !tt.ptr<f32>, %arg1: !tt.ptr<f32>, %arg2: f32, %arg3: f32, "
+                "%arg4: i32)")
+        body = (_masked_index(block, "%arg4") + _load(block, "x", "%arg0")
+                + f"    %scales = tt.splat %arg2 : f32 -> tensor<{block}xf32>\n"
+                + f"    %scaled = arith.mulf %x, %scales : tensor<{block}xf32>\n"
+                + f"    %biases = tt.splat %arg3 : f32 -> tensor<{block}xf32>\n"
+                + f"    %r = arith.addf %scaled, %biases : tensor<{block}xf32>\n" + _store(block, "r", "%arg1"))
+    else:
+        raise ValueError(f"unknown element-wise kernel '{kind}'")
+    return f"module {{\n  tt.func public {head} {{\n{body}  }}\n}}\n"
+
+
+def softmax_ir(block):
+    """One program per row: exp(x - max) / sum over the first n_cols (< BLOCK) columns."""
+    t = f"tensor<{block}xf32>"
+    return f"""module {{
+  tt.func public @softmax_kernel(%arg0: !tt.ptr<f32>, %arg1: !tt.ptr<f32>, %arg2: i32, %arg3: i32, %arg4: i32) {{
+    %minus_inf = arith.constant dense<0xFF800000> : {t}
+    %row = tt.get_program_id x : i32
+    %in_off = arith.muli %row, %arg2 : i32
+    %in_row = tt.addptr %arg0, %in_off : !tt.ptr<f32>, i32
+    %col = tt.make_range {{end = {block} : i32, start = 0 : i32}} : tensor<{block}xi32>
+    %in_base = tt.splat %in_row : !tt.ptr<f32> -> tensor<{block}x!tt.ptr<f32>>
+    %in_ptr = tt.addptr %in_base, %col : tensor<{block}x!tt.ptr<f32>>, tensor<{block}xi32>
+    %ncols = tt.splat %arg4 : i32 -> tensor<{block}xi32>
+    %mask = arith.cmpi slt, %col, %ncols : tensor<{block}xi32>
+    %x = tt.load %in_ptr, %mask, %minus_inf : {t}
+    %max = "tt.reduce"(%x) <{{axis = 0 : i32}}> ({{
+    ^bb0(%a: f32, %b: f32):
+      %m = arith.maxnumf %a, %b : f32
+      tt.reduce.return %m : f32
+    }}) : ({t}) -> f32
+    %maxes = tt.splat %max : f32 -> {t}
+    %shifted = arith.subf %x, %maxes : {t}
+    %e = math.exp %shifted : {t}
+    %sum = "tt.reduce"(%e) <{{axis = 0 : i32}}> ({{
+    ^bb0(%c: f32, %d: f32):
+      %s = arith.addf %c, %d : f32
+      tt.reduce.return %s : f32
+    }}) : ({t}) -> f32
+    %sums = tt.splat %sum : f32 -> {t}
+    %y = arith.divf %e, %sums : {t}
+    %out_off = arith.muli %row, %arg3 : i32
+    %out_row = tt.addptr %arg1, %out_off : !tt.ptr<f32>, i32
+    %out_base = tt.splat %out_row : !tt.ptr<f32> -> tensor<{block}x!tt.ptr<f32>>
+    %out_ptr = tt.addptr %out_base, %col : tensor<{block}x!tt.ptr<f32>>, tensor<{block}xi32>
+    tt.store %out_ptr, %y, %mask : tensor<{block}x!tt.ptr<f32>>
+    tt.return
+  }}
+}}
+"""
 
 
 class Kernel:
@@ -202,6 +300,44 @@ class AttnBwdDkdv(Kernel):
 
     def __call__(self, *args):
         self.launch(*self.arguments(*args))
+
+
+class Elementwise(Kernel):
+    """copy / add / mul / scale_bias over n fp32 elements, BLOCK per program."""
+
+    NAMES = {"copy": "copy_kernel", "add": "add_kernel", "mul": "mul_kernel",
+             "scale_bias": "scale_bias_kernel"}
+
+    def __init__(self, kind, block=1024, num_warps=4):
+        super().__init__(elementwise_ir(kind, block), self.NAMES[kind], num_warps)
+        self.kind, self.block = kind, block
+
+    def arguments(self, *operands, n, scale=1.0, bias=0.0, programs=None):
+        """operands: buffer handles (in, out) or (a, b, out)."""
+        grid = (programs if programs is not None else max(1, cdiv(n, self.block)), 1, 1)
+        if self.kind == "scale_bias":
+            return grid, [B, B, F, F, I], [operands[0], operands[1], _core.float_bits(scale),
+                                           _core.float_bits(bias), n]
+        return grid, [B] * len(operands) + [I], list(operands) + [n]
+
+    def __call__(self, *operands, **kw):
+        self.launch(*self.arguments(*operands, **kw))
+
+
+class Softmax(Kernel):
+    """Row softmax, one program per row, n_cols <= BLOCK columns."""
+
+    def __init__(self, block=128, num_warps=4):
+        super().__init__(softmax_ir(block), "softmax_kernel", num_warps)
+        self.block = block
+
+    def arguments(self, x, y, rows, n_cols, stride_in=None, stride_out=None):
+        stride_in = n_cols if stride_in is None else stride_in
+        stride_out = n_cols if stride_out is None else stride_out
+        return (rows, 1, 1), [B, B, I, I, I], [x, y, stride_in, stride_out, n_cols]
+
+    def __call__(self, *a, **kw):
+        self.launch(*self.arguments(*a, **kw))
 
 
 def default_scale(head_dim):
