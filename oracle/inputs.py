@@ -43,3 +43,17 @@ def closed_form_tensor(shape, seed):
     n = int(np.prod(shape))
     i = np.arange(n, dtype=np.int64)
     return ((i % seed).astype(np.float32) / np.float32(seed) - np.float32(0.5)).reshape(shape)
+
+
+def sae_synthetic(shape, offset, modulus):
+    """Deterministic values in [-0.5, 0.5): ((i + offset) * 13 mod modulus) / modulus - 0.5
+    (python/examples/sae_encode.py:61-65)."""
+    count = int(np.prod(shape))
+    i = np.arange(count, dtype=np.int64)
+    return (((i + offset) * 13 % modulus) / modulus - 0.5).astype(np.float32).reshape(shape)
+
+
+def sae_inputs(rows, model, features):
+    """x, W_enc, b_enc of the example's checks (sae_encode.py:121-123)."""
+    return (sae_synthetic((rows, model), 1, 71), sae_synthetic((model, features), 7, 53),
+            sae_synthetic((features,), 3, 29))

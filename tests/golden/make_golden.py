@@ -8,7 +8,8 @@ It imports python/examples/attention_training.py and python/examples/matmul.py
 from that tree (their `triton_metal` shim needs a library exporting the tm_*
 symbols: TRITON_METAL_CORE_LIB is pointed at libtmcuda.so, nothing is launched)
 and stores the outputs of `numpy_attention`, `numpy_attention_backward` and
-`a @ b` on seeded inputs.  Inputs are not stored: the tests regenerate them from
+`a @ b` on seeded inputs, and of python/examples/sae_encode.py `reference` on that
+example's own `synthetic` inputs.  Inputs are not stored: the tests regenerate them from
 the seeds below.
 """
 
@@ -30,6 +31,10 @@ ATTENTION_CASES = [
     ("h2_s127_d64_seed3", 2, 127, 64, 3, 1.0),
     ("h3_s33_d80_seed5", 3, 33, 80, 5, 1.0),
 ]
+
+
+#: (rows, model width, features) - python/examples/sae_encode.py:120
+SAE_CASES = [(8, 64, 128), (64, 512, 2048), (100, 300, 700)]
 
 
 def attention_inputs(heads, seq, dim, seed, scale):
@@ -66,7 +71,21 @@ def main(reference_root):
     expected = a @ b          # python/examples/matmul.py:71
     np.savez_compressed(HERE / "matmul_reference.npz", rows=np.arange(0, 256, 16),
                         c_rows=expected[::16].copy(), checksum=np.float64(expected.astype(np.float64).sum()))
-    print("wrote", HERE / "attention_reference.npz", HERE / "matmul_reference.npz")
+    # python/examples/sae_encode.py: `reference` on its own `synthetic` inputs, the three
+    # shapes the example checks (:120) - sampled rows for the larger two
+    import sae_encode as sae
+    sae_out = {}
+    for rows, model, features in SAE_CASES:
+        x = sae.synthetic((rows, model), 1, 71)
+        w = sae.synthetic((model, features), 7, 53)
+        b = sae.synthetic((features,), 3, 29)
+        want = sae.reference(x.astype(np.float64), w.astype(np.float64), b.astype(np.float64))
+        key = f"m{rows}_d{model}_f{features}"
+        sae_out[key + ".rows"] = np.arange(0, rows, max(1, rows // 8))
+        sae_out[key + ".out"] = want[sae_out[key + ".rows"]].astype(np.float64)
+        sae_out[key + ".x0"] = x.reshape(-1)[:16].copy()       # pins the input generator too
+    np.savez_compressed(HERE / "sae_reference.npz", **sae_out)
+    print("wrote", HERE / "attention_reference.npz", HERE / "matmul_reference.npz", HERE / "sae_reference.npz")
 
 
 if __name__ == "__main__":

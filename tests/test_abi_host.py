@@ -87,6 +87,19 @@ def test_one_dimensional_kernels_scan(core):
     assert (info["name"], info["block_size"], info["threads_per_threadgroup"]) == ("softmax_kernel", 128, 64)
 
 
+def test_sae_encoder_scans(core):
+    """sae_encode_kernel(x, w, bias, out, M, D, F): block shape from its tt.dot
+    (Sources/TritonMetalMLX/SAEEncoder.swift:40-56)."""
+    info = json.loads(core.kernel_info(kernels.sae_encode_ir(64, 32, 16), 8))["kernels"][0]
+    assert (info["name"], info["block_shape"], info["block_size"]) == ("sae_encode_kernel", [64, 32], 2048)
+    assert info["threads_per_threadgroup"] == 256
+    assert [a["kind"] for a in info["args"]] == ["pointer"] * 4 + ["scalar"] * 3
+    with pytest.raises(RuntimeError, match="body of 'sae_encode_kernel'"):
+        core.emit_msl(kernels.sae_encode_ir().replace("arith.maximumf", "arith.minimumf"))
+    with pytest.raises(RuntimeError, match="f32 only"):
+        core.emit_msl(kernels.sae_encode_ir().replace("f32", "f16"))
+
+
 def test_a_same_named_kernel_with_another_body_is_refused(core):
     """The precompiled kernels are selected by name; a body that computes something else
     must not be replaced silently."""

@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                  const __grid_constant__ CUtensorMap map_bhi, const __grid_constant__ CUtensorMap map_blo,
                  float* __restrict__ C, int M, int N, int K, int64_t scm, int64_t scn, int vec_store,
-                 DeviceStatus* status) {
+                 const float* __restrict__ bias, int relu, DeviceStatus* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   SharedStorage& ss = *reinterpret_cast<SharedStorage*>(smem + STAGES * STAGE_BYTES);
@@ -251,6 +251,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
       const int col_base = tn * BN + half * 128;
       float* crow = C + (int64_t)row * scm + (int64_t)col_base * scn;
       const int cols_left = N - col_base;
+      if (bias || relu) {
+        // fused epilogue on the summed accumulator: + bias[column], then max(., 0)
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          float v = sums[i];
+          if (bias && i < cols_left) v += __ldg(bias + col_base + i);
+          sums[i] = relu ? fmaxf(v, 0.f) : v;
+        }
+      }
       if (row < M) {
         if (vec_store) {
 #pragma unroll
@@ -344,7 +353,7 @@ std::string run_gemm_tf32(const GemmProblem& p, const LaunchCtx& ctx, void* scra
   const int vec = p.scn == 1 && p.scm % 4 == 0 && ((uintptr_t)p.c % 16 == 0);
   gemm_tf32_kernel<<<grid, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], (float*)p.c,
                                                            (int)M, (int)N, (int)kp, p.scm, p.scn, vec,
-                                                           ctx.status);
+                                                           p.bias, p.relu, ctx.status);
   ++*ctx.launches;
   e = cudaGetLastError();
   if (e != cudaSuccess) return std::string("matmul_kernel launch failed: ") + cudaGetErrorString(e);

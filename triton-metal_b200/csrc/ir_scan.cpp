@@ -36,6 +36,7 @@ const char* kernel_entry_name(KernelId id) {
     case KernelId::VecMul: return "mul_kernel";
     case KernelId::ScaleBias: return "scale_bias_kernel";
     case KernelId::Softmax: return "softmax_kernel";
+    case KernelId::SaeEncode: return "sae_encode_kernel";
     default: return "?";
   }
 }
@@ -184,6 +185,11 @@ bool assign_positional(KernelDesc& d, std::string& err) {
                     std::to_string(a.size()));
       set({Role::In0, Role::Out, Role::StrideIn, Role::StrideOut, Role::NCols});
       return true;
+    case KernelId::SaeEncode:
+      if (a.size() != 7)
+        return fail("takes 7 arguments (x, w, bias, out, M, D, F), found " + std::to_string(a.size()));
+      set({Role::A, Role::B, Role::BiasVec, Role::C, Role::M, Role::K, Role::N});
+      return true;
     default:
       return fail("is not a known entry");
   }
@@ -191,7 +197,7 @@ bool assign_positional(KernelDesc& d, std::string& err) {
 
 bool assign_roles(KernelDesc& d, std::string& err) {
   // By name when every argument has a recognisable role name, else by position.
-  bool all_named = !d.args.empty() && !is_rowwise(d.id);
+  bool all_named = !d.args.empty() && !is_rowwise(d.id) && d.id != KernelId::SaeEncode;
   std::set<int> seen;
   for (auto& a : d.args) {
     Role r = role_from_name(d.id, a.name);
@@ -241,7 +247,7 @@ bool assign_roles(KernelDesc& d, std::string& err) {
     switch (a.role) {
       case Role::A: case Role::B: case Role::C: case Role::Q: case Role::Kt: case Role::V:
       case Role::O: case Role::DO: case Role::DQ: case Role::DK: case Role::DV: case Role::L:
-      case Role::Delta: case Role::In0: case Role::In1: case Role::Out:
+      case Role::Delta: case Role::In0: case Role::In1: case Role::Out: case Role::BiasVec:
         want_ptr = true; break;
       default: break;
     }
@@ -362,7 +368,7 @@ bool scan_module(const std::string& ttir, int num_simdgroups, std::vector<Kernel
       error = "unimplemented: kernel '" + name + "' at " + loc_str(loc_of(ttir, header)) +
               " has no sm_100a implementation in libtmcuda (available: add_kernel, attn_bwd_dkdv, "
               "attn_bwd_dq, attn_bwd_preprocess, attn_fwd, copy_kernel, matmul_kernel, mul_kernel, "
-              "scale_bias_kernel, softmax_kernel)";
+              "sae_encode_kernel, scale_bias_kernel, softmax_kernel)";
       return false;
     }
     auto pieces = split_top(ttir.substr(open + 1, close - open - 1), open + 1);
@@ -461,6 +467,20 @@ bool scan_module(const std::string& ttir, int num_simdgroups, std::vector<Kernel
       pos = close;
       continue;
     }
+    if (d.id == KernelId::SaeEncode) {
+      auto has_op = [&](const char* op) { return body.find(op) != std::string::npos; };
+      if (d.elt != Elt::F32) {
+        error = "unsupported type '" + e0 + "' at " + loc_str(loc_of(ttir, header)) +
+                ": sae_encode_kernel is precompiled for f32 only";
+        return false;
+      }
+      if (!(has_op("tt.dot") && has_op("arith.addf") && has_op("arith.maximumf") && has_op("tt.store"))) {
+        error = "unimplemented: the body of '" + name + "' at " + loc_str(loc_of(ttir, header)) +
+                " is not the computation libtmcuda's precompiled sae_encode_kernel performs "
+                "(relu(x @ w + bias))";
+        return false;
+      }
+    }
     size_t dot = body.find("tt.dot");
     int r0 = 0, r1 = 0;
     std::string te;
@@ -471,7 +491,7 @@ bool scan_module(const std::string& ttir, int num_simdgroups, std::vector<Kernel
       if (colon != std::string::npos && parse_tensor_2d(body, colon, a0, a1, te, &p1) &&
           parse_tensor_2d(body, p1, b0, b1, te, &p2)) {
         // lhs [a0 x a1] * rhs [b0 x b1]
-        if (d.id == KernelId::Matmul) { d.block_m = a0; d.block_k = a1; d.block_n = b1; }
+        if (d.id == KernelId::Matmul || d.id == KernelId::SaeEncode) { d.block_m = a0; d.block_k = a1; d.block_n = b1; }
         else if (d.id == KernelId::AttnBwdDkdv) { d.block_n = a0; d.head_dim = a1; d.block_m = b1; }
         else { d.block_m = a0; d.head_dim = a1; d.block_n = b1; }
       }
@@ -598,7 +618,7 @@ std::string kernel_info_json(const std::vector<KernelDesc>& kernels) {
     auto& k = kernels[i];
     std::vector<int> shape;
     switch (k.id) {
-      case KernelId::Matmul: shape = {k.block_m, k.block_n}; break;
+      case KernelId::Matmul: case KernelId::SaeEncode: shape = {k.block_m, k.block_n}; break;
       case KernelId::AttnBwdPreprocess: shape = {k.block_m, k.head_dim}; break;
       case KernelId::AttnBwdDkdv: shape = {k.block_n, k.block_m}; break;
       case KernelId::VecCopy: case KernelId::VecAdd: case KernelId::VecMul: case KernelId::ScaleBias:

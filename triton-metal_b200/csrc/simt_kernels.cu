@@ -54,7 +54,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int64_t M,
                  int64_t N, int64_t K, int64_t sam, int64_t sak, int64_t sbk, int64_t sbn,
-                 int64_t scm, int64_t scn) {
+                 int64_t scm, int64_t scn, const float* __restrict__ bias, int relu) {
   __shared__ float As[16][64 + 4];
   __shared__ float Bs[16][64 + 4];
   const int tid = threadIdx.x;
@@ -105,7 +105,13 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       int64_t n = n0 + tx * 4 + j;
-      if (n < N) C[m * scm + n * scn] = from_f32<T>(acc[i][j]);
+      if (n < N) {
+        // optional fused epilogue: + bias[n], then max(., 0), on the accumulator
+        float v = acc[i][j];
+        if (bias) v += bias[n];
+        if (relu) v = fmaxf(v, 0.f);
+        C[m * scm + n * scn] = from_f32<T>(v);
+      }
     }
   }
 }
@@ -487,7 +493,7 @@ std::string launch_gemm_simt(const GemmProblem& p, const LaunchCtx& ctx) {
   dim3 grid((unsigned)gm, (unsigned)gn, 1);
   TM_DISPATCH_ELT(p.elt, (gemm_simt_kernel<T><<<grid, 256, 0, ctx.stream>>>(
                              (const T*)p.a, (const T*)p.b, (T*)p.c, p.M, p.N, p.K, p.sam, p.sak,
-                             p.sbk, p.sbn, p.scm, p.scn)));
+                             p.sbk, p.sbn, p.scm, p.scn, p.bias, p.relu)));
   ++*ctx.launches;
   return check_launch("matmul_kernel");
 }

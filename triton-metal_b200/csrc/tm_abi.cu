@@ -443,10 +443,11 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
     return true;
   }
 
-  if (desc.id == KernelId::Matmul) {
+  if (desc.id == KernelId::Matmul || desc.id == KernelId::SaeEncode) {
     GemmProblem p{};
     p.elt = desc.elt;
     int64_t M = get_int(d, Role::M, 0), N = get_int(d, Role::N, 0), K = get_int(d, Role::K, 0);
+    const bool sae = desc.id == KernelId::SaeEncode;   // relu(x @ w + bias), row-major, no strides
     p.sam = get_int(d, Role::StrideAm, K);   // absent strides: row-major with unit inner stride
     p.sak = get_int(d, Role::StrideAk, 1);
     p.sbk = get_int(d, Role::StrideBk, N);
@@ -469,6 +470,12 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
       if (!check_extent(*B, (K - 1) * p.sbk + (N - 1) * p.sbn, eb, "B", err)) return false;
     }
     if (!check_extent(*C, (M - 1) * p.scm + (N - 1) * p.scn, eb, "C", err)) return false;
+    if (sae) {
+      BufferObj* bias = buf(Role::BiasVec);
+      if (!check_extent(*bias, N - 1, 4, "the bias", err)) return false;
+      p.bias = (const float*)bias->ptr;
+      p.relu = 1;
+    }
     prefetch_exposed(d);
     std::string why;
     const bool f32 = p.elt == Elt::F32;

@@ -32,9 +32,14 @@ enum class KernelId : int {
   VecMul = 7,        // mul_kernel(a, b, out, n)
   ScaleBias = 8,     // scale_bias_kernel(in, out, scale, bias, n)
   Softmax = 9,       // softmax_kernel(in, out, in_row_stride, out_row_stride, n_cols)
-  Count = 10
+  // The fused sparse-autoencoder encoder, out = relu(x @ w + bias), fp32, row-major
+  // (Sources/TritonMetalMLX/SAEEncoder.swift:40-200): the matmul with an epilogue.
+  SaeEncode = 10,    // sae_encode_kernel(x, w, bias, out, M, D, F)
+  Count = 11
 };
-inline bool is_rowwise(KernelId id) { return (int)id >= (int)KernelId::VecCopy; }
+inline bool is_rowwise(KernelId id) {
+  return (int)id >= (int)KernelId::VecCopy && (int)id <= (int)KernelId::Softmax;
+}
 
 const char* kernel_entry_name(KernelId id);
 
@@ -47,7 +52,9 @@ enum class Role : int {
   Q, Kt, V, O, DO, DQ, DK, DV, L, Delta, SmScale, StrideHead, StrideSeq, StrideLse, NCtx,
   // one-dimensional kernels
   In0, In1, Out, Count, Scale, Bias, StrideIn, StrideOut, NCols,
-  Last = NCols
+  // sae_encode_kernel (x, w, out, M, D, F reuse A, B, C, M, K, N)
+  BiasVec,
+  Last = BiasVec
 };
 
 struct ArgInfo {
@@ -86,6 +93,9 @@ struct GemmProblem {
   const void* a; const void* b; void* c;
   int64_t M, N, K;                 // effective extents (already clamped by the grid)
   int64_t sam, sak, sbk, sbn, scm, scn;   // strides in elements
+  // fused epilogue (fp32 kernels only): C = max(acc + bias[n], 0) when `relu`; bias may be null
+  const float* bias = nullptr;
+  int relu = 0;
 };
 
 struct AttnProblem {

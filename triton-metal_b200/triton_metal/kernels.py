@@ -173,6 +173,25 @@ def softmax_ir(block):
 """
 
 
+def sae_encode_ir(block_m=64, block_f=64, block_d=16):
+    """out = relu(x @ w + bias), fp32, row-major (Sources/TritonMetalMLX/SAEEncoder.swift:40-200).
+    Signature-level like the matmul: the header, the tt.dot that carries the BLOCK shape and the
+    epilogue operations libtmcuda checks for (+ bias, maximum with 0, store)."""
+    t = f"tensor<{block_m}x{block_f}xf32>"
+    return f"""module {{
+  tt.func public @sae_encode_kernel(
+      %x: !tt.ptr<f32>, %w: !tt.ptr<f32>, %bias: !tt.ptr<f32>, %out: !tt.ptr<f32>,
+      %M: i32, %D: i32, %F: i32) {{
+    %acc = tt.dot %xv, %wv, %zero, inputPrecision = tf32 : tensor<{block_m}x{block_d}xf32> * tensor<{block_d}x{block_f}xf32> -> {t}
+    %biased = arith.addf %acc, %b_bcast : {t}
+    %activated = arith.maximumf %biased, %relu0 : {t}
+    tt.store %o_ptrs, %activated, %o_mask : tensor<{block_m}x{block_f}x!tt.ptr<f32>>
+    tt.return
+  }}
+}}
+"""
+
+
 class Kernel:
     """emit -> compile -> load, the flow of MetalUtils.load_binary
     (python/plugin/backend/driver.py:31-40); `release()` drops both handles."""
@@ -300,6 +319,21 @@ class AttnBwdDkdv(Kernel):
 
     def __call__(self, *args):
         self.launch(*self.arguments(*args))
+
+
+class SaeEncode(Kernel):
+    """out[M, F] = relu(x[M, D] @ w[D, F] + bias[F]); grid (cdiv(M, BM), cdiv(F, BF))."""
+
+    def __init__(self, block=(64, 64, 16), num_warps=4):
+        super().__init__(sae_encode_ir(*block), "sae_encode_kernel", num_warps)
+        self.block = block
+
+    def arguments(self, x, w, bias, out, rows, model, features):
+        grid = (cdiv(rows, self.block[0]), cdiv(features, self.block[1]), 1)
+        return grid, [B, B, B, B, I, I, I], [x, w, bias, out, rows, model, features]
+
+    def __call__(self, *a):
+        self.launch(*self.arguments(*a))
 
 
 class Elementwise(Kernel):
