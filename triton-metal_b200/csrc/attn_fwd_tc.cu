@@ -53,7 +53,7 @@ constexpr float kRescaleThreshold = 8.0f;
 
 enum Site : uint32_t {
   kLoadQEmpty = 10, kLoadKEmpty = 11, kLoadVEmpty = 12, kMmaQ = 13, kMmaK = 14, kMmaV = 15, kMmaP = 16,
-  kSoftS = 17, kSoftPv = 18, kSoftFinal = 19, kDrainLoad = 20
+  kSoftS = 17, kSoftFinal = 19, kDrainLoad = 20
 };
 
 struct Shared {
@@ -348,7 +348,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                              tmem + S_COL + t * BLOCK_N + (kk / 4) * HALF_N + (kk % 4) * 8,
                              vb.at(kk * 2048), idesc_pv, (j | kk) != 0);
                 }
-                mma_commit(smem_u32(&ss.pv_done[t]));
+                // O_t is only read after the last block; rescales in between are ordered by the
+                // next s_full (a commit covers every MMA issued before it, P.V(j) included)
+                if (j + 1 == nb[t]) mma_commit(smem_u32(&ss.pv_done[t]));
               }
               // V(j) has been read by both tiles: release it as early as possible
               if (t == TILES - 1) mma_commit(smem_u32(&ss.v_empty[s]));
@@ -380,10 +382,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const float qk_scale = prm.sm_scale * kLog2e;
     const int pair_barrier = 1 + t;               // named barrier of the tile's 256 threads
     uint32_t c = 0;                               // score blocks this tile has consumed
+    uint32_t item = 0;                            // query blocks done (phase of pv_done)
     bool ok = true;
     for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
       const int bh = sch.head(u);
-      for (int sub = 0; sub < sch.subs(u) && ok; ++sub) {
+      for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
         const int m0 = sch.block(u, sub) * (TILES * BLOCK_M);
         const int q_row = m0 + t * BLOCK_M + row_in_tile;
         const int my_blocks = key_blocks(m0, t);
@@ -410,10 +413,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             rescale = j > 0;
           }
           if (__any_sync(0xffffffffu, rescale)) {
-            // O_t may only be touched once the P.V MMA of block j-1 has finished; each half
-            // rescales its own D/2 columns of the accumulator
-            if (!mbar_wait(smem_u32(&ss.pv_done[t]), (c - 1) & 1, wc, kSoftPv)) { ok = false; break; }
-            tc_fence_after();
+            // O_t may only be touched once the P.V MMA of block j-1 has finished: it has, the
+            // s_full this thread waited for above was committed after it.  Each half rescales
+            // its own D/2 columns of the accumulator.
 #pragma unroll 1
             for (int cc = 0; cc < D / 64; ++cc) {
               uint32_t r[32];
@@ -438,7 +440,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         ss.half_sum[t][half][row_in_tile] = l;
         asm volatile("bar.sync %0, 256;" ::"r"(pair_barrier) : "memory");
         l += ss.half_sum[t][half ^ 1][row_in_tile];
-        if (ok && my_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done[t]), (c - 1) & 1, wc, kSoftFinal);
+        if (ok && my_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done[t]), item & 1, wc, kSoftFinal);
         tc_fence_after();
         if (ok && my_blocks > 0) {
           const float inv_l = 1.f / l;
