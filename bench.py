@@ -286,24 +286,38 @@ class GemmJob:
                 work.wait()      # the library's stream waits; the host does not
 
     def e2e_setup(self):
-        b = self.b_host
-        self.pin_a = []
+        """Pinned host copies of A (in row pieces), B and C, and per-piece device buffers: a piece's
+        C is read back on the library's side stream while the next piece's A goes up and its GEMM
+        runs, so the two PCIe directions and the tensor cores work at the same time."""
+        from triton_metal import cuda
+        w, b = self.w, self.b_host
+        self.pieces = []
+        # plain device memory for everything the copies touch (managed memory copies slower)
+        self.b_e2e = cuda.alloc_device_buffer(b.nbytes)
+        sub = max(1, min(8, self.block // 1024))       # pieces per row block
+        rows = self.block // sub
         for a in self.a_host:
-            p = pinned(a.nbytes)
-            p.numpy()[:] = a.reshape(-1).view(np.uint8)
-            self.pin_a.append(p)
+            for i in range(sub):
+                part = a[i * rows:(i + 1) * rows] if i + 1 < sub else a[i * rows:]
+                pin_a = pinned(part.nbytes)
+                pin_a.numpy()[:] = np.ascontiguousarray(part).reshape(-1).view(np.uint8)
+                n_rows = part.shape[0]
+                a_buf = cuda.alloc_device_buffer(part.nbytes)
+                c_buf = cuda.alloc_device_buffer(n_rows * w["N"] * 2)
+                args = self.kernel.arguments(a_buf, self.b_e2e, c_buf, n_rows, w["N"], w["K"])
+                self.pieces.append((pin_a, a_buf, c_buf, pinned(n_rows * w["N"] * 2), args))
         self.pin_b = pinned(b.nbytes)
         self.pin_b.numpy()[:] = b.reshape(-1).view(np.uint8)
-        self.pin_c = [pinned(self.block * self.w["N"] * 2) for _ in range(self.chunks)]
-        return sum(a.nbytes for a in self.a_host) + b.nbytes, self.rows * self.w["N"] * 2
+        return sum(a.nbytes for a in self.a_host) + b.nbytes, self.rows * w["N"] * 2
 
     def e2e_step(self):
-        c = self.core
-        c.buffer_write(self.b, 0, self.pin_b.data_ptr(), self.pin_b.numel())
-        for i in range(self.chunks):
-            c.buffer_write(self.a[i], 0, self.pin_a[i].data_ptr(), self.pin_a[i].numel())
-            self.kernel.launch(*self.args[i])
-            c.buffer_read(self.c_local[i], 0, self.pin_c[i].data_ptr(), self.pin_c[i].numel())
+        from triton_metal import cuda
+        cuda.write_async(self.b_e2e, 0, self.pin_b.data_ptr(), self.pin_b.numel())
+        for pin_a, a_buf, c_buf, pin_c, args in self.pieces:
+            cuda.write_async(a_buf, 0, pin_a.data_ptr(), pin_a.numel())
+            self.kernel.launch_async(*args)
+            cuda.read_async(c_buf, 0, pin_c.data_ptr(), pin_c.numel())
+        cuda.synchronize()           # every piece of C is in host memory
 
     def sample_rows(self, rows):
         """(A rows as bf16 words, GPU result rows) of the first block, for the checker."""

@@ -138,7 +138,11 @@ int32_t tmx_launch_timed(int64_t kernel, int64_t grid_x, int64_t grid_y, int64_t
 /* Wait for everything enqueued on the library's stream; surfaces device-side
  * status words (bounded waits that gave up) as -1. */
 int32_t tmx_synchronize(void);
-/* Asynchronous copies on the library's stream (host memory should be pinned). */
+/* Asynchronous copies (host memory should be pinned).  A write is ordered on the library's
+ * stream.  A read starts after everything enqueued before it but runs on a side stream, so it
+ * overlaps the writes and launches enqueued after it: a buffer being read back must not be
+ * written by later work until tmx_synchronize, tmx_timer_end or any blocking tm_* call has
+ * returned (they wait for the read-backs too). */
 int32_t tmx_buffer_write_async(int64_t buffer, int64_t offset, const void *source, int64_t length);
 int32_t tmx_buffer_read_async(int64_t buffer, int64_t offset, void *destination, int64_t length);
 /* Fill `length` bytes of the buffer with `byte` (asynchronous). */

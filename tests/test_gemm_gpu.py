@@ -247,3 +247,47 @@ def test_device_only_buffers(core):
         core.free_buffer(c)
         ab.free()
         bb.free()
+
+
+def test_pipelined_pieces_with_side_stream_read_back(core):
+    """Asynchronous writes and launches on the library's stream, read-backs on its side stream:
+    four row pieces in flight give the same C as one blocking launch, and tmx_synchronize /
+    tmx_timer_end wait for the read-backs."""
+    from triton_metal import kernels
+    m, n, k, pieces = 1024, 512, 256, 4
+    a, b = inputs.gemm_normal(m, n, k, seed=9)
+    a, b = ref.round_to(a, "bf16"), ref.round_to(b, "bf16")
+    dt = ref.storage_dtype("bf16")
+    a_host, b_host = np.ascontiguousarray(a.astype(dt)), np.ascontiguousarray(b.astype(dt))
+    rows = m // pieces
+    mm = kernels.Matmul("bf16")
+    bb = core.alloc_buffer(b_host.nbytes)
+    a_bufs = [core.alloc_buffer(rows * k * 2) for _ in range(pieces)]
+    c_bufs = [cuda.alloc_device_buffer(rows * n * 2) for _ in range(pieces)]
+    outs = [np.zeros((rows, n), dtype=dt) for _ in range(pieces)]
+    parts = [np.ascontiguousarray(a_host[i * rows:(i + 1) * rows]) for i in range(pieces)]
+    try:
+        for rounds in range(2):                       # the second round reuses every buffer
+            cuda.timer_begin()
+            cuda.write_async(bb, 0, b_host.ctypes.data, b_host.nbytes)
+            for i in range(pieces):
+                cuda.write_async(a_bufs[i], 0, parts[i].ctypes.data, parts[i].nbytes)
+                mm.launch_async(*mm.arguments(a_bufs[i], bb, c_bufs[i], rows, n, k))
+                cuda.read_async(c_bufs[i], 0, outs[i].ctypes.data, outs[i].nbytes)
+            assert cuda.timer_end() > 0               # waits for the side stream as well
+            got = np.concatenate(outs).astype(np.float32)
+            assert ref.relative_error(got, ref.matmul(a, b)) <= 2e-2
+            for o in outs:
+                o[:] = 0
+        whole, _ = tmtest.run_matmul(a, b, "bf16", (128, 256, 64))
+        cuda.write_async(bb, 0, b_host.ctypes.data, b_host.nbytes)
+        for i in range(pieces):
+            cuda.write_async(a_bufs[i], 0, parts[i].ctypes.data, parts[i].nbytes)
+            mm.launch_async(*mm.arguments(a_bufs[i], bb, c_bufs[i], rows, n, k))
+            cuda.read_async(c_bufs[i], 0, outs[i].ctypes.data, outs[i].nbytes)
+        cuda.synchronize()
+        assert np.array_equal(np.concatenate(outs).astype(np.float32), whole)
+    finally:
+        mm.release()
+        for h in [bb] + a_bufs + c_bufs:
+            core.free_buffer(h)

@@ -149,6 +149,11 @@ struct Device {
   int count = 0;
   cudaDeviceProp prop{};
   cudaStream_t stream = nullptr;
+  // device -> host copies of tmx_buffer_read_async run here, behind an event on `stream`, so
+  // that they overlap the host -> device copies and kernels enqueued after them
+  cudaStream_t read_stream = nullptr;
+  cudaEvent_t ev_read = nullptr, ev_join = nullptr;
+  bool reads_in_flight = false;
   DeviceStatus* status = nullptr;   // pinned, device-visible
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   // capability probe
@@ -195,6 +200,10 @@ bool ensure_device(std::string& err) {
   std::memset(g_dev.status, 0, sizeof(DeviceStatus));
   cudaEventCreate(&g_dev.ev_begin);
   cudaEventCreate(&g_dev.ev_end);
+  if ((e = cudaStreamCreateWithFlags(&g_dev.read_stream, cudaStreamNonBlocking)) != cudaSuccess)
+    return fail(std::string("could not create the read-back stream: ") + cudaGetErrorString(e));
+  cudaEventCreateWithFlags(&g_dev.ev_read, cudaEventDisableTiming);
+  cudaEventCreateWithFlags(&g_dev.ev_join, cudaEventDisableTiming);
   g_dev.ok = true;
   return true;
 }
@@ -241,7 +250,16 @@ const std::string& unusable_reason() {
 }
 
 // Wait for the stream and surface device-side status.
+// Make the library's stream wait for the read-backs enqueued on the side stream.
+void join_reads() {
+  if (!g_dev.reads_in_flight) return;
+  cudaEventRecord(g_dev.ev_join, g_dev.read_stream);
+  cudaStreamWaitEvent(g_dev.stream, g_dev.ev_join, 0);
+  g_dev.reads_in_flight = false;
+}
+
 bool sync_stream(std::string& err) {
+  join_reads();
   cudaError_t e = cudaStreamSynchronize(g_dev.stream);
   if (e != cudaSuccess) {
     err = cuda_error(std::string("kernel execution failed: ") + cudaGetErrorString(e));
@@ -603,7 +621,7 @@ int32_t do_launch(int64_t kernel, int64_t gx, int64_t gy, int64_t gz, int64_t th
 }
 
 int32_t do_copy(int64_t buffer, int64_t offset, const void* host, int64_t length, bool to_device,
-                bool wait) {
+                bool wait, bool side_stream = false) {
   // NULL / negative bounds are refused before the handle is looked at
   // (Compiler.swift:354-357).
   if (!host || length < 0 || offset < 0) {
@@ -622,9 +640,17 @@ int32_t do_copy(int64_t buffer, int64_t offset, const void* host, int64_t length
   if (length == 0) return 0;
   if (!bind_device(err)) { store_error(err); return -1; }
   char* dev = (char*)b->ptr + offset;
+  cudaStream_t copy_stream = g_dev.stream;
+  if (side_stream && !to_device) {
+    // after everything enqueued so far, but not in the way of what is enqueued next
+    cudaEventRecord(g_dev.ev_read, g_dev.stream);
+    cudaStreamWaitEvent(g_dev.read_stream, g_dev.ev_read, 0);
+    copy_stream = g_dev.read_stream;
+    g_dev.reads_in_flight = true;
+  }
   cudaError_t e = to_device
-      ? cudaMemcpyAsync(dev, host, (size_t)length, cudaMemcpyDefault, g_dev.stream)
-      : cudaMemcpyAsync((void*)host, dev, (size_t)length, cudaMemcpyDefault, g_dev.stream);
+      ? cudaMemcpyAsync(dev, host, (size_t)length, cudaMemcpyDefault, copy_stream)
+      : cudaMemcpyAsync((void*)host, dev, (size_t)length, cudaMemcpyDefault, copy_stream);
   if (e != cudaSuccess) {
     store_error(cuda_error(std::string("buffer copy failed: ") + cudaGetErrorString(e)));
     return -1;
@@ -926,7 +952,7 @@ int32_t tmx_buffer_write_async(int64_t buffer, int64_t offset, const void* sourc
 }
 
 int32_t tmx_buffer_read_async(int64_t buffer, int64_t offset, void* destination, int64_t length) {
-  return do_copy(buffer, offset, destination, length, false, false);
+  return do_copy(buffer, offset, destination, length, false, false, true);
 }
 
 int32_t tmx_buffer_fill(int64_t buffer, int64_t offset, int32_t byte, int64_t length) {
@@ -963,6 +989,7 @@ int32_t tmx_timer_end(float* elapsed_ms) {
   std::string err;
   if (!elapsed_ms) { store_error(invalid_argument("tmx_timer_end needs a result pointer")); return -1; }
   if (!bind_device(err)) { store_error(err); return -1; }
+  join_reads();
   cudaEventRecord(g_dev.ev_end, g_dev.stream);
   if (!sync_stream(err)) { store_error(err); return -1; }
   cudaEventElapsedTime(elapsed_ms, g_dev.ev_begin, g_dev.ev_end);
