@@ -218,7 +218,20 @@ def gemm_chunks(rows_per_rank):
     """How many row blocks each rank's share of M is cut into so that the all-gather of one
     block overlaps the GEMM of the next (at least 512 rows per block: a block should still
     fill the 148 SMs with 128 x 256 tiles)."""
-    return max(1, min(4, rows_per_rank // 512))
+    chunks = max(1, min(4, rows_per_rank // 512))
+    while rows_per_rank % chunks:
+        chunks -= 1
+    return chunks
+
+
+def gemm_row_blocks(M, rank, world):
+    """(first row, rows) of every row block of C that `rank` computes: the M rows are cut into
+    world * chunks equal blocks dealt round-robin, so chunk c of every rank - blocks
+    c*world ... c*world + world-1 - is one contiguous slab of C and one all-gather fills it."""
+    rows = M // world
+    chunks = gemm_chunks(rows) if world > 1 else 1
+    block = rows // chunks
+    return [((c * world + rank) * block, block) for c in range(chunks)]
 
 
 class GemmJob:
@@ -236,11 +249,10 @@ class GemmJob:
         if M % dist.world:
             raise SystemExit("M must be a multiple of the number of ranks")
         self.rows = M // dist.world
-        self.chunks = gemm_chunks(self.rows) if dist.world > 1 else 1
-        self.block = self.rows // self.chunks
+        blocks = gemm_row_blocks(M, dist.rank, dist.world)
+        self.chunks, self.block = len(blocks), blocks[0][1]
         self.a_host, self.b_host = [], None
-        for c in range(self.chunks):
-            row0 = (c * dist.world + dist.rank) * self.block
+        for row0, _ in blocks:
             a, b = gemm_inputs_bf16(M, N, K, seed, row0, self.block)
             self.a_host.append(a)
             self.b_host = b

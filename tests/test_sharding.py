@@ -31,16 +31,29 @@ def test_shard_partitions_exactly():
 
 
 def test_flop_accounting_matches_the_reference():
-    assert bench.gemm_chunks(4096) == 4 and bench.gemm_chunks(1024) == 2 and bench.gemm_chunks(8192) == 4
     assert bench.flops(bench.WORKLOADS["gemm_bf16_8192"]) == 2 * 8192 ** 3
     fwd = bench.WORKLOADS["attn_fwd_bf16_s4096_full"]
-    assert bench.gemm_chunks(4096) == 4 and bench.gemm_chunks(1024) == 2 and bench.gemm_chunks(8192) == 4
     assert bench.flops(fwd) == 4 * 4096 ** 2 * 128 * 128
-    assert bench.gemm_chunks(4096) == 4 and bench.gemm_chunks(1024) == 2 and bench.gemm_chunks(8192) == 4
     assert bench.flops(bench.WORKLOADS["attn_fwd_bf16_s4096"]) == bench.flops(fwd) / 2
     bwd = bench.WORKLOADS["attn_bwd_bf16_s4096_d128"]
-    assert bench.gemm_chunks(4096) == 4 and bench.gemm_chunks(1024) == 2 and bench.gemm_chunks(8192) == 4
     assert bench.flops(bwd) == 10 * 4096 ** 2 * 128 * 128 / 2
+
+
+def test_gemm_row_blocks_tile_the_rows():
+    assert bench.gemm_chunks(4096) == 4 and bench.gemm_chunks(1024) == 2 and bench.gemm_chunks(8192) == 4
+    assert bench.gemm_chunks(1536) == 3 and bench.gemm_chunks(1100) == 2 and bench.gemm_chunks(100) == 1
+    for M, world in ((8192, 1), (8192, 2), (8192, 4), (8192, 8), (16384, 8), (3072, 2)):
+        owned = [bench.gemm_row_blocks(M, r, world) for r in range(world)]
+        chunks = len(owned[0])
+        assert all(len(o) == chunks for o in owned)
+        covered = sorted(b for o in owned for b in o)
+        assert covered[0][0] == 0 and sum(n for _, n in covered) == M
+        for (r0, n), (r1, _) in zip(covered, covered[1:]):
+            assert r0 + n == r1
+        # chunk c of ranks 0..world-1 is one contiguous slab, in rank order
+        for c in range(chunks):
+            starts = [owned[r][c][0] for r in range(world)]
+            assert starts == [starts[0] + r * owned[0][c][1] for r in range(world)]
 
 
 def _free_port():
@@ -63,6 +76,16 @@ def _worker(rank, world, port, results):
         gathered = [torch.empty_like(c_local) for _ in range(world)]
         dist.all_gather(gathered, c_local)
         c_full = torch.cat(gathered, dim=0)
+        # the benchmark's layout: block-cyclic row blocks, one all-gather per chunk into its
+        # contiguous slab of the replicated C
+        Mc = 4096
+        mine = bench.gemm_row_blocks(Mc, rank, world)
+        full = torch.zeros(Mc, 3)
+        per_chunk = world * mine[0][1]
+        for c, (r0, n) in enumerate(mine):
+            local = torch.arange(r0, r0 + n, dtype=torch.float32).repeat(3, 1).T.contiguous()
+            dist.all_gather_into_tensor(full[c * per_chunk:(c + 1) * per_chunk], local)
+        cyclic_ok = bool(torch.equal(full[:, 0], torch.arange(Mc, dtype=torch.float32)))
         # every rank derives the same B and its own rows of A: rebuild the whole product
         blocks = []
         for r in range(world):
@@ -78,7 +101,7 @@ def _worker(rank, world, port, results):
         bh0, bh = bench.shard(128, rank, world)
         spans = [None] * world
         dist.all_gather_object(spans, (bh0, bh))
-        results[rank] = (ok, float(t.item()), spans)
+        results[rank] = (ok and cyclic_ok, float(t.item()), spans)
     finally:
         dist.destroy_process_group()
 
