@@ -403,30 +403,58 @@ class AttnJob:
             self.fwd.launch_async(*self.fwd_args)
 
     def e2e_setup(self):
+        """Pinned host copies of the inputs and outputs, and per-piece device buffers: the heads
+        are cut into up to eight pieces, and a piece's outputs are read back on the library's side
+        stream while the next piece's inputs go up and its kernels run."""
+        from triton_metal import cuda
+        S, D = self.w["seq"], self.w["d"]
         self.pins = {}
-        names = ["q", "k", "v"] + (["do"] if self.backward else [])
+        ins = ["q", "k", "v"] + (["do"] if self.backward else [])
         h2d = 0
-        for name, arr in zip(names, self.host):
+        for name, arr in zip(ins, self.host):
             p = pinned(arr.nbytes)
             p.numpy()[:] = arr.reshape(-1).view(np.uint8)
             self.pins[name] = p
             h2d += arr.nbytes
         outs = ["dq", "dk", "dv"] if self.backward else ["o"]
-        self.pin_out = {name: pinned(self.bh * self.w["seq"] * self.w["d"] * 2) for name in outs}
-        return h2d, sum(p.numel() for p in self.pin_out.values())
+        self.pin_out = {name: pinned(max(1, self.bh) * S * D * 2) for name in outs}
+        self.pieces = []
+        n_pieces = max(1, min(8, self.bh // 8)) if self.bh else 0
+        for i in range(n_pieces):
+            h0, hn = shard(self.bh, i, n_pieces)
+            nbytes, offset = hn * S * D * 2, h0 * S * D * 2
+            buf = {name: cuda.alloc_device_buffer(nbytes) for name in set(ins + outs + ["o"])}
+            for name in ("lse", "delta"):
+                buf[name] = cuda.alloc_device_buffer(hn * S * 4)
+            launches = []
+            fwd_args = self.fwd.arguments(buf["q"], buf["k"], buf["v"], buf["o"], buf["lse"], self.scale, hn, S)
+            if self.backward:
+                # the backward consumes the forward's O and L of the same heads: once, untimed
+                for name in ("q", "k", "v"):
+                    self.core.buffer_write(buf[name], 0, self.pins[name].data_ptr() + offset, nbytes)
+                self.fwd.launch(*fwd_args)
+                launches = [
+                    (self.pre, self.pre.arguments(buf["o"], buf["do"], buf["delta"], hn, S)),
+                    (self.dq, self.dq.arguments(buf["q"], buf["k"], buf["v"], buf["do"], buf["dq"], buf["lse"],
+                                                buf["delta"], self.scale, hn, S)),
+                    (self.dkdv, self.dkdv.arguments(buf["q"], buf["k"], buf["v"], buf["do"], buf["dk"], buf["dv"],
+                                                    buf["lse"], buf["delta"], self.scale, hn, S))]
+            else:
+                launches = [(self.fwd, fwd_args)]
+            self.pieces.append((buf, launches, offset, nbytes))
+        self.e2e_in, self.e2e_out = ins, outs
+        return h2d, sum(p.numel() for p in self.pin_out.values()) if self.bh else 0
 
     def e2e_step(self):
-        c = self.core
-        for name, p in self.pins.items():
-            c.buffer_write(self.buf[name], 0, p.data_ptr(), p.numel())
-        if self.backward:
-            self.pre.launch(*self.pre_args)
-            self.dq.launch(*self.dq_args)
-            self.dkdv.launch(*self.dkdv_args)
-        else:
-            self.fwd.launch(*self.fwd_args)
-        for name, p in self.pin_out.items():
-            c.buffer_read(self.buf[name], 0, p.data_ptr(), p.numel())
+        from triton_metal import cuda
+        for buf, launches, offset, nbytes in self.pieces:
+            for name in self.e2e_in:
+                cuda.write_async(buf[name], 0, self.pins[name].data_ptr() + offset, nbytes)
+            for kernel, args in launches:
+                kernel.launch_async(*args)
+            for name in self.e2e_out:
+                cuda.read_async(buf[name], 0, self.pin_out[name].data_ptr() + offset, nbytes)
+        cuda.synchronize()           # every output is in host memory
 
     def sample_output(self, name):
         """Head 0 of an output tensor, as bf16 words."""
