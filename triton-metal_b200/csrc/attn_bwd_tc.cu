@@ -346,41 +346,52 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       constexpr uint32_t idesc_tn = make_idesc(FMT, BLK, D, 0, 1);
       const SmemDesc q_km = kmajor(q_addr), do_km = kmajor(do_addr), k_km = kmajor(k_addr), v_km = kmajor(v_addr);
       const SmemDesc k_mn = mnmajor(k_addr);
-      bool ok = mbar_wait(smem_u32(&ss.qdo_full), 0, wc, 33);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j % K_STAGES;
-        if (!mbar_wait(smem_u32(&ss.k_full[s]), (j / K_STAGES) & 1, wc, 34)) return false;
-        tc_fence_after();
-        mma_nt<D>(tmem + S_COL + (j & 1) * BLK, q_km, k_km.advanced(s * TILE), idesc_nt);
-        mma_commit(smem_u32(&ss.s_full[j & 1]));
-        return true;
+      auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
+        mbar_wait_issuer(smem_u32(bar), parity, wc, site);
       };
-      auto issue_dp = [&](int j) -> bool {
+      // S(j) = Q K(j)^T into S[j & 1]; `ks` = j mod K_STAGES, `kp` = parity of (j / K_STAGES)
+      auto issue_qk = [&](int j, int ks, uint32_t kp) {
+        wait(&ss.k_full[ks], kp, 34);
+        tc_fence_after();
+        mma_nt<D>(tmem + S_COL + (j & 1) * BLK, q_km, k_km.advanced(ks * TILE), idesc_nt);
+        mma_commit(smem_u32(&ss.s_full[j & 1]));
+      };
+      auto issue_dp = [&](int j) {
         const int s = j % V_STAGES;
-        if (!mbar_wait(smem_u32(&ss.v_full[s]), (j / V_STAGES) & 1, wc, 35)) return false;
+        wait(&ss.v_full[s], (j / V_STAGES) & 1, 35);
         tc_fence_after();
         mma_nt<D>(tmem + DP_COL, do_km, v_km.advanced(s * TILE), idesc_nt);
         mma_commit(smem_u32(&ss.v_empty[s]));
         mma_commit(smem_u32(&ss.dp_full));
-        return true;
       };
-      if (ok && n_blocks > 0) ok = issue_qk(0) && issue_dp(0);
-      if (ok && n_blocks > 1) ok = issue_qk(1);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        if (j + 1 < n_blocks) {
+      wait(&ss.qdo_full, 0, 33);
+      issue_qk(0, 0, 0);
+      issue_dp(0);
+      if (n_blocks > 1) issue_qk(1, 1, 0);
+      // ring position of K(j) and of K(j+2), carried along instead of divided out
+      int ks = 0, ks2 = 2 % K_STAGES;
+      uint32_t kp2 = (2 / K_STAGES) & 1;
+      auto block = [&](int j, bool next, bool next2) {
+        if (next) {
           // the element-wise warps have dP(j) in registers: the next dP may overwrite it while
           // they are still working on block j
-          if (!mbar_wait(smem_u32(&ss.dp_read), j & 1, wc, 41)) { ok = false; break; }
-          if (!issue_dp(j + 1)) { ok = false; break; }
+          wait(&ss.dp_read, j & 1, 41);
+          issue_dp(j + 1);
         }
-        if (!mbar_wait(smem_u32(&ss.ds_full), j & 1, wc, 36)) { ok = false; break; }
+        wait(&ss.ds_full, j & 1, 36);
         tc_fence_after();
-        mma_tn<D>(tmem + DQ_COL, tmem + S_COL + (j & 1) * BLK, k_mn.advanced((j % K_STAGES) * TILE), idesc_tn, j != 0);
-        mma_commit(smem_u32(&ss.k_empty[j % K_STAGES]));
-        if (j + 1 == n_blocks) mma_commit(smem_u32(&ss.dq_done));
+        mma_tn<D>(tmem + DQ_COL, tmem + S_COL + (j & 1) * BLK, k_mn.advanced(ks * TILE), idesc_tn, j != 0);
+        mma_commit(smem_u32(&ss.k_empty[ks]));
+        if (!next) mma_commit(smem_u32(&ss.dq_done));
         // S(j+2) reuses the buffer dS(j) sits in: MMAs run in issue order
-        if (j + 2 < n_blocks && !issue_qk(j + 2)) { ok = false; break; }
-      }
+        if (next2) issue_qk(j + 2, ks2, kp2);
+        if (++ks == K_STAGES) ks = 0;
+        if (++ks2 == K_STAGES) { ks2 = 0; kp2 ^= 1; }
+      };
+      int j = 0;
+      for (; j + 2 < n_blocks; ++j) block(j, true, true);
+      if (j + 1 < n_blocks) { block(j, true, false); ++j; }
+      block(j, false, false);
     }
   } else {
     const int group = warp / 4;                   // owns columns group*32 ... of every block
@@ -551,31 +562,32 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       constexpr uint32_t idesc_tn = make_idesc(FMT, BLK, D, 0, 1);
       const SmemDesc k_km = kmajor(k_addr), v_km = kmajor(v_addr), q_km = kmajor(q_addr), do_km = kmajor(do_addr);
       const SmemDesc q_mn = mnmajor(q_addr), do_mn = mnmajor(do_addr), p_km = kmajor(p_addr);
-      bool ok = mbar_wait(smem_u32(&ss.kv_full), 0, wc, 53);
-      if (ok && n_iter > 0) ok = mbar_wait(smem_u32(&ss.qdo_full[0]), 0, wc, 54);
-      if (ok && n_iter > 0) {
-        tc_fence_after();
-        mma_nt<D>(tmem + ST_COL, k_km, q_km, idesc_nt);
-        mma_commit(smem_u32(&ss.st_full));
-        mma_nt<D>(tmem + DPT_COL, v_km, do_km, idesc_nt);
-        mma_commit(smem_u32(&ss.dpt_full));
-      }
-      for (int t = 0; t < n_iter && ok; ++t) {
+      auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
+        mbar_wait_issuer(smem_u32(bar), parity, wc, site);
+      };
+      wait(&ss.kv_full, 0, 53);
+      wait(&ss.qdo_full[0], 0, 54);
+      tc_fence_after();
+      mma_nt<D>(tmem + ST_COL, k_km, q_km, idesc_nt);
+      mma_commit(smem_u32(&ss.st_full));
+      mma_nt<D>(tmem + DPT_COL, v_km, do_km, idesc_nt);
+      mma_commit(smem_u32(&ss.dpt_full));
+      // every block but the last also starts the next block's S^T and dP^T
+      auto block = [&](int t, bool more) {
         const int s = t & 1;
-        const bool more = t + 1 < n_iter;
         if (more) {
           // S^T(t) is in registers and Q(t+1) has landed: the next scores can go
-          if (!mbar_wait(smem_u32(&ss.s_read), t & 1, wc, 63)) { ok = false; break; }
-          if (!mbar_wait(smem_u32(&ss.qdo_full[s ^ 1]), ((t + 1) >> 1) & 1, wc, 54)) { ok = false; break; }
+          wait(&ss.s_read, t & 1, 63);
+          wait(&ss.qdo_full[s ^ 1], ((t + 1) >> 1) & 1, 54);
           tc_fence_after();
           mma_nt<D>(tmem + ST_COL, k_km, q_km.advanced((s ^ 1) * TILE), idesc_nt);
           mma_commit(smem_u32(&ss.st_full));
         }
-        if (!mbar_wait(smem_u32(&ss.p_full), t & 1, wc, 56)) { ok = false; break; }
+        wait(&ss.p_full, t & 1, 56);
         tc_fence_after();
         mma_sn<D>(tmem + DV_COL, p_km, do_mn.advanced(s * TILE), idesc_tn, t != 0);
         mma_commit(smem_u32(&ss.p_empty));
-        if (!mbar_wait(smem_u32(&ss.ds_full), t & 1, wc, 57)) { ok = false; break; }
+        wait(&ss.ds_full, t & 1, 57);
         tc_fence_after();
         mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_mn.advanced(s * TILE), idesc_tn, t != 0);
         mma_commit(smem_u32(&ss.qdo_empty[s]));        // last use of Q(t) and dO(t)
@@ -585,7 +597,9 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         } else {
           mma_commit(smem_u32(&ss.done));
         }
-      }
+      };
+      for (int t = 0; t + 1 < n_iter; ++t) block(t, true);
+      block(n_iter - 1, false);
     }
   } else if (warp < EW_THREADS / 32) {
     const int group = warp / 4;                   // owns query columns group*32 ... of every block

@@ -87,6 +87,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   }
 }
 
+// The same wait for the thread that issues the MMAs.  That thread runs alone in its warp, so
+// every branch costs it tens of cycles (measured: about 35 per compare-and-branch) and the
+// tensor pipe waits for it: the fast path here is one test and one branch, the rest is out
+// of line, and the caller does not branch on the outcome.  After a timeout (or another
+// role's abort) every later wait returns at once, so the issuer simply runs to the end of
+// its loop on stale data and the launch is reported as failed.
+static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t site) {
+  if (*w.abort_flag) return;
+  const long long start = clock64();
+  for (uint32_t spins = 1;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((spins & 63u) == 0u) {
+      if (*w.abort_flag) return;
+      if (clock64() - start > kWaitCycles) {
+        report_timeout(w, site, parity);
+        return;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void mbar_wait_issuer(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t site) {
+  if (!mbar_try_wait(bar, parity)) mbar_wait_slow(bar, parity, w, site);
+}
+
 // ---- TMA (tile mode, one CTA, completion on an mbarrier) ----------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int x, int y) {
