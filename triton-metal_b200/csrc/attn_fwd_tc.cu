@@ -36,6 +36,7 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <type_traits>
 
 namespace tmc {
 namespace {
@@ -325,17 +326,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           for (int t = 0; t < TILES; ++t) issue_qk(t, g & 1);
           mma_commit(smem_u32(&ss.k_empty[g & 1]));      // K(0) is free once both S(0) retire
           if (nb_max == 1) mma_commit(smem_u32(&ss.q_empty));
-          for (int j = 0; j < nb_max && ok; ++j, ++g) {
+          // One key block.  `steady` (a compile-time constant at both call sites) marks blocks with
+          // two more to come for both tiles: every condition below is then known, and the issuing
+          // thread - alone in its warp, it pays tens of cycles for each compare-and-branch - keeps
+          // only the barrier waits.
+          auto key_block = [&](int j, auto steady_tag) {
+            constexpr bool steady = decltype(steady_tag)::value;
             const int s = g & 1;
-            if (!mbar_wait(smem_u32(&ss.v_full[s]), (g >> 1) & 1, wc, kMmaV)) { ok = false; break; }
-            if (j + 1 < nb_max && !mbar_wait(smem_u32(&ss.k_full[s ^ 1]), ((g + 1) >> 1) & 1, wc, kMmaK)) {
+            if (!mbar_wait(smem_u32(&ss.v_full[s]), (g >> 1) & 1, wc, kMmaV)) { ok = false; return; }
+            if ((steady || j + 1 < nb_max) &&
+                !mbar_wait(smem_u32(&ss.k_full[s ^ 1]), ((g + 1) >> 1) & 1, wc, kMmaK)) {
               ok = false;
-              break;
+              return;
             }
 #pragma unroll
             for (int t = 0; t < TILES; ++t) {
-              if (j < nb[t]) {
-                if (!mbar_wait(smem_u32(&ss.p_full[t]), c[t] & 1, wc, kMmaP)) { ok = false; break; }
+              if (steady || j < nb[t]) {
+                if (!mbar_wait(smem_u32(&ss.p_full[t]), c[t] & 1, wc, kMmaP)) { ok = false; return; }
                 ++c[t];
                 tc_fence_after();
                 const SmemDesc vb = v_desc.advanced(s * TILE_BYTES);
@@ -350,20 +357,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 // O_t is only read after the last block; rescales in between are ordered by the
                 // next s_full (a commit covers every MMA issued before it, P.V(j) included)
-                if (j + 1 == nb[t]) mma_commit(smem_u32(&ss.pv_done[t]));
+                if (!steady && j + 1 == nb[t]) mma_commit(smem_u32(&ss.pv_done[t]));
               }
               // V(j) has been read by both tiles: release it as early as possible
               if (t == TILES - 1) mma_commit(smem_u32(&ss.v_empty[s]));
               // the next scores of this tile overwrite its P: MMAs run in issue order
-              if (j + 1 < nb[t]) issue_qk(t, s ^ 1);
-              if (t == TILES - 1 && j + 1 < nb_max) {
+              if (steady || j + 1 < nb[t]) issue_qk(t, s ^ 1);
+              if (t == TILES - 1 && (steady || j + 1 < nb_max)) {
                 // the last tile always walks every block: K(j+1) is free once its S retires,
                 // and after the last block's scores so is Q
                 mma_commit(smem_u32(&ss.k_empty[s ^ 1]));
-                if (j + 2 == nb_max) mma_commit(smem_u32(&ss.q_empty));
+                if (!steady && j + 2 == nb_max) mma_commit(smem_u32(&ss.q_empty));
               }
             }
-          }
+          };
+          int j = 0;
+          for (; j + 2 < nb[0] && ok; ++j, ++g) key_block(j, std::true_type{});
+          for (; j < nb_max && ok; ++j, ++g) key_block(j, std::false_type{});
         }
       }
     }
