@@ -290,7 +290,8 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
   } else if (warp == MMA_WARP) {
     // ---------------------------------------------------------------- MMA issue
-    if (lane == 0) {
+    // The whole warp runs this loop, converged; one elected lane issues (see mma_f16_ss_elect).
+    {
       constexpr uint32_t idesc_qk = make_idesc(FMT, BLOCK_M, BLOCK_N, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc(FMT, BLOCK_M, D, 0, 1);
       // S_t = Q_t K^T with K in ring stage `stage`.  The caller has made sure K has landed.
@@ -303,9 +304,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
-          mma_f16_ss(tmem + S_COL + t * BLOCK_N, qb.at(off), kb.at(off), idesc_qk, kk != 0);
+          mma_f16_ss_elect(tmem + S_COL + t * BLOCK_N, qb.at(off), kb.at(off), idesc_qk, kk != 0);
         }
-        mma_commit(smem_u32(&ss.s_full[t]));
+        mma_commit_elect(smem_u32(&ss.s_full[t]));
       };
       uint32_t item = 0, g = 0, c[TILES] = {0, 0};
       bool ok = true;
@@ -316,16 +317,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
           for (int t = 0; t < TILES; ++t) nb[t] = key_blocks(m0, t);
           const int nb_max = nb[TILES - 1];               // later rows see at least as many keys
-          if (!mbar_wait(smem_u32(&ss.q_full), item & 1, wc, kMmaQ)) { ok = false; break; }
-          if (!mbar_wait(smem_u32(&ss.k_full[g & 1]), (g >> 1) & 1, wc, kMmaK)) { ok = false; break; }
+          if (!mbar_wait_warp(smem_u32(&ss.q_full), item & 1, wc, kMmaQ)) { ok = false; break; }
+          if (!mbar_wait_warp(smem_u32(&ss.k_full[g & 1]), (g >> 1) & 1, wc, kMmaK)) { ok = false; break; }
           tc_fence_after();
           // The first scores of this query block go over the last P of the previous one, and
           // its first P.V starts a fresh O: MMAs run in issue order, and the softmax threads
           // hand over P(0) only after they have read the previous O out of TMEM.
 #pragma unroll
           for (int t = 0; t < TILES; ++t) issue_qk(t, g & 1);
-          mma_commit(smem_u32(&ss.k_empty[g & 1]));      // K(0) is free once both S(0) retire
-          if (nb_max == 1) mma_commit(smem_u32(&ss.q_empty));
+          mma_commit_elect(smem_u32(&ss.k_empty[g & 1]));      // K(0) is free once both S(0) retire
+          if (nb_max == 1) mma_commit_elect(smem_u32(&ss.q_empty));
           // One key block.  `steady` (a compile-time constant at both call sites) marks blocks with
           // two more to come for both tiles: every condition below is then known, and the issuing
           // thread - alone in its warp, it pays tens of cycles for each compare-and-branch - keeps
@@ -333,16 +334,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           auto key_block = [&](int j, auto steady_tag) {
             constexpr bool steady = decltype(steady_tag)::value;
             const int s = g & 1;
-            if (!mbar_wait(smem_u32(&ss.v_full[s]), (g >> 1) & 1, wc, kMmaV)) { ok = false; return; }
+            if (!mbar_wait_warp(smem_u32(&ss.v_full[s]), (g >> 1) & 1, wc, kMmaV)) { ok = false; return; }
             if ((steady || j + 1 < nb_max) &&
-                !mbar_wait(smem_u32(&ss.k_full[s ^ 1]), ((g + 1) >> 1) & 1, wc, kMmaK)) {
+                !mbar_wait_warp(smem_u32(&ss.k_full[s ^ 1]), ((g + 1) >> 1) & 1, wc, kMmaK)) {
               ok = false;
               return;
             }
 #pragma unroll
             for (int t = 0; t < TILES; ++t) {
               if (steady || j < nb[t]) {
-                if (!mbar_wait(smem_u32(&ss.p_full[t]), c[t] & 1, wc, kMmaP)) { ok = false; return; }
+                if (!mbar_wait_warp(smem_u32(&ss.p_full[t]), c[t] & 1, wc, kMmaP)) { ok = false; return; }
                 ++c[t];
                 tc_fence_after();
                 const SmemDesc vb = v_desc.advanced(s * TILE_BYTES);
@@ -351,23 +352,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                   // P: TMEM operand, 16 keys = 8 packed 32-bit columns; keys 0-63 sit at the start
                   // of the score buffer, keys 64-127 at its column 64 (one piece per softmax group).
                   // V: MN-major, 16 keys = 2048 bytes further, 64-column halves HALF_BYTES apart.
-                  mma_f16_ts(tmem + O_COL + t * D,
+                  mma_f16_ts_elect(tmem + O_COL + t * D,
                              tmem + S_COL + t * BLOCK_N + (kk / 4) * HALF_N + (kk % 4) * 8,
                              vb.at(kk * 2048), idesc_pv, (j | kk) != 0);
                 }
                 // O_t is only read after the last block; rescales in between are ordered by the
                 // next s_full (a commit covers every MMA issued before it, P.V(j) included)
-                if (!steady && j + 1 == nb[t]) mma_commit(smem_u32(&ss.pv_done[t]));
+                if (!steady && j + 1 == nb[t]) mma_commit_elect(smem_u32(&ss.pv_done[t]));
               }
               // V(j) has been read by both tiles: release it as early as possible
-              if (t == TILES - 1) mma_commit(smem_u32(&ss.v_empty[s]));
+              if (t == TILES - 1) mma_commit_elect(smem_u32(&ss.v_empty[s]));
               // the next scores of this tile overwrite its P: MMAs run in issue order
               if (steady || j + 1 < nb[t]) issue_qk(t, s ^ 1);
               if (t == TILES - 1 && (steady || j + 1 < nb_max)) {
                 // the last tile always walks every block: K(j+1) is free once its S retires,
                 // and after the last block's scores so is Q
-                mma_commit(smem_u32(&ss.k_empty[s ^ 1]));
-                if (!steady && j + 2 == nb_max) mma_commit(smem_u32(&ss.q_empty));
+                mma_commit_elect(smem_u32(&ss.k_empty[s ^ 1]));
+                if (!steady && j + 2 == nb_max) mma_commit_elect(smem_u32(&ss.q_empty));
               }
             }
           };

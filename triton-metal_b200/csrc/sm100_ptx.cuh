@@ -238,6 +238,63 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
                : "memory");
 }
 
+// ---- issuing from a converged warp -------------------------------------------------
+// The same instructions for an issuer warp that stays converged: all 32 lanes run the issue
+// loop (its control flow is warp-uniform), and one lane, elected inside the asm block, issues.
+// Measured per 128 x N x 16 instruction with N small enough that the pipe does not limit: 57
+// cycles from one lane of a diverged warp (`if (lane == 0)`), 39 this way - which is also the
+// most the SM accepts from any number of issuers.  Every lane must reach these calls.
+__device__ __forceinline__ void mma_f16_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, e;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, e;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
+  asm volatile(
+      "{\n"
+      ".reg .pred e;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n" ::"r"(bar)
+      : "memory");
+}
+// mbar_wait for such a warp: every decision is taken by vote, so the lanes leave together
+// (a lane that left early would make the next elect.sync wait for ever).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t site) {
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+  const long long start = clock64();
+  for (uint32_t spins = 1;; ++spins) {
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    if ((spins & 63u) == 0u) {
+      const bool give_up = *w.abort_flag != 0 || clock64() - start > kWaitCycles;
+      if (__any_sync(0xffffffffu, give_up)) {
+        if ((threadIdx.x & 31) == 0 && *w.abort_flag == 0) report_timeout(w, site, parity);
+        __syncwarp();
+        return false;
+      }
+    }
+  }
+}
+
 // ---- TMEM <-> registers ----------------------------------------------------------
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane
 // (warp%4)*32 + t, registers r[0..31] = columns col..col+31.
