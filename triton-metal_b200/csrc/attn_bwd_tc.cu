@@ -93,7 +93,7 @@ __device__ __forceinline__ void mma_nt(uint32_t d_tmem, SmemDesc a, SmemDesc b, 
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     const uint32_t off = (kk / 4) * (BLK * 128) + (kk % 4) * 32;
-    mma_f16_ss(d_tmem, a.at(off), b.at(off), idesc, kk != 0);
+    mma_f16_ss_elect(d_tmem, a.at(off), b.at(off), idesc, kk != 0);
   }
 }
 
@@ -105,7 +105,7 @@ __device__ __forceinline__ void mma_tn(uint32_t d_tmem, uint32_t a_tmem, SmemDes
                                        bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < BLK / 16; ++kk)
-    mma_f16_ts(d_tmem, a_tmem + (kk / 2) * GCOLS + (kk % 2) * 8, b.at(kk * 2048), idesc, accumulate || kk != 0);
+    mma_f16_ts_elect(d_tmem, a_tmem + (kk / 2) * GCOLS + (kk % 2) * 8, b.at(kk * 2048), idesc, accumulate || kk != 0);
 }
 
 // D_tmem[128 x D] (+)= A[128 x 128] * B[128 x D]: A a K-major 128 x 128 tile in shared memory
@@ -114,7 +114,7 @@ template <int D>
 __device__ __forceinline__ void mma_sn(uint32_t d_tmem, SmemDesc a, SmemDesc b, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < BLK / 16; ++kk)
-    mma_f16_ss(d_tmem, a.at((kk / 4) * (BLK * 128) + (kk % 4) * 32), b.at(kk * 2048), idesc, accumulate || kk != 0);
+    mma_f16_ss_elect(d_tmem, a.at((kk / 4) * (BLK * 128) + (kk % 4) * 32), b.at(kk * 2048), idesc, accumulate || kk != 0);
 }
 
 // Descriptors of a K-major tile (operand of mma_nt) and of a row-major tile used as the
@@ -341,28 +341,29 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     // One thread issues every MMA.  A tcgen05.mma costs its issuer about 55 cycles whatever
     // its size (measured; a 128 x 128 x 16 one occupies the pipe for 64), a commit or a
     // barrier wait about 50 more, so this loop is kept to the minimum of both.
-    if (lane == 0) {
+    // the whole warp runs this loop, converged; one elected lane issues (see mma_f16_ss_elect)
+    {
       constexpr uint32_t idesc_nt = make_idesc(FMT, BLK, BLK, 0, 0);
       constexpr uint32_t idesc_tn = make_idesc(FMT, BLK, D, 0, 1);
       const SmemDesc q_km = kmajor(q_addr), do_km = kmajor(do_addr), k_km = kmajor(k_addr), v_km = kmajor(v_addr);
       const SmemDesc k_mn = mnmajor(k_addr);
       auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
-        mbar_wait_issuer(smem_u32(bar), parity, wc, site);
+        mbar_wait_warp(smem_u32(bar), parity, wc, site);
       };
       // S(j) = Q K(j)^T into S[j & 1]; `ks` = j mod K_STAGES, `kp` = parity of (j / K_STAGES)
       auto issue_qk = [&](int j, int ks, uint32_t kp) {
         wait(&ss.k_full[ks], kp, 34);
         tc_fence_after();
         mma_nt<D>(tmem + S_COL + (j & 1) * BLK, q_km, k_km.advanced(ks * TILE), idesc_nt);
-        mma_commit(smem_u32(&ss.s_full[j & 1]));
+        mma_commit_elect(smem_u32(&ss.s_full[j & 1]));
       };
       auto issue_dp = [&](int j) {
         const int s = j % V_STAGES;
         wait(&ss.v_full[s], (j / V_STAGES) & 1, 35);
         tc_fence_after();
         mma_nt<D>(tmem + DP_COL, do_km, v_km.advanced(s * TILE), idesc_nt);
-        mma_commit(smem_u32(&ss.v_empty[s]));
-        mma_commit(smem_u32(&ss.dp_full));
+        mma_commit_elect(smem_u32(&ss.v_empty[s]));
+        mma_commit_elect(smem_u32(&ss.dp_full));
       };
       wait(&ss.qdo_full, 0, 33);
       issue_qk(0, 0, 0);
@@ -381,8 +382,8 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         wait(&ss.ds_full, j & 1, 36);
         tc_fence_after();
         mma_tn<D>(tmem + DQ_COL, tmem + S_COL + (j & 1) * BLK, k_mn.advanced(ks * TILE), idesc_tn, j != 0);
-        mma_commit(smem_u32(&ss.k_empty[ks]));
-        if (!next) mma_commit(smem_u32(&ss.dq_done));
+        mma_commit_elect(smem_u32(&ss.k_empty[ks]));
+        if (!next) mma_commit_elect(smem_u32(&ss.dq_done));
         // S(j+2) reuses the buffer dS(j) sits in: MMAs run in issue order
         if (next2) issue_qk(j + 2, ks2, kp2);
         if (++ks == K_STAGES) ks = 0;
@@ -557,21 +558,22 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // One thread issues every MMA.  A tcgen05.mma costs its issuer about 55 cycles whatever
     // its size (measured; a 128 x 128 x 16 one occupies the pipe for 64), a commit or a
     // barrier wait about 50 more: four waits and four commits per block, no more.
-    if (lane == 0) {
+    // the whole warp runs this loop, converged; one elected lane issues (see mma_f16_ss_elect)
+    {
       constexpr uint32_t idesc_nt = make_idesc(FMT, BLK, BLK, 0, 0);
       constexpr uint32_t idesc_tn = make_idesc(FMT, BLK, D, 0, 1);
       const SmemDesc k_km = kmajor(k_addr), v_km = kmajor(v_addr), q_km = kmajor(q_addr), do_km = kmajor(do_addr);
       const SmemDesc q_mn = mnmajor(q_addr), do_mn = mnmajor(do_addr), p_km = kmajor(p_addr);
       auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
-        mbar_wait_issuer(smem_u32(bar), parity, wc, site);
+        mbar_wait_warp(smem_u32(bar), parity, wc, site);
       };
       wait(&ss.kv_full, 0, 53);
       wait(&ss.qdo_full[0], 0, 54);
       tc_fence_after();
       mma_nt<D>(tmem + ST_COL, k_km, q_km, idesc_nt);
-      mma_commit(smem_u32(&ss.st_full));
+      mma_commit_elect(smem_u32(&ss.st_full));
       mma_nt<D>(tmem + DPT_COL, v_km, do_km, idesc_nt);
-      mma_commit(smem_u32(&ss.dpt_full));
+      mma_commit_elect(smem_u32(&ss.dpt_full));
       // every block but the last also starts the next block's S^T and dP^T
       auto block = [&](int t, bool more) {
         const int s = t & 1;
@@ -581,21 +583,21 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           wait(&ss.qdo_full[s ^ 1], ((t + 1) >> 1) & 1, 54);
           tc_fence_after();
           mma_nt<D>(tmem + ST_COL, k_km, q_km.advanced((s ^ 1) * TILE), idesc_nt);
-          mma_commit(smem_u32(&ss.st_full));
+          mma_commit_elect(smem_u32(&ss.st_full));
         }
         wait(&ss.p_full, t & 1, 56);
         tc_fence_after();
         mma_sn<D>(tmem + DV_COL, p_km, do_mn.advanced(s * TILE), idesc_tn, t != 0);
-        mma_commit(smem_u32(&ss.p_empty));
+        mma_commit_elect(smem_u32(&ss.p_empty));
         wait(&ss.ds_full, t & 1, 57);
         tc_fence_after();
         mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_mn.advanced(s * TILE), idesc_tn, t != 0);
-        mma_commit(smem_u32(&ss.qdo_empty[s]));        // last use of Q(t) and dO(t)
+        mma_commit_elect(smem_u32(&ss.qdo_empty[s]));        // last use of Q(t) and dO(t)
         if (more) {
           mma_nt<D>(tmem + DPT_COL, v_km, do_km.advanced((s ^ 1) * TILE), idesc_nt);
-          mma_commit(smem_u32(&ss.dpt_full));
+          mma_commit_elect(smem_u32(&ss.dpt_full));
         } else {
-          mma_commit(smem_u32(&ss.done));
+          mma_commit_elect(smem_u32(&ss.done));
         }
       };
       for (int t = 0; t + 1 < n_iter; ++t) block(t, true);
