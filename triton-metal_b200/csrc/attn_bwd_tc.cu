@@ -455,7 +455,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 struct SharedDkdv {
   alignas(8) uint64_t kv_full;
   alignas(8) uint64_t qdo_full[2], qdo_empty[2];
-  alignas(8) uint64_t st_full, s_read, p_full, p_empty, dpt_full, ds_full, done;
+  alignas(8) uint64_t st_full, s_read, p_full, dpt_full, ds_full, done;
   alignas(16) float lse[2][BLK];
   alignas(16) float delta[2][BLK];
   uint32_t tmem_base;
@@ -514,7 +514,6 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     mbar_init(smem_u32(&ss.st_full), 1);
     mbar_init(smem_u32(&ss.s_read), EW_THREADS / 32);
     mbar_init(smem_u32(&ss.p_full), EW_THREADS / 32);
-    mbar_init(smem_u32(&ss.p_empty), 1);
     mbar_init(smem_u32(&ss.dpt_full), 1);
     mbar_init(smem_u32(&ss.ds_full), EW_THREADS / 32);
     mbar_init(smem_u32(&ss.done), 1);
@@ -588,7 +587,6 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         wait(&ss.p_full, t & 1, 56);
         tc_fence_after();
         mma_sn<D>(tmem + DV_COL, p_km, do_mn.advanced(s * TILE), idesc_tn, t != 0);
-        mma_commit_elect(smem_u32(&ss.p_empty));
         wait(&ss.ds_full, t & 1, 57);
         tc_fence_after();
         mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_mn.advanced(s * TILE), idesc_tn, t != 0);
@@ -656,8 +654,9 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       uint32_t keep[16];
       if (diagonal) pt_part<T, true>(sv, qk_scale, lse_s, k_row - q0, keep);
       else pt_part<T, false>(sv, qk_scale, lse_s, 0, keep);
-      // dV(t-1) must have read the previous P^T before it is replaced
-      if (t > 0 && !mbar_wait(smem_u32(&ss.p_empty), (t - 1) & 1, wc, 64)) { ok = false; break; }
+      // dV(t-1) must have read the previous P^T before it is replaced: dP^T(t) was issued after
+      // it, so its commit covers it (and is waited for here instead of before the dS^T pass)
+      if (!mbar_wait(smem_u32(&ss.dpt_full), t & 1, wc, 60)) { ok = false; break; }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const uint32_t dst = p_row + (((p_chunk0 + i) ^ p_xor) << 4);
@@ -668,7 +667,6 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       fence_proxy_async();          // the tensor core reads shared memory through the async proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ss.p_full));
-      if (!mbar_wait(smem_u32(&ss.dpt_full), t & 1, wc, 60)) { ok = false; break; }
       tc_fence_after();
       dst_part<T>(tmem + lane_addr + DPT_COL + group * GCOLS, delta_s, keep);
       tmem_st_wait();
