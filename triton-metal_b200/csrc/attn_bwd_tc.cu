@@ -454,7 +454,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // ===========================================================================
 struct SharedDkdv {
   alignas(8) uint64_t kv_full;
-  alignas(8) uint64_t qdo_full[2], qdo_empty[2];
+  alignas(8) uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
   alignas(8) uint64_t st_full, s_read, p_full, dpt_full, ds_full, done;
   alignas(16) float lse[2][BLK];
   alignas(16) float delta[2][BLK];
@@ -508,8 +508,10 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ss.kv_full), 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&ss.qdo_full[s]), 1);
-      mbar_init(smem_u32(&ss.qdo_empty[s]), 1);
+      mbar_init(smem_u32(&ss.q_full[s]), 1);
+      mbar_init(smem_u32(&ss.q_empty[s]), 1);
+      mbar_init(smem_u32(&ss.do_full[s]), 1);
+      mbar_init(smem_u32(&ss.do_empty[s]), 1);
     }
     mbar_init(smem_u32(&ss.st_full), 1);
     mbar_init(smem_u32(&ss.s_read), EW_THREADS / 32);
@@ -538,20 +540,25 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_expect_tx(smem_u32(&ss.kv_full), 2 * TILE);
       load_tile<D>(k_addr, &map_k, smem_u32(&ss.kv_full), n0, bh);
       load_tile<D>(v_addr, &map_v, smem_u32(&ss.kv_full), n0, bh);
-      int issued = 0;
+      int issued = 0, do_issued = 0;
       for (int t = 0; t < n_iter; ++t) {
         const int s = t & 1;
         const uint32_t ph = (t >> 1) & 1;
         const int row0 = (first + t) * BLK;
-        // Q(t) and dO(t) travel together: one barrier to fill, one to release
-        if (!mbar_wait(smem_u32(&ss.qdo_empty[s]), ph ^ 1, wc, 51)) break;
-        mbar_expect_tx(smem_u32(&ss.qdo_full[s]), 2 * TILE);
-        load_tile<D>(q_addr + s * TILE, &map_q, smem_u32(&ss.qdo_full[s]), row0, bh);
-        load_tile<D>(do_addr + s * TILE, &map_do, smem_u32(&ss.qdo_full[s]), row0, bh);
+        // dO(t)'s slot is freed by dV(t-2), half a block before dK(t-2) frees Q(t)'s: dO goes
+        // first, and the Q refill - 32 KB, on the critical path of S^T(t) - is not held up by it
+        if (!mbar_wait(smem_u32(&ss.do_empty[s]), ph ^ 1, wc, 52)) break;
+        mbar_expect_tx(smem_u32(&ss.do_full[s]), TILE);
+        load_tile<D>(do_addr + s * TILE, &map_do, smem_u32(&ss.do_full[s]), row0, bh);
+        ++do_issued;
+        if (!mbar_wait(smem_u32(&ss.q_empty[s]), ph ^ 1, wc, 51)) break;
+        mbar_expect_tx(smem_u32(&ss.q_full[s]), TILE);
+        load_tile<D>(q_addr + s * TILE, &map_q, smem_u32(&ss.q_full[s]), row0, bh);
         ++issued;
       }
       drain(smem_u32(&ss.kv_full), 0, wc, 59);
-      for (int t = max(0, issued - 2); t < issued; ++t) drain(smem_u32(&ss.qdo_full[t & 1]), (t >> 1) & 1, wc, 59);
+      for (int t = max(0, issued - 2); t < issued; ++t) drain(smem_u32(&ss.q_full[t & 1]), (t >> 1) & 1, wc, 59);
+      for (int t = max(0, do_issued - 2); t < do_issued; ++t) drain(smem_u32(&ss.do_full[t & 1]), (t >> 1) & 1, wc, 59);
     }
   } else if (warp == MMA_WARP) {
     // One thread issues every MMA.  A tcgen05.mma costs its issuer about 55 cycles whatever
@@ -567,10 +574,12 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         mbar_wait_warp(smem_u32(bar), parity, wc, site);
       };
       wait(&ss.kv_full, 0, 53);
-      wait(&ss.qdo_full[0], 0, 54);
+      wait(&ss.q_full[0], 0, 54);
       tc_fence_after();
       mma_nt<D>(tmem + ST_COL, k_km, q_km, idesc_nt);
       mma_commit_elect(smem_u32(&ss.st_full));
+      wait(&ss.do_full[0], 0, 55);
+      tc_fence_after();
       mma_nt<D>(tmem + DPT_COL, v_km, do_km, idesc_nt);
       mma_commit_elect(smem_u32(&ss.dpt_full));
       // every block but the last also starts the next block's S^T and dP^T
@@ -579,7 +588,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (more) {
           // S^T(t) is in registers and Q(t+1) has landed: the next scores can go
           wait(&ss.s_read, t & 1, 63);
-          wait(&ss.qdo_full[s ^ 1], ((t + 1) >> 1) & 1, 54);
+          wait(&ss.q_full[s ^ 1], ((t + 1) >> 1) & 1, 54);
           tc_fence_after();
           mma_nt<D>(tmem + ST_COL, k_km, q_km.advanced((s ^ 1) * TILE), idesc_nt);
           mma_commit_elect(smem_u32(&ss.st_full));
@@ -587,11 +596,14 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         wait(&ss.p_full, t & 1, 56);
         tc_fence_after();
         mma_sn<D>(tmem + DV_COL, p_km, do_mn.advanced(s * TILE), idesc_tn, t != 0);
+        mma_commit_elect(smem_u32(&ss.do_empty[s]));         // last use of dO(t)
         wait(&ss.ds_full, t & 1, 57);
         tc_fence_after();
         mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_mn.advanced(s * TILE), idesc_tn, t != 0);
-        mma_commit_elect(smem_u32(&ss.qdo_empty[s]));        // last use of Q(t) and dO(t)
+        mma_commit_elect(smem_u32(&ss.q_empty[s]));          // last use of Q(t)
         if (more) {
+          wait(&ss.do_full[s ^ 1], ((t + 1) >> 1) & 1, 55);
+          tc_fence_after();
           mma_nt<D>(tmem + DPT_COL, v_km, do_km.advanced((s ^ 1) * TILE), idesc_nt);
           mma_commit_elect(smem_u32(&ss.dpt_full));
         } else {
