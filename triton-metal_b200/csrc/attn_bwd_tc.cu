@@ -454,7 +454,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // ===========================================================================
 struct SharedDkdv {
   alignas(8) uint64_t kv_full;
-  alignas(8) uint64_t q_full[2], q_empty[2], do_full[2], do_empty[2];
+  alignas(8) uint64_t q_full[2][2], q_empty[2], do_full[2], do_empty[2];   // q_full[stage][64-column half]
   alignas(8) uint64_t st_full, s_read, p_full, dpt_full, ds_full, done;
   alignas(16) float lse[2][BLK];
   alignas(16) float delta[2][BLK];
@@ -508,7 +508,8 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ss.kv_full), 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&ss.q_full[s]), 1);
+      mbar_init(smem_u32(&ss.q_full[s][0]), 1);
+      mbar_init(smem_u32(&ss.q_full[s][1]), 1);
       mbar_init(smem_u32(&ss.q_empty[s]), 1);
       mbar_init(smem_u32(&ss.do_full[s]), 1);
       mbar_init(smem_u32(&ss.do_empty[s]), 1);
@@ -552,12 +553,18 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         load_tile<D>(do_addr + s * TILE, &map_do, smem_u32(&ss.do_full[s]), row0, bh);
         ++do_issued;
         if (!mbar_wait(smem_u32(&ss.q_empty[s]), ph ^ 1, wc, 51)) break;
-        mbar_expect_tx(smem_u32(&ss.q_full[s]), TILE);
-        load_tile<D>(q_addr + s * TILE, &map_q, smem_u32(&ss.q_full[s]), row0, bh);
+        // one barrier per 64-column half: the scores start on the first half while the second
+        // is still in flight
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          mbar_expect_tx(smem_u32(&ss.q_full[s][h]), BLK * 128);
+          tma_load_3d(q_addr + s * TILE + h * (BLK * 128), &map_q, smem_u32(&ss.q_full[s][h]), h * 64, row0, bh);
+        }
         ++issued;
       }
       drain(smem_u32(&ss.kv_full), 0, wc, 59);
-      for (int t = max(0, issued - 2); t < issued; ++t) drain(smem_u32(&ss.q_full[t & 1]), (t >> 1) & 1, wc, 59);
+      for (int t = max(0, issued - 2); t < issued; ++t)
+        for (int h = 0; h < D / 64; ++h) drain(smem_u32(&ss.q_full[t & 1][h]), (t >> 1) & 1, wc, 59);
       for (int t = max(0, do_issued - 2); t < do_issued; ++t) drain(smem_u32(&ss.do_full[t & 1]), (t >> 1) & 1, wc, 59);
     }
   } else if (warp == MMA_WARP) {
@@ -573,11 +580,23 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
         mbar_wait_warp(smem_u32(bar), parity, wc, site);
       };
+      // S^T = K Q(t)^T, one 64-column half of the head dimension at a time as Q's halves land
+      auto issue_scores = [&](int stage, uint32_t parity) {
+        const SmemDesc q = q_km.advanced(stage * TILE);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          wait(&ss.q_full[stage][h], parity, 54);
+          tc_fence_after();
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint32_t off = h * (BLK * 128) + q4 * 32;
+            mma_f16_ss_elect(tmem + ST_COL, k_km.at(off), q.at(off), idesc_nt, (h | q4) != 0);
+          }
+        }
+        mma_commit_elect(smem_u32(&ss.st_full));
+      };
       wait(&ss.kv_full, 0, 53);
-      wait(&ss.q_full[0], 0, 54);
-      tc_fence_after();
-      mma_nt<D>(tmem + ST_COL, k_km, q_km, idesc_nt);
-      mma_commit_elect(smem_u32(&ss.st_full));
+      issue_scores(0, 0);
       wait(&ss.do_full[0], 0, 55);
       tc_fence_after();
       mma_nt<D>(tmem + DPT_COL, v_km, do_km, idesc_nt);
@@ -588,10 +607,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         if (more) {
           // S^T(t) is in registers and Q(t+1) has landed: the next scores can go
           wait(&ss.s_read, t & 1, 63);
-          wait(&ss.q_full[s ^ 1], ((t + 1) >> 1) & 1, 54);
-          tc_fence_after();
-          mma_nt<D>(tmem + ST_COL, k_km, q_km.advanced((s ^ 1) * TILE), idesc_nt);
-          mma_commit_elect(smem_u32(&ss.st_full));
+          issue_scores(s ^ 1, ((t + 1) >> 1) & 1);
         }
         wait(&ss.p_full, t & 1, 56);
         tc_fence_after();
