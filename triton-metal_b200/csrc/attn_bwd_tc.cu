@@ -233,12 +233,38 @@ __device__ __forceinline__ void store_rows(uint32_t acc_tmem, T* orow, float sca
 constexpr int K_STAGES = 3, V_STAGES = 2;
 
 struct SharedDq {
-  alignas(8) uint64_t qdo_full;
+  alignas(8) uint64_t qdo_full, qdo_empty;
   alignas(8) uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
   alignas(8) uint64_t s_full[2];
   alignas(8) uint64_t dp_full, dp_read, ds_full, dq_done;
   uint32_t tmem_base;
   int abort_flag;
+};
+
+// Work list of a persistent kernel: a unit is one (batch, head) and one 128-row tile of the
+// resident side - or, under a causal mask, a long tile paired with a short one, so that every
+// unit costs the same.  `long_last` says which end of the sequence is long: query tile i sees
+// i + 1 key blocks (dq: the last tiles are long), key tile i is seen by T - i query blocks
+// (dkdv: the first are).  Units of one head are adjacent, so CTAs running side by side share
+// that head's streamed tensors in L2.
+struct TileSchedule {
+  int tiles;            // 128-row tiles per head
+  int units_per_head;
+  int total_units;
+  int causal;
+  int long_last;
+  __device__ __forceinline__ int subs(int u) const {
+    if (!causal) return 1;
+    const int k = u % units_per_head;
+    return (tiles - 1 - k != k) ? 2 : 1;
+  }
+  __device__ __forceinline__ int head(int u) const { return u / units_per_head; }
+  __device__ __forceinline__ int tile(int u, int sub) const {   // the long tile first
+    const int k = u % units_per_head;
+    if (!causal) return k;
+    const int far = tiles - 1 - k;
+    return (sub == 0) == (long_last != 0) ? far : k;
+  }
 };
 
 // Pipeline of block j (keys j*128 ...):
@@ -248,11 +274,14 @@ struct SharedDq {
 //   elem  dS(j) written over S[j&1]
 //   MMA   dQ += dS(j) K(j)
 // so the chain from one block's element-wise pass to the next is one MMA (dP) long.
+// Persistent: one CTA per SM walks its units; barrier phases follow running counters (`item`
+// query tiles, `c` key blocks), the K and V rings run on across tiles, and the loads and first
+// MMAs of the next tile go out while the element-wise warps still store the current dQ.
 template <typename T, int D, uint32_t FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                      Params prm, DeviceStatus* status) {
+                      Params prm, TileSchedule sch, DeviceStatus* status) {
   constexpr int TILE = BLK * D * 2;
   constexpr int S_COL = 0, DP_COL = 256, DQ_COL = 384;     // S[b] at b*128
   extern __shared__ uint8_t smem_raw[];
@@ -262,15 +291,16 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   SharedDq& ss = *reinterpret_cast<SharedDq*>(smem + (2 + K_STAGES + V_STAGES) * TILE);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   WaitCtx wc{&ss.abort_flag, status};
-  const int m_tile = prm.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-  const int bh = blockIdx.y;
-  const int m0 = m_tile * BLK;
-  int key_end = prm.n_ctx;
-  if (prm.causal) key_end = min(prm.n_ctx, m0 + BLK);
-  const int n_blocks = (key_end + BLK - 1) / BLK;
+  // key blocks the query tile starting at row m0 walks
+  auto key_blocks = [&](int m0) {
+    int key_end = prm.n_ctx;
+    if (prm.causal) key_end = min(prm.n_ctx, m0 + BLK);
+    return (key_end + BLK - 1) / BLK;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ss.qdo_full), 1);
+    mbar_init(smem_u32(&ss.qdo_empty), 1);
     for (int s = 0; s < K_STAGES; ++s) {
       mbar_init(smem_u32(&ss.k_full[s]), 1);
       mbar_init(smem_u32(&ss.k_empty[s]), 1);
@@ -303,44 +333,54 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
       tma_prefetch_desc(&map_do);
-      mbar_expect_tx(smem_u32(&ss.qdo_full), 2 * TILE);
-      load_tile<D>(q_addr, &map_q, smem_u32(&ss.qdo_full), m0, bh);
-      load_tile<D>(do_addr, &map_do, smem_u32(&ss.qdo_full), m0, bh);
-      // K runs up to two blocks ahead of V (its S MMA is issued two blocks early)
-      int k_issued = 0, v_issued = 0;
+      // ring positions run on across tiles; K is two blocks ahead of V inside a tile
+      uint32_t item = 0, k_issued = 0, v_issued = 0;
       bool ok = true;
-      auto load_k = [&](int j) {
-        const int s = j % K_STAGES;
-        if (!mbar_wait(smem_u32(&ss.k_empty[s]), ((j / K_STAGES) & 1) ^ 1, wc, 31)) return false;
+      auto load_k = [&](int j, int bh) {
+        const int s = k_issued % K_STAGES;
+        if (!mbar_wait(smem_u32(&ss.k_empty[s]), ((k_issued / K_STAGES) & 1) ^ 1, wc, 31)) return false;
         mbar_expect_tx(smem_u32(&ss.k_full[s]), TILE);
         load_tile<D>(k_addr + s * TILE, &map_k, smem_u32(&ss.k_full[s]), j * BLK, bh);
         ++k_issued;
         return true;
       };
-      auto load_v = [&](int j) {
-        const int s = j % V_STAGES;
-        if (!mbar_wait(smem_u32(&ss.v_empty[s]), ((j / V_STAGES) & 1) ^ 1, wc, 32)) return false;
+      auto load_v = [&](int j, int bh) {
+        const int s = v_issued % V_STAGES;
+        if (!mbar_wait(smem_u32(&ss.v_empty[s]), ((v_issued / V_STAGES) & 1) ^ 1, wc, 32)) return false;
         mbar_expect_tx(smem_u32(&ss.v_full[s]), TILE);
         load_tile<D>(v_addr + s * TILE, &map_v, smem_u32(&ss.v_full[s]), j * BLK, bh);
         ++v_issued;
         return true;
       };
-      if (n_blocks > 0) ok = load_k(0) && load_v(0);
-      if (ok && n_blocks > 1) ok = load_k(1);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        if (j + 1 < n_blocks && !load_v(j + 1)) break;
-        if (j + 2 < n_blocks && !load_k(j + 2)) break;
+      for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
+        const int bh = sch.head(u);
+        for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
+          const int m0 = sch.tile(u, sub) * BLK;
+          const int n_blocks = key_blocks(m0);
+          // Q and dO are single-buffered: the previous tile's last S and dP must have retired
+          if (!mbar_wait(smem_u32(&ss.qdo_empty), (item & 1) ^ 1, wc, 30)) { ok = false; break; }
+          mbar_expect_tx(smem_u32(&ss.qdo_full), 2 * TILE);
+          load_tile<D>(q_addr, &map_q, smem_u32(&ss.qdo_full), m0, bh);
+          load_tile<D>(do_addr, &map_do, smem_u32(&ss.qdo_full), m0, bh);
+          ok = load_k(0, bh) && load_v(0, bh);
+          if (ok && n_blocks > 1) ok = load_k(1, bh);
+          for (int j = 0; j < n_blocks && ok; ++j) {
+            if (j + 1 < n_blocks && !load_v(j + 1, bh)) { ok = false; break; }
+            if (j + 2 < n_blocks && !load_k(j + 2, bh)) { ok = false; break; }
+          }
+        }
       }
-      drain(smem_u32(&ss.qdo_full), 0, wc, 39);
-      for (int j = max(0, k_issued - K_STAGES); j < k_issued; ++j)
-        drain(smem_u32(&ss.k_full[j % K_STAGES]), (j / K_STAGES) & 1, wc, 39);
-      for (int j = max(0, v_issued - V_STAGES); j < v_issued; ++j)
-        drain(smem_u32(&ss.v_full[j % V_STAGES]), (j / V_STAGES) & 1, wc, 39);
+      // every copy started here must have landed before the CTA exits
+      if (item) drain(smem_u32(&ss.qdo_full), (item - 1) & 1, wc, 39);
+      for (uint32_t n = k_issued > K_STAGES ? k_issued - K_STAGES : 0; n < k_issued; ++n)
+        drain(smem_u32(&ss.k_full[n % K_STAGES]), (n / K_STAGES) & 1, wc, 39);
+      for (uint32_t n = v_issued > V_STAGES ? v_issued - V_STAGES : 0; n < v_issued; ++n)
+        drain(smem_u32(&ss.v_full[n % V_STAGES]), (n / V_STAGES) & 1, wc, 39);
     }
   } else if (warp == MMA_WARP) {
-    // One thread issues every MMA.  A tcgen05.mma costs its issuer about 55 cycles whatever
-    // its size (measured; a 128 x 128 x 16 one occupies the pipe for 64), a commit or a
-    // barrier wait about 50 more, so this loop is kept to the minimum of both.
+    // One warp issues every MMA.  A tcgen05.mma costs its issuer about 39 cycles whatever its
+    // size when the warp stays converged (57 from one diverged lane; a 128 x 128 x 16 one occupies
+    // the pipe for 64), a commit or a barrier wait about 50 more, every branch tens of cycles.
     // the whole warp runs this loop, converged; one elected lane issues (see mma_f16_ss_elect)
     {
       constexpr uint32_t idesc_nt = make_idesc(FMT, BLK, BLK, 0, 0);
@@ -350,94 +390,121 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       auto wait = [&](uint64_t* bar, uint32_t parity, uint32_t site) {
         mbar_wait_warp(smem_u32(bar), parity, wc, site);
       };
-      // S(j) = Q K(j)^T into S[j & 1]; `ks` = j mod K_STAGES, `kp` = parity of (j / K_STAGES)
-      auto issue_qk = [&](int j, int ks, uint32_t kp) {
-        wait(&ss.k_full[ks], kp, 34);
+      // running positions: c = key blocks done (S buffer c & 1, phases of dp/ds barriers),
+      // K ring position of the block dQ uses next (ks, kp) and of the block S uses next
+      // (ks2, kp2), V ring position (vs, vp)
+      uint32_t item = 0, c = 0, c_qk = 0;
+      int ks = 0, ks2 = 0, vs = 0;
+      uint32_t kp2 = 0, vp = 0;
+      auto issue_qk = [&]() {          // S of the next block not yet issued, into S[c_qk & 1]
+        wait(&ss.k_full[ks2], kp2, 34);
         tc_fence_after();
-        mma_nt<D>(tmem + S_COL + (j & 1) * BLK, q_km, k_km.advanced(ks * TILE), idesc_nt);
-        mma_commit_elect(smem_u32(&ss.s_full[j & 1]));
+        mma_nt<D>(tmem + S_COL + (c_qk & 1) * BLK, q_km, k_km.advanced(ks2 * TILE), idesc_nt);
+        mma_commit_elect(smem_u32(&ss.s_full[c_qk & 1]));
+        ++c_qk;
+        if (++ks2 == K_STAGES) { ks2 = 0; kp2 ^= 1; }
       };
-      auto issue_dp = [&](int j) {
-        const int s = j % V_STAGES;
-        wait(&ss.v_full[s], (j / V_STAGES) & 1, 35);
+      auto issue_dp = [&]() {
+        wait(&ss.v_full[vs], vp, 35);
         tc_fence_after();
-        mma_nt<D>(tmem + DP_COL, do_km, v_km.advanced(s * TILE), idesc_nt);
-        mma_commit_elect(smem_u32(&ss.v_empty[s]));
+        mma_nt<D>(tmem + DP_COL, do_km, v_km.advanced(vs * TILE), idesc_nt);
+        mma_commit_elect(smem_u32(&ss.v_empty[vs]));
         mma_commit_elect(smem_u32(&ss.dp_full));
+        if (++vs == V_STAGES) { vs = 0; vp ^= 1; }
       };
-      wait(&ss.qdo_full, 0, 33);
-      issue_qk(0, 0, 0);
-      issue_dp(0);
-      if (n_blocks > 1) issue_qk(1, 1, 0);
-      // ring position of K(j) and of K(j+2), carried along instead of divided out
-      int ks = 0, ks2 = 2 % K_STAGES;
-      uint32_t kp2 = (2 / K_STAGES) & 1;
-      auto block = [&](int j, bool next, bool next2) {
+      // one key block: `next` = another block follows in this tile, `next2` = two do
+      auto block = [&](bool first, bool next, bool next2) {
         if (next) {
           // the element-wise warps have dP(j) in registers: the next dP may overwrite it while
           // they are still working on block j
-          wait(&ss.dp_read, j & 1, 41);
-          issue_dp(j + 1);
+          wait(&ss.dp_read, c & 1, 41);
+          issue_dp();
+          // Q and dO are free once the tile's last S (issued a block earlier) and dP retire
+          if (!next2) mma_commit_elect(smem_u32(&ss.qdo_empty));
         }
-        wait(&ss.ds_full, j & 1, 36);
+        wait(&ss.ds_full, c & 1, 36);
         tc_fence_after();
-        mma_tn<D>(tmem + DQ_COL, tmem + S_COL + (j & 1) * BLK, k_mn.advanced(ks * TILE), idesc_tn, j != 0);
+        mma_tn<D>(tmem + DQ_COL, tmem + S_COL + (c & 1) * BLK, k_mn.advanced(ks * TILE), idesc_tn, !first);
         mma_commit_elect(smem_u32(&ss.k_empty[ks]));
         if (!next) mma_commit_elect(smem_u32(&ss.dq_done));
         // S(j+2) reuses the buffer dS(j) sits in: MMAs run in issue order
-        if (next2) issue_qk(j + 2, ks2, kp2);
+        if (next2) issue_qk();
+        ++c;
         if (++ks == K_STAGES) ks = 0;
-        if (++ks2 == K_STAGES) { ks2 = 0; kp2 ^= 1; }
       };
-      int j = 0;
-      for (; j + 2 < n_blocks; ++j) block(j, true, true);
-      if (j + 1 < n_blocks) { block(j, true, false); ++j; }
-      block(j, false, false);
+      for (int u = blockIdx.x; u < sch.total_units; u += gridDim.x) {
+        for (int sub = 0; sub < sch.subs(u); ++sub, ++item) {
+          const int n_blocks = key_blocks(sch.tile(u, sub) * BLK);
+          // The first S and dP of this tile go out while the element-wise warps may still be
+          // storing the previous dQ: they use other TMEM columns, and the first dQ MMA waits
+          // for ds_full, which those warps only signal after that store.
+          wait(&ss.qdo_full, item & 1, 33);
+          issue_qk();
+          issue_dp();
+          if (n_blocks > 1) issue_qk();
+          else mma_commit_elect(smem_u32(&ss.qdo_empty));
+          int j = 0;
+          if (n_blocks > 2) {
+            block(true, true, true);
+            for (j = 1; j + 2 < n_blocks; ++j) block(false, true, true);
+          }
+          if (j + 1 < n_blocks) { block(j == 0, true, false); ++j; }
+          block(j == 0, false, false);
+        }
+      }
     }
-  } else {
+  } else if (warp < EW_THREADS / 32) {
     const int group = warp / 4;                   // owns columns group*32 ... of every block
     const int row_in_tile = (warp % 4) * 32 + lane;
-    const int q_row = m0 + row_in_tile;
     const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
     const float qk_scale = prm.sm_scale * kLog2e;
-    float lse = 0.f, delta = 0.f;
-    if (q_row < prm.n_ctx) {
-      lse = prm.lse[(int64_t)bh * prm.stride_lse + q_row];
-      delta = prm.delta[(int64_t)bh * prm.stride_lse + q_row];
-    }
+    uint32_t item = 0, c = 0;
     bool ok = true;
-    for (int j = 0; j < n_blocks && ok; ++j) {
-      if (!mbar_wait(smem_u32(&ss.s_full[j & 1]), (j >> 1) & 1, wc, 37)) { ok = false; break; }
-      if (!mbar_wait(smem_u32(&ss.dp_full), j & 1, wc, 38)) { ok = false; break; }
-      tc_fence_after();
-      const int n0 = j * BLK + group * GCOLS;
-      const bool boundary = (n0 + GCOLS > prm.n_ctx) || (prm.causal && n0 + GCOLS > m0);
-      const KeyMask km{n0, q_row, prm.n_ctx, prm.causal};
-      const uint32_t s_tmem = tmem + lane_addr + S_COL + (j & 1) * BLK + group * GCOLS;
-      const uint32_t dp_tmem = tmem + lane_addr + DP_COL + group * GCOLS;
-      uint32_t sv[32], dv[32];
-      tmem_ld_32x32(dp_tmem, dv);
-      tmem_ld_32x32(s_tmem, sv);
-      tmem_ld_wait();
-      // dP(j) is in registers: let the next dP start
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ss.dp_read));
-      if (boundary) ds_part<T, true>(s_tmem, sv, dv, qk_scale, -lse, delta, km);
-      else ds_part<T, false>(s_tmem, sv, dv, qk_scale, -lse, delta, km);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ss.ds_full));   // one arrival per warp
-    }
-    if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&ss.dq_done), 0, wc, 40);
-    tc_fence_after();
-    if (ok && n_blocks > 0) {
-      // the groups share the columns of dQ, 32 at a time
-      constexpr int SC = 32;
-      if (group * SC < D) {
-        T* orow = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq + group * SC;
-        store_rows<T, SC>(tmem + lane_addr + DQ_COL + group * SC, orow, prm.sm_scale, q_row < prm.rows);
+    for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
+      const int bh = sch.head(u);
+      for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
+        const int m0 = sch.tile(u, sub) * BLK;
+        const int n_blocks = key_blocks(m0);
+        const int q_row = m0 + row_in_tile;
+        float lse = 0.f, delta = 0.f;
+        if (q_row < prm.n_ctx) {
+          lse = prm.lse[(int64_t)bh * prm.stride_lse + q_row];
+          delta = prm.delta[(int64_t)bh * prm.stride_lse + q_row];
+        }
+        for (int j = 0; j < n_blocks && ok; ++j, ++c) {
+          if (!mbar_wait(smem_u32(&ss.s_full[c & 1]), (c >> 1) & 1, wc, 37)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&ss.dp_full), c & 1, wc, 38)) { ok = false; break; }
+          tc_fence_after();
+          const int n0 = j * BLK + group * GCOLS;
+          const bool boundary = (n0 + GCOLS > prm.n_ctx) || (prm.causal && n0 + GCOLS > m0);
+          const KeyMask km{n0, q_row, prm.n_ctx, prm.causal};
+          const uint32_t s_tmem = tmem + lane_addr + S_COL + (c & 1) * BLK + group * GCOLS;
+          const uint32_t dp_tmem = tmem + lane_addr + DP_COL + group * GCOLS;
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32(dp_tmem, dv);
+          tmem_ld_32x32(s_tmem, sv);
+          tmem_ld_wait();
+          // dP(j) is in registers: let the next dP start
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ss.dp_read));
+          if (boundary) ds_part<T, true>(s_tmem, sv, dv, qk_scale, -lse, delta, km);
+          else ds_part<T, false>(s_tmem, sv, dv, qk_scale, -lse, delta, km);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ss.ds_full));   // one arrival per warp
+        }
+        if (ok) ok = mbar_wait(smem_u32(&ss.dq_done), item & 1, wc, 40);
+        tc_fence_after();
+        if (ok) {
+          // the groups share the columns of dQ, 32 at a time
+          constexpr int SC = 32;
+          if (group * SC < D) {
+            T* orow = (T*)prm.out0 + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq + group * SC;
+            store_rows<T, SC>(tmem + lane_addr + DQ_COL + group * SC, orow, prm.sm_scale, q_row < prm.rows);
+          }
+        }
       }
     }
   }
@@ -775,7 +842,14 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
     auto kernel = attn_bwd_dq_tc_kernel<T, D, FMT>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return std::string(what) + ": " + cudaGetErrorString(e);
-    kernel<<<grid, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, ctx.status);
+    TileSchedule sch{};
+    sch.tiles = (int)((p.rows + BLK - 1) / BLK);
+    sch.causal = p.causal;
+    sch.long_last = 1;
+    sch.units_per_head = p.causal ? (sch.tiles + 1) / 2 : sch.tiles;
+    sch.total_units = sch.units_per_head * (int)p.bh;
+    const int persistent = sch.total_units < ctx.sm_count ? sch.total_units : ctx.sm_count;
+    kernel<<<persistent, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, sch, ctx.status);
   }
   ++*ctx.launches;
   e = cudaGetLastError();
@@ -809,7 +883,8 @@ bool attn_bwd_tc_eligible(const AttnProblem& p, std::string* why) {
        (uintptr_t)p.out1) % 16)
     return no("base pointers are not 16-byte aligned");
   if (p.n_ctx < 128) return no("sequence shorter than one 128-row tile");
-  if (p.n_ctx > 0x7fffffff / 256 || p.bh > 65535) return no("extent out of range");
+  if (p.n_ctx > 0x7fffffff / 256 || p.bh > 65535 || (p.rows / 128 + 1) * p.bh > 0x7fffffff)
+    return no("extent out of range");
   return true;
 }
 
