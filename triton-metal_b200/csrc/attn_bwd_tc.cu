@@ -520,7 +520,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // dK, dV
 // ===========================================================================
 struct SharedDkdv {
-  alignas(8) uint64_t kv_full;
+  alignas(8) uint64_t kv_full, kv_empty;
   alignas(8) uint64_t q_full[2][2], q_empty[2], do_full[2], do_empty[2];   // q_full[stage][64-column half]
   alignas(8) uint64_t st_full, s_read, p_full, dpt_full, ds_full, done;
   alignas(16) float lse[2][BLK];
@@ -542,11 +542,14 @@ constexpr int P_TILE = BLK * BLK * 2;     // the 16-bit P^T tile in shared memor
 // P^T goes through shared memory because in TMEM it can only sit on top of S^T, and then
 // S^T(t+1) has to wait for dV(t), which has to wait for the whole exponential pass: that chain
 // (about 3500 cycles a block, measured) and not the 2048 cycles of tensor work set the pace.
+// Persistent like dq: one CTA per SM walks its units; phases follow running counters (`item` key
+// tiles, `c` query blocks), the Q and dO rings run on across tiles, and the next tile's K, V and
+// first MMAs go out while the element-wise warps still store the current dK and dV.
 template <typename T, int D, uint32_t FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                        Params prm, DeviceStatus* status) {
+                        Params prm, TileSchedule sch, DeviceStatus* status) {
   constexpr int TILE = BLK * D * 2;
   constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -557,11 +560,9 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   SharedDkdv& ss = *reinterpret_cast<SharedDkdv*>(smem + 6 * TILE + P_TILE);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   WaitCtx wc{&ss.abort_flag, status};
-  const int bh = blockIdx.y;
-  const int n0 = blockIdx.x * BLK;                       // first key row of this CTA
   const int total_q_blocks = (prm.n_ctx + BLK - 1) / BLK;
-  const int first = prm.causal ? n0 / BLK : 0;            // earlier queries never see these keys
-  const int n_iter = total_q_blocks - first;
+  // first query block that sees the key tile starting at row n0 (earlier queries never do)
+  auto first_block = [&](int n0) { return prm.causal ? n0 / BLK : 0; };
 
   // the swizzled tiles need the 1024-byte alignment asked for above
   if (k_addr & 1023u) {
@@ -574,6 +575,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ss.kv_full), 1);
+    mbar_init(smem_u32(&ss.kv_empty), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&ss.q_full[s][0]), 1);
       mbar_init(smem_u32(&ss.q_full[s][1]), 1);
@@ -605,34 +607,47 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
       tma_prefetch_desc(&map_do);
-      mbar_expect_tx(smem_u32(&ss.kv_full), 2 * TILE);
-      load_tile<D>(k_addr, &map_k, smem_u32(&ss.kv_full), n0, bh);
-      load_tile<D>(v_addr, &map_v, smem_u32(&ss.kv_full), n0, bh);
-      int issued = 0, do_issued = 0;
-      for (int t = 0; t < n_iter; ++t) {
-        const int s = t & 1;
-        const uint32_t ph = (t >> 1) & 1;
-        const int row0 = (first + t) * BLK;
-        // dO(t)'s slot is freed by dV(t-2), half a block before dK(t-2) frees Q(t)'s: dO goes
-        // first, and the Q refill - 32 KB, on the critical path of S^T(t) - is not held up by it
-        if (!mbar_wait(smem_u32(&ss.do_empty[s]), ph ^ 1, wc, 52)) break;
-        mbar_expect_tx(smem_u32(&ss.do_full[s]), TILE);
-        load_tile<D>(do_addr + s * TILE, &map_do, smem_u32(&ss.do_full[s]), row0, bh);
-        ++do_issued;
-        if (!mbar_wait(smem_u32(&ss.q_empty[s]), ph ^ 1, wc, 51)) break;
-        // one barrier per 64-column half: the scores start on the first half while the second
-        // is still in flight
+      uint32_t issued = 0, do_issued = 0;
+      uint32_t item = 0, c = 0;          // key tiles and query blocks loaded so far
+      bool ok = true;
+      for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
+        const int bh = sch.head(u);
+        for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
+          const int n0 = sch.tile(u, sub) * BLK;
+          const int first = first_block(n0), n_iter = total_q_blocks - first;
+          // K and V are single-buffered: the previous tile's last S^T and dP^T must have retired
+          if (!mbar_wait(smem_u32(&ss.kv_empty), (item & 1) ^ 1, wc, 50)) { ok = false; break; }
+          mbar_expect_tx(smem_u32(&ss.kv_full), 2 * TILE);
+          load_tile<D>(k_addr, &map_k, smem_u32(&ss.kv_full), n0, bh);
+          load_tile<D>(v_addr, &map_v, smem_u32(&ss.kv_full), n0, bh);
+          for (int t = 0; t < n_iter; ++t, ++c) {
+            const int s = c & 1;
+            const uint32_t ph = (c >> 1) & 1;
+            const int row0 = (first + t) * BLK;
+            // dO(t)'s slot is freed by dV(t-2), half a block before dK(t-2) frees Q(t)'s: dO goes
+            // first, and the Q refill - 32 KB, on the critical path of S^T(t) - is not held up by it
+            if (!mbar_wait(smem_u32(&ss.do_empty[s]), ph ^ 1, wc, 52)) { ok = false; break; }
+            mbar_expect_tx(smem_u32(&ss.do_full[s]), TILE);
+            load_tile<D>(do_addr + s * TILE, &map_do, smem_u32(&ss.do_full[s]), row0, bh);
+            ++do_issued;
+            if (!mbar_wait(smem_u32(&ss.q_empty[s]), ph ^ 1, wc, 51)) { ok = false; break; }
+            // one barrier per 64-column half: the scores start on the first half while the second
+            // is still in flight
 #pragma unroll
-        for (int h = 0; h < D / 64; ++h) {
-          mbar_expect_tx(smem_u32(&ss.q_full[s][h]), BLK * 128);
-          tma_load_3d(q_addr + s * TILE + h * (BLK * 128), &map_q, smem_u32(&ss.q_full[s][h]), h * 64, row0, bh);
+            for (int h = 0; h < D / 64; ++h) {
+              mbar_expect_tx(smem_u32(&ss.q_full[s][h]), BLK * 128);
+              tma_load_3d(q_addr + s * TILE + h * (BLK * 128), &map_q, smem_u32(&ss.q_full[s][h]), h * 64, row0, bh);
+            }
+            ++issued;
+          }
         }
-        ++issued;
       }
-      drain(smem_u32(&ss.kv_full), 0, wc, 59);
-      for (int t = max(0, issued - 2); t < issued; ++t)
-        for (int h = 0; h < D / 64; ++h) drain(smem_u32(&ss.q_full[t & 1][h]), (t >> 1) & 1, wc, 59);
-      for (int t = max(0, do_issued - 2); t < do_issued; ++t) drain(smem_u32(&ss.do_full[t & 1]), (t >> 1) & 1, wc, 59);
+      // every copy started here must have landed before the CTA exits
+      if (item) drain(smem_u32(&ss.kv_full), (item - 1) & 1, wc, 59);
+      for (uint32_t n = issued > 2 ? issued - 2 : 0; n < issued; ++n)
+        for (int h = 0; h < D / 64; ++h) drain(smem_u32(&ss.q_full[n & 1][h]), (n >> 1) & 1, wc, 59);
+      for (uint32_t n = do_issued > 2 ? do_issued - 2 : 0; n < do_issued; ++n)
+        drain(smem_u32(&ss.do_full[n & 1]), (n >> 1) & 1, wc, 59);
     }
   } else if (warp == MMA_WARP) {
     // One thread issues every MMA.  A tcgen05.mma costs its issuer about 55 cycles whatever
@@ -662,123 +677,152 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         mma_commit_elect(smem_u32(&ss.st_full));
       };
-      wait(&ss.kv_full, 0, 53);
-      issue_scores(0, 0);
-      wait(&ss.do_full[0], 0, 55);
-      tc_fence_after();
-      mma_nt<D>(tmem + DPT_COL, v_km, do_km, idesc_nt);
-      mma_commit_elect(smem_u32(&ss.dpt_full));
-      // every block but the last also starts the next block's S^T and dP^T
-      auto block = [&](int t, bool more) {
-        const int s = t & 1;
+      // One query block; c counts them across tiles (ring stage c & 1, phases from c).
+      // `first` = first block of its key tile, `more` = another block of this tile follows;
+      // every block but a tile's last also starts the next block's S^T and dP^T.
+      uint32_t item = 0, c = 0;
+      auto block = [&](bool first, bool more, bool release_kv) {
+        const int s = c & 1;
         if (more) {
           // S^T(t) is in registers and Q(t+1) has landed: the next scores can go
-          wait(&ss.s_read, t & 1, 63);
-          issue_scores(s ^ 1, ((t + 1) >> 1) & 1);
+          wait(&ss.s_read, c & 1, 63);
+          issue_scores(s ^ 1, ((c + 1) >> 1) & 1);
         }
-        wait(&ss.p_full, t & 1, 56);
+        wait(&ss.p_full, c & 1, 56);
         tc_fence_after();
-        mma_sn<D>(tmem + DV_COL, p_km, do_mn.advanced(s * TILE), idesc_tn, t != 0);
+        mma_sn<D>(tmem + DV_COL, p_km, do_mn.advanced(s * TILE), idesc_tn, !first);
         mma_commit_elect(smem_u32(&ss.do_empty[s]));         // last use of dO(t)
-        wait(&ss.ds_full, t & 1, 57);
+        wait(&ss.ds_full, c & 1, 57);
         tc_fence_after();
-        mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_mn.advanced(s * TILE), idesc_tn, t != 0);
+        mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_mn.advanced(s * TILE), idesc_tn, !first);
         mma_commit_elect(smem_u32(&ss.q_empty[s]));          // last use of Q(t)
         if (more) {
-          wait(&ss.do_full[s ^ 1], ((t + 1) >> 1) & 1, 55);
+          wait(&ss.do_full[s ^ 1], ((c + 1) >> 1) & 1, 55);
           tc_fence_after();
           mma_nt<D>(tmem + DPT_COL, v_km, do_km.advanced((s ^ 1) * TILE), idesc_nt);
           mma_commit_elect(smem_u32(&ss.dpt_full));
+          // K and V are free once the tile's last S^T and dP^T (both just issued) retire
+          if (release_kv) mma_commit_elect(smem_u32(&ss.kv_empty));
         } else {
           mma_commit_elect(smem_u32(&ss.done));
         }
+        ++c;
       };
-      for (int t = 0; t + 1 < n_iter; ++t) block(t, true);
-      block(n_iter - 1, false);
+      for (int u = blockIdx.x; u < sch.total_units; u += gridDim.x) {
+        for (int sub = 0; sub < sch.subs(u); ++sub, ++item) {
+          const int n_iter = total_q_blocks - first_block(sch.tile(u, sub) * BLK);
+          // The first S^T and dP^T of this tile go out while the element-wise warps may still be
+          // storing the previous dK and dV: they use other TMEM columns, and the first dV and dK
+          // MMAs wait for p_full / ds_full, which those warps only signal after that store.
+          wait(&ss.kv_full, item & 1, 53);
+          issue_scores(c & 1, (c >> 1) & 1);
+          wait(&ss.do_full[c & 1], (c >> 1) & 1, 55);
+          tc_fence_after();
+          mma_nt<D>(tmem + DPT_COL, v_km, do_km.advanced((c & 1) * TILE), idesc_nt);
+          mma_commit_elect(smem_u32(&ss.dpt_full));
+          if (n_iter == 1) mma_commit_elect(smem_u32(&ss.kv_empty));
+          int t = 0;
+          if (n_iter > 2) {
+            block(true, true, false);
+            for (t = 1; t + 2 < n_iter; ++t) block(false, true, false);
+          }
+          if (t + 1 < n_iter) { block(t == 0, true, true); ++t; }
+          block(t == 0, false, false);
+        }
+      }
     }
   } else if (warp < EW_THREADS / 32) {
     const int group = warp / 4;                   // owns query columns group*32 ... of every block
     const int row_in_tile = (warp % 4) * 32 + lane;
-    const int k_row = n0 + row_in_tile;
     const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
     const float qk_scale = prm.sm_scale * kLog2e;
-    const float* lse_base = prm.lse + (int64_t)bh * prm.stride_lse;
-    const float* delta_base = prm.delta + (int64_t)bh * prm.stride_lse;
     // This thread's 64 bytes of a P^T row in the K-major, 128-byte-swizzled tile: 64-query
     // atoms 16 KiB apart, rows of 128 bytes, 16-byte chunks XORed with the row (mod 8).
     const uint32_t p_row = p_addr + (group / 2) * (BLK * 128) + row_in_tile * 128;
     const uint32_t p_chunk0 = (group % 2) * 4, p_xor = row_in_tile & 7;
-    // Row statistics of the streamed query block go through shared memory (every thread
-    // needs 32 of each): the threads of group 0 fetch the 128 values of L, those of group 1
-    // the 128 values of Delta.  The global load for block t+1 is issued at the top of
-    // iteration t into a register and stored to shared memory at its end, so its latency is
-    // off the critical path.  +inf as L makes exp2(x - L) vanish for queries past the end.
-    auto fetch_stat = [&](int t) -> float {
-      const int q = (first + t) * BLK + row_in_tile;
-      float v = group ? 0.f : INFINITY;
-      if (group < 2 && q < prm.n_ctx) {
-        const float* src = (group ? delta_base : lse_base) + q;
-        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(src));
-      }
-      return v;
-    };
-    auto put_stat = [&](int t, float v) {
-      if (group == 1) ss.delta[t & 1][row_in_tile] = v;
-      else if (group == 0) ss.lse[t & 1][row_in_tile] = v;
-    };
-    if (n_iter > 0) put_stat(0, fetch_stat(0));
+    uint32_t item = 0, c = 0;
     bool ok = true;
-    for (int t = 0; t < n_iter && ok; ++t) {
-      // all element-wise threads: statistics of block t are visible, block t-1 is no longer read
-      asm volatile("bar.sync 1, %0;" ::"n"(EW_THREADS) : "memory");
-      float next_stat = 0.f;
-      if (t + 1 < n_iter) next_stat = fetch_stat(t + 1);
-      const float* lse_s = ss.lse[t & 1] + group * GCOLS;
-      const float* delta_s = ss.delta[t & 1] + group * GCOLS;
-      const int q0 = (first + t) * BLK + group * GCOLS;     // first query of this group's columns
-      const bool diagonal = prm.causal && q0 < n0 + BLK;
-      if (!mbar_wait(smem_u32(&ss.st_full), t & 1, wc, 58)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t sv[32];
-      tmem_ld_32x32(tmem + lane_addr + ST_COL + group * GCOLS, sv);
-      tmem_ld_wait();
-      // S^T(t) is in registers: the next scores may overwrite it
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ss.s_read));
-      uint32_t keep[16];
-      if (diagonal) pt_part<T, true>(sv, qk_scale, lse_s, k_row - q0, keep);
-      else pt_part<T, false>(sv, qk_scale, lse_s, 0, keep);
-      // dV(t-1) must have read the previous P^T before it is replaced: dP^T(t) was issued after
-      // it, so its commit covers it (and is waited for here instead of before the dS^T pass)
-      if (!mbar_wait(smem_u32(&ss.dpt_full), t & 1, wc, 60)) { ok = false; break; }
+    for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
+      const int bh = sch.head(u);
+      const float* lse_base = prm.lse + (int64_t)bh * prm.stride_lse;
+      const float* delta_base = prm.delta + (int64_t)bh * prm.stride_lse;
+      for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
+        const int n0 = sch.tile(u, sub) * BLK;
+        const int first = first_block(n0), n_iter = total_q_blocks - first;
+        const int k_row = n0 + row_in_tile;
+        // Row statistics of the streamed query block go through shared memory (every thread
+        // needs 32 of each): the threads of group 0 fetch the 128 values of L, those of group 1
+        // the 128 values of Delta.  The global load for block t+1 is issued at the top of
+        // iteration t into a register and stored to shared memory at its end, so its latency is
+        // off the critical path.  +inf as L makes exp2(x - L) vanish for queries past the end.
+        auto fetch_stat = [&](int t) -> float {
+          const int q = (first + t) * BLK + row_in_tile;
+          float v = group ? 0.f : INFINITY;
+          if (group < 2 && q < prm.n_ctx) {
+            const float* src = (group ? delta_base : lse_base) + q;
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(src));
+          }
+          return v;
+        };
+        auto put_stat = [&](uint32_t slot, float v) {
+          if (group == 1) ss.delta[slot & 1][row_in_tile] = v;
+          else if (group == 0) ss.lse[slot & 1][row_in_tile] = v;
+        };
+        // slot c & 1 was last read in block c - 2, two barriers ago
+        put_stat(c, fetch_stat(0));
+        for (int t = 0; t < n_iter && ok; ++t, ++c) {
+          // all element-wise threads: statistics of block t are visible, block t-1 is no longer read
+          asm volatile("bar.sync 1, %0;" ::"n"(EW_THREADS) : "memory");
+          float next_stat = 0.f;
+          if (t + 1 < n_iter) next_stat = fetch_stat(t + 1);
+          const float* lse_s = ss.lse[c & 1] + group * GCOLS;
+          const float* delta_s = ss.delta[c & 1] + group * GCOLS;
+          const int q0 = (first + t) * BLK + group * GCOLS;     // first query of this group's columns
+          const bool diagonal = prm.causal && q0 < n0 + BLK;
+          if (!mbar_wait(smem_u32(&ss.st_full), c & 1, wc, 58)) { ok = false; break; }
+          tc_fence_after();
+          uint32_t sv[32];
+          tmem_ld_32x32(tmem + lane_addr + ST_COL + group * GCOLS, sv);
+          tmem_ld_wait();
+          // S^T(t) is in registers: the next scores may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ss.s_read));
+          uint32_t keep[16];
+          if (diagonal) pt_part<T, true>(sv, qk_scale, lse_s, k_row - q0, keep);
+          else pt_part<T, false>(sv, qk_scale, lse_s, 0, keep);
+          // dV(t-1) must have read the previous P^T before it is replaced: dP^T(t) was issued after
+          // it, so its commit covers it (and is waited for here instead of before the dS^T pass)
+          if (!mbar_wait(smem_u32(&ss.dpt_full), c & 1, wc, 60)) { ok = false; break; }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t dst = p_row + (((p_chunk0 + i) ^ p_xor) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(keep[4 * i]), "r"(keep[4 * i + 1]),
-                     "r"(keep[4 * i + 2]), "r"(keep[4 * i + 3])
-                     : "memory");
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t dst = p_row + (((p_chunk0 + i) ^ p_xor) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(keep[4 * i]),
+                         "r"(keep[4 * i + 1]), "r"(keep[4 * i + 2]), "r"(keep[4 * i + 3])
+                         : "memory");
+          }
+          fence_proxy_async();          // the tensor core reads shared memory through the async proxy
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ss.p_full));
+          tc_fence_after();
+          dst_part<T>(tmem + lane_addr + DPT_COL + group * GCOLS, delta_s, keep);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ss.ds_full));   // one arrival per warp
+          if (t + 1 < n_iter) put_stat(c + 1, next_stat);
+        }
+        if (ok) ok = mbar_wait(smem_u32(&ss.done), item & 1, wc, 61);
+        tc_fence_after();
+        if (ok) {
+          // groups 0 and 1 store the halves of dV, groups 2 and 3 those of dK
+          const bool live = k_row < prm.rows;
+          const int c0 = (group & 1) * (D / 2);
+          const int64_t row_off = (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq + c0;
+          if (group < 2) store_rows<T, D / 2>(tmem + lane_addr + DV_COL + c0, (T*)prm.out1 + row_off, 1.f, live);
+          else store_rows<T, D / 2>(tmem + lane_addr + DK_COL + c0, (T*)prm.out0 + row_off, prm.sm_scale, live);
+        }
       }
-      fence_proxy_async();          // the tensor core reads shared memory through the async proxy
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ss.p_full));
-      tc_fence_after();
-      dst_part<T>(tmem + lane_addr + DPT_COL + group * GCOLS, delta_s, keep);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ss.ds_full));   // one arrival per warp
-      if (t + 1 < n_iter) put_stat(t + 1, next_stat);
-    }
-    if (ok && n_iter > 0) ok = mbar_wait(smem_u32(&ss.done), 0, wc, 61);
-    tc_fence_after();
-    if (ok && n_iter > 0) {
-      // groups 0 and 1 store the halves of dV, groups 2 and 3 those of dK
-      const bool live = k_row < prm.rows;
-      const int c0 = (group & 1) * (D / 2);
-      const int64_t row_off = (int64_t)bh * prm.stride_head + (int64_t)k_row * prm.stride_seq + c0;
-      if (group < 2) store_rows<T, D / 2>(tmem + lane_addr + DV_COL + c0, (T*)prm.out1 + row_off, 1.f, live);
-      else store_rows<T, D / 2>(tmem + lane_addr + DK_COL + c0, (T*)prm.out0 + row_off, prm.sm_scale, live);
     }
   }
   tc_fence_before();
@@ -833,22 +877,22 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   if (smem < 120 * 1024) smem = 120 * 1024;
   dim3 grid((unsigned)((p.rows + BLK - 1) / BLK), (unsigned)p.bh, 1);
   cudaError_t e;
+  TileSchedule sch{};
+  sch.tiles = (int)((p.rows + BLK - 1) / BLK);
+  sch.causal = p.causal;
+  sch.long_last = dkdv ? 0 : 1;       // early key tiles are seen by every query block, late query tiles see every key
+  sch.units_per_head = p.causal ? (sch.tiles + 1) / 2 : sch.tiles;
+  sch.total_units = sch.units_per_head * (int)p.bh;
+  const int persistent = sch.total_units < ctx.sm_count ? sch.total_units : ctx.sm_count;
   if (dkdv) {
     auto kernel = attn_bwd_dkdv_tc_kernel<T, D, FMT>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return std::string(what) + ": " + cudaGetErrorString(e);
-    kernel<<<grid, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, ctx.status);
+    kernel<<<persistent, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, sch, ctx.status);
   } else {
     auto kernel = attn_bwd_dq_tc_kernel<T, D, FMT>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return std::string(what) + ": " + cudaGetErrorString(e);
-    TileSchedule sch{};
-    sch.tiles = (int)((p.rows + BLK - 1) / BLK);
-    sch.causal = p.causal;
-    sch.long_last = 1;
-    sch.units_per_head = p.causal ? (sch.tiles + 1) / 2 : sch.tiles;
-    sch.total_units = sch.units_per_head * (int)p.bh;
-    const int persistent = sch.total_units < ctx.sm_count ? sch.total_units : ctx.sm_count;
     kernel<<<persistent, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, sch, ctx.status);
   }
   ++*ctx.launches;
