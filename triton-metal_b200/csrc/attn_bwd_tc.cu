@@ -9,10 +9,12 @@
 // directions stay separate kernels, as in the reference, so every gradient is
 // deterministic (no atomics).
 //
-// Both kernels: one CTA per 128 resident rows of one (batch, head) (queries for
-// dq, keys for dkdv); the other side streams through in blocks of 128 rows (MMAs
-// with N = 128: narrower score tiles ran the tensor pipe at half rate, measured).
-// Warp 16 issues TMA loads, warp 17 issues every tcgen05.mma, and four warpgroups (warps
+// Both kernels are persistent: one CTA per SM walks work units of 128 resident rows of one
+// (batch, head) (queries for dq, keys for dkdv; under a causal mask a long tile paired with a
+// short one); the other side streams through in blocks of 128 rows (MMAs with N = 128:
+// narrower score tiles ran the tensor pipe at half rate, measured).
+// Warp 16 issues TMA loads, warp 17 - converged, one lane elected per instruction - issues every
+// tcgen05.mma, and four warpgroups (warps
 // 0-15) do the exponentials and products: a thread owns one resident row (its TMEM lane)
 // and one quarter of the 128 columns of a block, so the TMEM round trips of one group are
 // covered by the arithmetic of the others.  The element-wise warps copy a fresh score (or
@@ -20,10 +22,11 @@
 // those columns does not wait for the exponentials.  dS (and P in dq) go back into TMEM over
 // the fp32 columns they were computed from and feed the next MMA as TMEM operands; P^T in
 // dkdv goes through shared memory (see there).  Measured on a B200, per SM: a tcgen05.mma
-// costs the issuing thread about 55 cycles whatever its size (a 128 x 128 x 16 one occupies
-// the tensor pipe for 64, so one issuer just keeps up and N = 64 runs at half rate), a
-// tcgen05.commit or a completed barrier wait about 50; two issuing warps interleave their
-// MMAs and were slower; ex2.approx runs at 16 per cycle.
+// costs its issuer about 57 cycles from one lane of a diverged warp and 39 from a converged
+// warp, whatever its size (a 128 x 128 x 16 one occupies the tensor pipe for 64, and N = 64
+// runs at half rate), a tcgen05.commit or a completed barrier wait about 50, a branch of the
+// lone issuing warp tens of cycles; two issuing warps interleave their MMAs and were slower;
+// ex2.approx runs at 16 per cycle.
 //
 // TMEM columns (512):  dq:    S[2] (dS aliases) | dP | dQ
 //                      dkdv:  S^T | dP^T (dS^T aliases) | dV | dK
