@@ -175,3 +175,87 @@ def test_attention_argument_validation(core):
         fwd.release()
         small.free()
         stat.free()
+
+
+# ---- the tcgen05 kernels: persistent CTAs, ragged sequences, several work units per CTA ----
+
+@pytest.mark.parametrize("bh,seq,d,causal", [
+    (3, 384, 64, True), (2, 1000, 128, True), (2, 1000, 128, False), (5, 2304, 64, False),
+    (1, 128, 128, True), (2, 130, 128, False),
+])
+def test_tensor_core_paths_on_ragged_and_long_sequences(bh, seq, d, causal):
+    q, k, v, do = inputs.attention_normal(bh, seq, d, seed=seq + d + causal)
+    paths = check_all(q, k, v, do, "bf16", causal, path=cuda.PATH_TCGEN05)
+    assert [paths[n] for n in ("fwd", "dq", "dkdv")] == [cuda.PATH_TCGEN05] * 3
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_more_work_units_than_sms(causal):
+    """160 heads of 512 rows: every persistent CTA walks several units (and, under a causal mask,
+    long and short tiles alternately); three heads are checked against the oracle."""
+    bh, seq, d = 160, 512, 128
+    q, k, v, do = (ref.round_to(t, "bf16") for t in inputs.attention_normal(bh, seq, d, seed=11))
+    heads = [0, 77, 159]
+    want = tmtest.oracle_attention(q[heads], k[heads], v[heads], do[heads], causal)
+    with tmtest.AttentionRun(q, k, v, do, "bf16", causal, (128, 128), cuda.PATH_TCGEN05) as run:
+        o, lse = run.forward()
+        dq, dk, dv = run.backward()
+    for name, got, ref_value in zip(("O", "dQ", "dK", "dV"), (o, dq, dk, dv),
+                                    (want[0], want[2], want[3], want[4])):
+        assert ref.relative_error(got[heads], ref_value) <= 2e-2, name
+    assert np.max(np.abs(lse[heads] - want[1])) <= 2e-2
+    # no head was skipped or written twice with something else: every head is finite and non-zero
+    for got in (o, dq, dk, dv):
+        per_head = np.abs(got.astype(np.float32)).reshape(bh, -1).max(axis=1)
+        assert np.all(np.isfinite(per_head)) and np.all(per_head > 0)
+
+
+def test_tensor_core_paths_leave_rows_outside_the_grid_alone():
+    """grid_x covers 3 of 8 row blocks: the other rows of O, dQ, dK, dV keep their sentinel."""
+    from triton_metal import kernels
+    from triton_metal.buffer import MetalBuffer
+    bh, seq, d, blocks = 2, 1024, 128, 3
+    q, k, v, do = (ref.round_to(t, "bf16") for t in inputs.attention_normal(bh, seq, d, seed=5))
+    dt = ref.storage_dtype("bf16")
+    want = tmtest.oracle_attention(q, k, v, do, False)
+    scale = kernels.default_scale(d)
+    bufs = {n: MetalBuffer.from_numpy(t.astype(dt)) for n, t in (("q", q), ("k", k), ("v", v), ("do", do))}
+    sentinel = np.full((bh, seq, d), -7.0, dtype=np.float32).astype(dt)
+    for n in ("o", "dq", "dk", "dv"):
+        bufs[n] = MetalBuffer.from_numpy(sentinel)
+    for n in ("lse", "delta"):
+        bufs[n] = MetalBuffer((bh, seq), "float32")
+    h = {n: b.tm_handle for n, b in bufs.items()}
+    fwd = kernels.AttnFwd("bf16", d, (128, 128), False)
+    pre = kernels.AttnBwdPreprocess("bf16", d, 128)
+    dq = kernels.AttnBwdDq("bf16", d, (128, 128), False)
+    dkdv = kernels.AttnBwdDkdv("bf16", d, (128, 128), False)
+    try:
+        for kern in (fwd, dq, dkdv):
+            kern.set_path(cuda.PATH_TCGEN05)
+        # the forward and the preprocess over every row (the backward reads L and Delta of all
+        # queries), then dQ and dK/dV over the first `blocks` row blocks only
+        fwd(h["q"], h["k"], h["v"], h["o"], h["lse"], scale, bh, seq)
+        full_o = bufs["o"].numpy().astype(np.float32).copy()
+        pre(h["o"], h["do"], h["delta"], bh, seq)
+        bufs["o"].copy_from(sentinel.ctypes.data, sentinel.nbytes)
+        for kern, args in ((fwd, (h["q"], h["k"], h["v"], h["o"], h["lse"], scale, bh, seq)),
+                           (dq, (h["q"], h["k"], h["v"], h["do"], h["dq"], h["lse"], h["delta"], scale, bh, seq)),
+                           (dkdv, (h["q"], h["k"], h["v"], h["do"], h["dk"], h["dv"], h["lse"], h["delta"],
+                                   scale, bh, seq))):
+            grid, kinds, values = kern.arguments(*args)
+            kern.launch((blocks, grid[1], grid[2]), kinds, values)
+        rows = blocks * 128
+        got = {n: bufs[n].numpy().astype(np.float32).reshape(bh, seq, d) for n in ("o", "dq", "dk", "dv")}
+        assert ref.relative_error(full_o, want[0]) <= 2e-2
+        assert ref.relative_error(got["o"][:, :rows], want[0][:, :rows]) <= 2e-2
+        assert ref.relative_error(got["dq"][:, :rows], want[2][:, :rows]) <= 2e-2
+        assert ref.relative_error(got["dk"][:, :rows], want[3][:, :rows]) <= 2e-2
+        assert ref.relative_error(got["dv"][:, :rows], want[4][:, :rows]) <= 2e-2
+        for n in ("o", "dq", "dk", "dv"):
+            assert np.all(got[n][:, rows:] == -7.0), n
+    finally:
+        for kern in (fwd, pre, dq, dkdv):
+            kern.release()
+        for b in bufs.values():
+            b.free()
