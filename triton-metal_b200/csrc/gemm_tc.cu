@@ -197,7 +197,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // the whole warp runs this loop, converged; one elected lane issues (see mma_f16_ss_elect)
+    {
       constexpr uint32_t idesc = make_idesc(FMT, BM, BN, 0, 1);
       const SmemDesc a_base = make_desc_sw128(smem_base, 0, 1024);
       const SmemDesc b_base = make_desc_sw128(smem_base + A_BYTES, B_BOX_BYTES, 1024);
@@ -208,11 +209,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
-        if (!mbar_wait(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1, wc, kMmaAccEmpty)) { ok = false; break; }
+        if (!mbar_wait_warp(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1, wc, kMmaAccEmpty)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(smem_u32(&ss.full[stage]), phase, wc, kMmaFull)) { ok = false; break; }
+          if (!mbar_wait_warp(smem_u32(&ss.full[stage]), phase, wc, kMmaFull)) { ok = false; break; }
           tc_fence_after();
           const SmemDesc a_desc = a_base.advanced(stage * STAGE_BYTES);
           const SmemDesc b_desc = b_base.advanced(stage * STAGE_BYTES);
@@ -220,12 +221,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int k = 0; k < BK / 16; ++k) {
             // A: K-major, 16 elements = 32 bytes further along the 128-byte row.
             // B: MN-major, 16 K rows = 2048 bytes further; 64-column blocks 8 KiB apart.
-            mma_f16_ss(d_tmem, a_desc.at(k * 32), b_desc.at(k * 2048), idesc, (kb | k) != 0);
+            mma_f16_ss_elect(d_tmem, a_desc.at(k * 32), b_desc.at(k * 2048), idesc, (kb | k) != 0);
           }
-          mma_commit(smem_u32(&ss.empty[stage]));
+          mma_commit_elect(smem_u32(&ss.empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) mma_commit(smem_u32(&ss.acc_full[acc]));
+        if (ok) mma_commit_elect(smem_u32(&ss.acc_full[acc]));
       }
       // All MMAs must have retired before TMEM is released: commit to a drained
       // barrier slot and wait for it (bounded).  acc_full[0..1] may still be in use
