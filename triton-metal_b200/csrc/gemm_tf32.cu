@@ -178,7 +178,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
       }
     }
   } else if (warp == 5) {
-    if (lane == 0) {
+    // the whole warp runs this loop, converged; one elected lane issues (see mma_f16_ss_elect)
+    {
       constexpr uint32_t idesc = make_idesc(2, BM, BN, 0, 0);     // tf32, both operands K-major
       int stage = 0;
       uint32_t phase = 0;
@@ -189,12 +190,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
         for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += CHUNK_KB, ++local) {
           const int acc = local & 1;
           const uint32_t acc_phase = (local >> 1) & 1;
-          if (!mbar_wait(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1, wc, 73)) { ok = false; break; }
+          if (!mbar_wait_warp(smem_u32(&ss.acc_empty[acc]), acc_phase ^ 1, wc, 73)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BN;
           const int kb_end = min(k_blocks, kb0 + CHUNK_KB);
           for (int kb = kb0; kb < kb_end; ++kb) {
-            if (!mbar_wait(smem_u32(&ss.full[stage]), phase, wc, 72)) { ok = false; break; }
+            if (!mbar_wait_warp(smem_u32(&ss.full[stage]), phase, wc, 72)) { ok = false; break; }
             tc_fence_after();
             // operands of a stage: A hi | A lo | B hi | B lo
             const SmemDesc ahi = stage_base.advanced(stage * STAGE_BYTES);
@@ -205,14 +206,14 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_const
               const uint64_t d_alo = ahi.at(A_BYTES + k * 32);
               const uint64_t d_bhi = ahi.at(2 * A_BYTES + k * 32);
               const uint64_t d_blo = ahi.at(2 * A_BYTES + B_BYTES + k * 32);
-              mma_tf32_ss(d_tmem, d_alo, d_bhi, idesc, (kb != kb0) || k != 0);
-              mma_tf32_ss(d_tmem, d_ahi, d_blo, idesc, 1);
-              mma_tf32_ss(d_tmem, d_ahi, d_bhi, idesc, 1);
+              mma_tf32_ss_elect(d_tmem, d_alo, d_bhi, idesc, (kb != kb0) || k != 0);
+              mma_tf32_ss_elect(d_tmem, d_ahi, d_blo, idesc, 1);
+              mma_tf32_ss_elect(d_tmem, d_ahi, d_bhi, idesc, 1);
             }
-            mma_commit(smem_u32(&ss.empty[stage]));
+            mma_commit_elect(smem_u32(&ss.empty[stage]));
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
-          if (ok) mma_commit(smem_u32(&ss.acc_full[acc]));
+          if (ok) mma_commit_elect(smem_u32(&ss.acc_full[acc]));
         }
       }
     }
