@@ -82,9 +82,9 @@ def config_of(name):
 #: dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 #: ncu captures summarised under profiles/ (same workload sizes as the benchmark).
 NCU_TRAFFIC_BYTES = {
-    "gemm_bf16_8192": 1124.5e6,
-    "attn_fwd_bf16_s4096": 515.9e6,
-    "attn_bwd_bf16_s4096_d128": 781.5e6,   # dkdv, the dominant of the three backward kernels
+    "gemm_bf16_8192": 1106.4e6,
+    "attn_fwd_bf16_s4096": 518.1e6,
+    "attn_bwd_bf16_s4096_d128": 776.4e6,   # dkdv, the dominant of the three backward kernels
 }
 
 
