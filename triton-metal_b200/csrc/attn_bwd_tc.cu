@@ -653,9 +653,8 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         drain(smem_u32(&ss.do_full[n & 1]), (n >> 1) & 1, wc, 59);
     }
   } else if (warp == MMA_WARP) {
-    // One thread issues every MMA.  A tcgen05.mma costs its issuer about 55 cycles whatever
-    // its size (measured; a 128 x 128 x 16 one occupies the pipe for 64), a commit or a
-    // barrier wait about 50 more: four waits and four commits per block, no more.
+    // One warp issues every MMA (cost of issuing: see the head of this file): per block five
+    // waits and five commits, no branch that does not depend on a barrier.
     // the whole warp runs this loop, converged; one elected lane issues (see mma_f16_ss_elect)
     {
       constexpr uint32_t idesc_nt = make_idesc(FMT, BLK, BLK, 0, 0);
