@@ -193,6 +193,23 @@ int32_t tmx_matmul_f32_static(int64_t a, int64_t b, int64_t c, int64_t M, int64_
 /* Size in bytes of the fixed scratch array behind tmx_matmul_f32_static. */
 int64_t tmx_matmul_f32_static_capacity(void);
 
+/* ---- failure-path aids (no counterpart in the reference) -------------------
+ *
+ * Every wait inside the tensor-core kernels is bounded: when its cycle budget runs out the
+ * kernel records where in a host-visible status word and returns, and the next call that
+ * synchronises (tm_launch, tm_buffer_read/write, tmx_synchronize, tmx_timer_end) returns -1
+ * with "a bounded wait gave up inside the kernel ..." and clears the word.  These two entry
+ * points let a test suite walk that path without breaking a kernel. */
+
+/* Launch a small kernel that waits - with the same bounded waits and `budget_cycles` (1...2e9)
+ * - on a barrier nothing arrives on, and wait for it.  The waits run out, the kernel records
+ * that and returns normally (no trap, the context stays usable).  results[0] (a wait by one
+ * thread) and results[1] (a wait by a whole warp) are 1 when the wait reported "gave up".
+ * The status word is left set: the next synchronising call returns -1. */
+int32_t tmx_selftest_bounded_wait(int64_t budget_cycles, int32_t *results);
+/* Set the device status word from the host, as a kernel whose wait gave up would. */
+int32_t tmx_debug_inject_status(int32_t code, int32_t where, int32_t block, int32_t extra);
+
 #ifdef __cplusplus
 }
 #endif

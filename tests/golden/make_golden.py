@@ -89,4 +89,7 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+    if len(sys.argv) < 2 and not os.environ.get("TRITON_METAL_REFERENCE"):
+        raise SystemExit("usage: make_golden.py <reference checkout>  (or set TRITON_METAL_REFERENCE)")
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ["TRITON_METAL_REFERENCE"])

@@ -772,16 +772,19 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         };
         // slot c & 1 was last read in block c - 2, two barriers ago
         put_stat(c, fetch_stat(0));
-        for (int t = 0; t < n_iter && ok; ++t, ++c) {
-          // all element-wise threads: statistics of block t are visible, block t-1 is no longer read
-          asm volatile("bar.sync 1, %0;" ::"n"(EW_THREADS) : "memory");
+        for (int t = 0; t < n_iter; ++t, ++c) {
+          // all element-wise threads: statistics of block t are visible, block t-1 is no longer read.
+          // The barrier also carries every thread's "still fine" flag: a thread whose wait gave up
+          // keeps walking (it skips the rest of its block) until this barrier, where all 512 leave
+          // in the same iteration.
+          if (!bar_sync_and(1, EW_THREADS, ok)) { ok = false; break; }
           float next_stat = 0.f;
           if (t + 1 < n_iter) next_stat = fetch_stat(t + 1);
           const float* lse_s = ss.lse[c & 1] + group * GCOLS;
           const float* delta_s = ss.delta[c & 1] + group * GCOLS;
           const int q0 = (first + t) * BLK + group * GCOLS;     // first query of this group's columns
           const bool diagonal = prm.causal && q0 < n0 + BLK;
-          if (!mbar_wait(smem_u32(&ss.st_full), c & 1, wc, 58)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&ss.st_full), c & 1, wc, 58)) { ok = false; continue; }
           tc_fence_after();
           uint32_t sv[32];
           tmem_ld_32x32(tmem + lane_addr + ST_COL + group * GCOLS, sv);
@@ -795,7 +798,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           else pt_part<T, false>(sv, qk_scale, lse_s, 0, keep);
           // dV(t-1) must have read the previous P^T before it is replaced: dP^T(t) was issued after
           // it, so its commit covers it (and is waited for here instead of before the dS^T pass)
-          if (!mbar_wait(smem_u32(&ss.dpt_full), c & 1, wc, 60)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&ss.dpt_full), c & 1, wc, 60)) { ok = false; continue; }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint32_t dst = p_row + (((p_chunk0 + i) ^ p_xor) << 4);
@@ -815,6 +818,8 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           if (t + 1 < n_iter) put_stat(c + 1, next_stat);
         }
         if (ok) ok = mbar_wait(smem_u32(&ss.done), item & 1, wc, 61);
+        // agreed on by all 512 threads, so that they enter (or skip) the next key tile together
+        ok = bar_sync_and(1, EW_THREADS, ok);
         tc_fence_after();
         if (ok) {
           // groups 0 and 1 store the halves of dV, groups 2 and 3 those of dK

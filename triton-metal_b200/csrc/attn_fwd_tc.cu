@@ -403,16 +403,19 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int my_blocks = key_blocks(m0, t);
         float m_used = -INFINITY, l = 0.f;
         for (int j = 0; j < my_blocks && ok; ++j, ++c) {
-          if (!mbar_wait(smem_u32(&ss.s_full[t]), c & 1, wc, kSoftS)) { ok = false; break; }
+          // A wait that gave up is not acted on alone: the flag goes through the tile's named
+          // barrier below, and all 256 threads leave in this same iteration.
+          const bool got = mbar_wait(smem_u32(&ss.s_full[t]), c & 1, wc, kSoftS);
           tc_fence_after();
           const int n0 = j * BLOCK_N + half * HALF_N;
           const bool boundary = (n0 + HALF_N > prm.n_ctx) || (prm.causal && n0 + HALF_N > m0 + t * BLOCK_M);
           const MaskInfo mi{n0, q_row, prm.n_ctx, prm.causal};
           // pass 1: max of the raw scores over this half row, then over the whole row
           // (qk_scale > 0, so the scaled max is max * qk_scale)
+          // (after a failed wait the scores read here are stale: harmless, the block is abandoned)
           float mx = boundary ? max_half<true>(s_tmem, mi) : max_half<false>(s_tmem, mi);
           ss.half_max[t][c & 1][half][row_in_tile] = mx;
-          asm volatile("bar.sync %0, 256;" ::"r"(pair_barrier) : "memory");
+          if (!bar_sync_and(pair_barrier, 256, got)) { ok = false; break; }
           mx = fmaxf(mx, ss.half_max[t][c & 1][half ^ 1][row_in_tile]) * qk_scale;
           // advance the working max only when it moved far (or on the first block); both
           // threads of a row see the same numbers and take the same decision
@@ -449,9 +452,11 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         // ---- whole-row sum, O / l and the row statistic of this query block
         ss.half_sum[t][half][row_in_tile] = l;
-        asm volatile("bar.sync %0, 256;" ::"r"(pair_barrier) : "memory");
-        l += ss.half_sum[t][half ^ 1][row_in_tile];
+        // the last P.V must have retired before O is read; the outcome of that wait, too, is
+        // agreed on by the whole tile at the barrier that publishes the half-row sums
         if (ok && my_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done[t]), item & 1, wc, kSoftFinal);
+        ok = bar_sync_and(pair_barrier, 256, ok);
+        l += ss.half_sum[t][half ^ 1][row_in_tile];
         tc_fence_after();
         if (ok && my_blocks > 0) {
           const float inv_l = 1.f / l;

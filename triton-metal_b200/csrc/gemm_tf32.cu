@@ -311,8 +311,11 @@ Workspace g_workspace;
 }  // namespace
 
 size_t gemm_tf32_scratch_bytes(int64_t M, int64_t N, int64_t K) {
-  const int64_t kp = (K + 3) / 4 * 4;
-  return (size_t)(8 * (M + N) * kp);
+  // in 128 bits: absurd extents must read as "too large", not wrap to something small
+  const __int128 kp = ((__int128)K + 3) / 4 * 4;
+  const __int128 need = 8 * ((__int128)M + (__int128)N) * kp;
+  if (M < 0 || N < 0 || K < 0 || need > (__int128)(SIZE_MAX / 2)) return SIZE_MAX / 2;
+  return (size_t)need;
 }
 
 // Runs split + GEMM with `scratch` (device pointer, at least gemm_tf32_scratch_bytes).

@@ -195,20 +195,10 @@ bool assign_positional(KernelDesc& d, std::string& err) {
   }
 }
 
-bool assign_roles(KernelDesc& d, std::string& err) {
-  // By name when every argument has a recognisable role name, else by position.
-  bool all_named = !d.args.empty() && !is_rowwise(d.id) && d.id != KernelId::SaeEncode;
-  std::set<int> seen;
-  for (auto& a : d.args) {
-    Role r = role_from_name(d.id, a.name);
-    if (r == Role::Unknown || seen.count((int)r)) { all_named = false; break; }
-    seen.insert((int)r);
-  }
-  if (all_named) {
-    for (auto& a : d.args) a.role = role_from_name(d.id, a.name);
-  } else if (!assign_positional(d, err)) {
-    return false;
-  }
+// Required roles, each present once, with the pointer / scalar kind and the statistic and scale
+// types the kernels expect.  Shared by the IR scan and by parse_descriptor, so a descriptor that
+// did not come from tm_emit_msl (truncated, stale, edited) is refused instead of trusted.
+bool check_roles(const KernelDesc& d, std::string& err) {
   // Required roles and their kinds.
   auto has = [&](Role r) {
     for (auto& a : d.args) if (a.role == r) return true;
@@ -233,7 +223,24 @@ bool assign_roles(KernelDesc& d, std::string& err) {
       need = {Role::Q, Role::Kt, Role::V, Role::DO, Role::DK, Role::DV, Role::L, Role::Delta,
               Role::SmScale, Role::StrideHead, Role::StrideSeq, Role::StrideLse, Role::NCtx};
       break;
+    case KernelId::VecCopy: need = {Role::In0, Role::Out, Role::Count}; break;
+    case KernelId::VecAdd: case KernelId::VecMul: need = {Role::In0, Role::In1, Role::Out, Role::Count}; break;
+    case KernelId::ScaleBias: need = {Role::In0, Role::Out, Role::Scale, Role::Bias, Role::Count}; break;
+    case KernelId::Softmax: need = {Role::In0, Role::Out, Role::StrideIn, Role::StrideOut, Role::NCols}; break;
+    case KernelId::SaeEncode:
+      need = {Role::A, Role::B, Role::BiasVec, Role::C, Role::M, Role::K, Role::N};
+      break;
     default: break;
+  }
+  {
+    std::set<int> once;
+    for (auto& a : d.args) {
+      if (a.role != Role::Unknown && !once.insert((int)a.role).second) {
+        err = std::string("lowering error at line 0, col 0: ") + kernel_entry_name(d.id) +
+              " has two arguments with the same role (" + std::to_string((int)a.role) + ")";
+        return false;
+      }
+    }
   }
   for (Role r : need) {
     if (!has(r)) {
@@ -267,6 +274,24 @@ bool assign_roles(KernelDesc& d, std::string& err) {
     }
   }
   return true;
+}
+
+
+bool assign_roles(KernelDesc& d, std::string& err) {
+  // By name when every argument has a recognisable role name, else by position.
+  bool all_named = !d.args.empty() && !is_rowwise(d.id) && d.id != KernelId::SaeEncode;
+  std::set<int> seen;
+  for (auto& a : d.args) {
+    Role r = role_from_name(d.id, a.name);
+    if (r == Role::Unknown || seen.count((int)r)) { all_named = false; break; }
+    seen.insert((int)r);
+  }
+  if (all_named) {
+    for (auto& a : d.args) a.role = role_from_name(d.id, a.name);
+  } else if (!assign_positional(d, err)) {
+    return false;
+  }
+  return check_roles(d, err);
 }
 
 // Split "a, b<c, d>, e {x, y}" on the commas at nesting depth 0.
@@ -596,6 +621,26 @@ bool parse_descriptor(const std::string& text, std::vector<KernelDesc>& out, std
       if (a.index != (int)cur.args.size()) return bad(t);
       cur.args.push_back(a);
     } else if (key == "end") {
+      // the same checks the IR scan applies: roles, their kinds, the element type of the entry
+      std::string why;
+      if (!check_roles(cur, why)) {
+        error = "metal error: MSL compilation failed: descriptor of " +
+                std::string(kernel_entry_name(cur.id)) + " is not usable: " + why;
+        return false;
+      }
+      if ((is_rowwise(cur.id) || cur.id == KernelId::SaeEncode) && cur.elt != Elt::F32) {
+        error = "metal error: MSL compilation failed: " + std::string(kernel_entry_name(cur.id)) +
+                " is precompiled for f32 only";
+        return false;
+      }
+      for (auto& a : cur.args) {
+        const bool data_ptr = a.is_pointer && a.role != Role::L && a.role != Role::Delta;
+        if (data_ptr && a.dtype != elt_name(cur.elt)) {
+          error = "metal error: MSL compilation failed: descriptor of " +
+                  std::string(kernel_entry_name(cur.id)) + " mixes element types";
+          return false;
+        }
+      }
       out.push_back(cur);
       open = false;
     } else {

@@ -53,12 +53,13 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Shared by every role of a CTA: the abort flag lives in shared memory.
+constexpr long long kWaitCycles = 2000000000ll;   // about one second
+
 struct WaitCtx {
   volatile int* abort_flag;   // shared memory
   DeviceStatus* status;       // host-visible
+  long long budget = kWaitCycles;   // cycles a wait may take before it gives up
 };
-
-constexpr long long kWaitCycles = 2000000000ll;   // about one second
 
 static __device__ __noinline__ void report_timeout(const WaitCtx& w, uint32_t site, uint32_t extra) {
   if (atomicCAS(&w.status->code, 0u, 1u) == 0u) {
@@ -79,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & 63u) == 0u) {
       if (*w.abort_flag) return false;
-      if (clock64() - start > kWaitCycles) {
+      if (clock64() - start > w.budget) {
         report_timeout(w, site, parity);
         return false;
       }
@@ -100,7 +101,7 @@ static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity
     if (mbar_try_wait(bar, parity)) return;
     if ((spins & 63u) == 0u) {
       if (*w.abort_flag) return;
-      if (clock64() - start > kWaitCycles) {
+      if (clock64() - start > w.budget) {
         report_timeout(w, site, parity);
         return;
       }
@@ -109,6 +110,26 @@ static __device__ __noinline__ void mbar_wait_slow(uint32_t bar, uint32_t parity
 }
 __device__ __forceinline__ void mbar_wait_issuer(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t site) {
   if (!mbar_try_wait(bar, parity)) mbar_wait_slow(bar, parity, w, site);
+}
+
+// Named barrier `id` over `threads` threads that also ANDs a predicate over them.  The groups
+// of warps that meet at a named barrier inside a loop pass their "still fine" flag through
+// it, so that after a wait gave up in one warp all of them leave in the same iteration - a
+// warp that left alone would leave the others waiting at the next barrier for an arrival
+// count that never completes.
+__device__ __forceinline__ bool bar_sync_and(int id, int threads, bool pred) {
+  uint32_t all;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.b32 p, %3, 0;\n"
+      "bar.red.and.pred q, %1, %2, p;\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}\n"
+      : "=r"(all)
+      : "r"(id), "r"(threads), "r"((uint32_t)pred)
+      : "memory");
+  return all != 0;
 }
 
 // ---- TMA (tile mode, one CTA, completion on an mbarrier) ----------------------
@@ -297,7 +318,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, co
   for (uint32_t spins = 1;; ++spins) {
     if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
     if ((spins & 63u) == 0u) {
-      const bool give_up = *w.abort_flag != 0 || clock64() - start > kWaitCycles;
+      const bool give_up = *w.abort_flag != 0 || clock64() - start > w.budget;
       if (__any_sync(0xffffffffu, give_up)) {
         if ((threadIdx.x & 31) == 0 && *w.abort_flag == 0) report_timeout(w, site, parity);
         __syncwarp();

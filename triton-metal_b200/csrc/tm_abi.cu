@@ -348,15 +348,36 @@ bool decode_args(KernelObj& k, const int32_t* kinds, const int64_t* values, int3
   return true;
 }
 
-bool check_extent(const BufferObj& b, int64_t last_elem, int elt_bytes, const char* what,
+// One dimension of the region a kernel addresses: `count` elements `stride` apart.
+struct Span {
+  int64_t count, stride;
+};
+
+// Refuses a launch whose largest element index - the sum of (count - 1) * stride over the
+// dimensions - lies beyond the buffer.  The index is formed in 128 bits from its factors, so
+// an absurd extent or stride cannot wrap into something that looks in bounds.
+bool check_extent(const BufferObj& b, std::initializer_list<Span> dims, int elt_bytes, const char* what,
                   std::string& err) {
-  // last_elem: the largest element index the kernel may touch (or -1 for none).
-  if (last_elem < 0) return true;
-  __int128 need = ((__int128)last_elem + 1) * elt_bytes;
+  __int128 last = 0;
+  for (const Span& d : dims) {
+    if (d.count <= 0) return true;      // an empty dimension: nothing is addressed
+    last += ((__int128)d.count - 1) * (__int128)d.stride;
+  }
+  const __int128 need = (last + 1) * elt_bytes;
   if (need > (__int128)b.length) {
-    err = invalid_argument(std::string("launch would address ") + std::to_string((long long)need) +
-                           " bytes of " + what + ", beyond its " + std::to_string(b.length) +
-                           "-byte buffer");
+    // the byte count is printed when it fits 64 bits, else as "more than 2^63"
+    const std::string shown = need < ((__int128)1 << 63) ? std::to_string((long long)need) : "more than 2^63";
+    err = invalid_argument(std::string("launch would address ") + shown + " bytes of " + what +
+                           ", beyond its " + std::to_string(b.length) + "-byte buffer");
+    return false;
+  }
+  return true;
+}
+
+// Extents the kernels index with 32-bit integers.
+bool check_int32(int64_t v, const char* name, std::string& err) {
+  if (v > 0x7fffffffll) {
+    err = invalid_argument(std::string(name) + " " + std::to_string(v) + " is above 2^31 - 1");
     return false;
   }
   return true;
@@ -425,6 +446,10 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
     RowProblem p{};
     p.id = desc.id;
     BufferObj *in0 = buf(Role::In0), *in1 = buf(Role::In1), *outb = buf(Role::Out);
+    if (!in0 || !outb || ((desc.id == KernelId::VecAdd || desc.id == KernelId::VecMul) && !in1)) {
+      err = invalid_argument(std::string(kernel_entry_name(desc.id)) + " was loaded from a descriptor without its buffer arguments");
+      return false;
+    }
     p.in0 = (const float*)in0->ptr;
     p.in1 = in1 ? (const float*)in1->ptr : nullptr;
     p.out = (float*)outb->ptr;
@@ -443,14 +468,15 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
       if (!nonneg(p.stride_in, "the input row stride") || !nonneg(p.stride_out, "the output row stride"))
         return false;
       if (p.cols <= 0) return true;
-      if (!check_extent(*in0, (p.rows - 1) * p.stride_in + p.cols - 1, 4, "the input", err)) return false;
-      if (!check_extent(*outb, (p.rows - 1) * p.stride_out + p.cols - 1, 4, "the output", err)) return false;
+      if (!check_int32(p.rows, "the row count", err)) return false;
+      if (!check_extent(*in0, {{p.rows, p.stride_in}, {p.cols, 1}}, 4, "the input", err)) return false;
+      if (!check_extent(*outb, {{p.rows, p.stride_out}, {p.cols, 1}}, 4, "the output", err)) return false;
     } else {
       p.limit = std::min<int64_t>(get_int(d, Role::Count, 0), gx * block);
       if (p.limit <= 0) return true;
-      if (!check_extent(*in0, p.limit - 1, 4, "the first input", err)) return false;
-      if (in1 && !check_extent(*in1, p.limit - 1, 4, "the second input", err)) return false;
-      if (!check_extent(*outb, p.limit - 1, 4, "the output", err)) return false;
+      if (!check_extent(*in0, {{p.limit, 1}}, 4, "the first input", err)) return false;
+      if (in1 && !check_extent(*in1, {{p.limit, 1}}, 4, "the second input", err)) return false;
+      if (!check_extent(*outb, {{p.limit, 1}}, 4, "the output", err)) return false;
     }
     prefetch_exposed(d);
     for (int r = 0; r < repeats; ++r) {
@@ -481,16 +507,19 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
     if (desc.block_n > 0) N = std::min<int64_t>(N, gy * (int64_t)desc.block_n);
     p.M = M; p.N = N; p.K = K;
     BufferObj *A = buf(Role::A), *B = buf(Role::B), *C = buf(Role::C);
+    if (!A || !B || !C || (sae && !buf(Role::BiasVec))) {
+      err = invalid_argument(std::string(kernel_entry_name(desc.id)) + " was loaded from a descriptor without its buffer arguments");
+      return false;
+    }
     p.a = A->ptr; p.b = B->ptr; p.c = C->ptr;
     if (M == 0 || N == 0) return true;
-    if (K > 0) {
-      if (!check_extent(*A, (M - 1) * p.sam + (K - 1) * p.sak, eb, "A", err)) return false;
-      if (!check_extent(*B, (K - 1) * p.sbk + (N - 1) * p.sbn, eb, "B", err)) return false;
-    }
-    if (!check_extent(*C, (M - 1) * p.scm + (N - 1) * p.scn, eb, "C", err)) return false;
+    if (!check_int32(M, "M", err) || !check_int32(N, "N", err) || !check_int32(K, "K", err)) return false;
+    if (!check_extent(*A, {{M, p.sam}, {K, p.sak}}, eb, "A", err)) return false;
+    if (!check_extent(*B, {{K, p.sbk}, {N, p.sbn}}, eb, "B", err)) return false;
+    if (!check_extent(*C, {{M, p.scm}, {N, p.scn}}, eb, "C", err)) return false;
     if (sae) {
       BufferObj* bias = buf(Role::BiasVec);
-      if (!check_extent(*bias, N - 1, 4, "the bias", err)) return false;
+      if (!check_extent(*bias, {{N, 1}}, 4, "the bias", err)) return false;
       p.bias = (const float*)bias->ptr;
       p.relu = 1;
     }
@@ -533,19 +562,18 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
   p.rows = p.n_ctx;
   if (block_rows > 0) p.rows = std::min<int64_t>(p.n_ctx, gx * (int64_t)block_rows);
   if (p.n_ctx == 0 || p.rows == 0) return true;
-  const int64_t last_data = (p.bh - 1) * p.stride_head + (p.n_ctx - 1) * p.stride_seq + p.head_dim - 1;
-  const int64_t last_stat = (p.bh - 1) * p.stride_lse + p.n_ctx - 1;
+  if (!check_int32(p.n_ctx, "n_ctx", err) || !check_int32(p.bh, "grid_y (batch*heads)", err)) return false;
   auto data = [&](Role r, const char* what, const void** slot) {
     BufferObj* b = buf(r);
     if (!b) return true;
-    if (!check_extent(*b, last_data, eb, what, err)) return false;
+    if (!check_extent(*b, {{p.bh, p.stride_head}, {p.n_ctx, p.stride_seq}, {p.head_dim, 1}}, eb, what, err)) return false;
     *slot = b->ptr;
     return true;
   };
   auto stat = [&](Role r, const char* what, const void** slot) {
     BufferObj* b = buf(r);
     if (!b) return true;
-    if (!check_extent(*b, last_stat, 4, what, err)) return false;
+    if (!check_extent(*b, {{p.bh, p.stride_lse}, {p.n_ctx, 1}}, 4, what, err)) return false;
     *slot = b->ptr;
     return true;
   };
@@ -1062,9 +1090,10 @@ int32_t tmx_matmul_f32_static(int64_t a, int64_t b, int64_t c, int64_t M, int64_
   p.M = M; p.N = N; p.K = K;
   p.sam = stride_am; p.sak = stride_ak; p.sbk = stride_bk; p.sbn = stride_bn;
   p.scm = stride_cm; p.scn = stride_cn;
-  if (!check_extent(*A, (M - 1) * p.sam + (K - 1) * p.sak, 4, "A", err) ||
-      !check_extent(*B, (K - 1) * p.sbk + (N - 1) * p.sbn, 4, "B", err) ||
-      !check_extent(*C, (M - 1) * p.scm + (N - 1) * p.scn, 4, "C", err)) {
+  if (!check_int32(M, "M", err) || !check_int32(N, "N", err) || !check_int32(K, "K", err) ||
+      !check_extent(*A, {{M, p.sam}, {K, p.sak}}, 4, "A", err) ||
+      !check_extent(*B, {{K, p.sbk}, {N, p.sbn}}, 4, "B", err) ||
+      !check_extent(*C, {{M, p.scm}, {N, p.scn}}, 4, "C", err)) {
     store_error(err);
     return -1;
   }
@@ -1093,5 +1122,40 @@ int32_t tmx_matmul_f32_static(int64_t a, int64_t b, int64_t c, int64_t M, int64_
 }
 
 int64_t tmx_matmul_f32_static_capacity(void) { return (int64_t)gemm_tf32_static_capacity(); }
+
+// ---- failure-path aids ------------------------------------------------------
+
+// Runs the bounded-wait self-test kernel (csrc/selftest.cu) with the given cycle budget and
+// waits for it.  The kernel's waits run out and it records that in the device status word;
+// the word is left in place, so the next tm_launch / tmx_synchronize / copy reports it.
+int32_t tmx_selftest_bounded_wait(int64_t budget_cycles, int32_t* results) {
+  std::string err;
+  if (!results || budget_cycles <= 0 || budget_cycles > 2000000000ll) {
+    store_error(invalid_argument("tmx_selftest_bounded_wait needs a result pointer and a budget of 1...2e9 cycles"));
+    return -1;
+  }
+  if (!bind_device(err)) { store_error(err); return -1; }
+  {
+    const std::string& why = unusable_reason();
+    if (!why.empty()) { store_error(cuda_error(why)); return -1; }
+  }
+  int got[2] = {0, 0};
+  std::string e = launch_bounded_wait_selftest(launch_ctx(), (long long)budget_cycles, got);
+  if (!e.empty()) { store_error(cuda_error("self-test launch failed: " + e)); return -1; }
+  results[0] = got[0];
+  results[1] = got[1];
+  return 0;
+}
+
+// Writes a device status record from the host, as if a kernel's bounded wait had given up.
+int32_t tmx_debug_inject_status(int32_t code, int32_t where, int32_t block, int32_t extra) {
+  std::string err;
+  if (!bind_device(err)) { store_error(err); return -1; }
+  g_dev.status->where = (unsigned)where;
+  g_dev.status->block = (unsigned)block;
+  g_dev.status->extra = (unsigned)extra;
+  g_dev.status->code = (unsigned)code;
+  return 0;
+}
 
 }  // extern "C"

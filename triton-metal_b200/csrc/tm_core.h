@@ -166,5 +166,8 @@ std::string launch_attn_bwd_dkdv_tc(const AttnProblem& p, const LaunchCtx& ctx);
 std::string launch_rowwise(const RowProblem& p, const LaunchCtx& ctx);
 
 std::string launch_probe(const LaunchCtx& ctx, int* out_host);
+// A kernel that waits, with the library's bounded waits and `budget_cycles`, on a barrier nothing
+// arrives on; results_host[0..1]: 1 = the wait gave up (expected), 2 = it claimed success.
+std::string launch_bounded_wait_selftest(const LaunchCtx& ctx, long long budget_cycles, int* results_host);
 
 }  // namespace tmc

@@ -32,6 +32,8 @@ EXPORTS = {
     "tmx_stream_handle": (_PTR, ()),
     "tmx_matmul_f32_static": (_I32, (_I64,) * 12),
     "tmx_matmul_f32_static_capacity": (_I64, ()),
+    "tmx_selftest_bounded_wait": (_I32, (_I64, _I32P)),
+    "tmx_debug_inject_status": (_I32, (_I32, _I32, _I32, _I32)),
 }
 
 for _symbol, (_ret, _args) in EXPORTS.items():
@@ -143,3 +145,15 @@ def device_pointer(handle: int) -> int:
 def stream_handle() -> int:
     """The library's cudaStream_t as an integer (for torch.cuda.ExternalStream)."""
     return _lib.tmx_stream_handle() or 0
+
+
+def selftest_bounded_wait(budget_cycles: int):
+    """Run the kernel whose waits are meant to run out; returns what its two waits reported
+    (1 = gave up).  The device status word stays set for the next synchronising call."""
+    results = (ctypes.c_int32 * 2)()
+    _ok(_lib.tmx_selftest_bounded_wait(budget_cycles, results))
+    return results[0], results[1]
+
+
+def inject_status(code: int, where: int = 0, block: int = 0, extra: int = 0) -> None:
+    _ok(_lib.tmx_debug_inject_status(code, where, block, extra))
