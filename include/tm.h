@@ -183,6 +183,13 @@ void *tmx_buffer_device_pointer(int64_t buffer);
  *  - The first call on a device looks up the array's device address (one
  *    cudaGetSymbolAddress with that device current).  Make that first call during start-up,
  *    before any stream capture is begun.
+ *  - "Allocates nothing" is a statement about calls, not about loading: the CUDA runtime loads
+ *    a module lazily, and the module that holds the array and these kernels is loaded by that
+ *    first address lookup (or first launch) - that is when the driver sets aside the 8 MiB and
+ *    the kernel images on the GPU.  A host that is about to hand all remaining device memory to
+ *    its own pool must therefore make the first call, or tmx_matmul_f32_static_prepare, before
+ *    it does so; a first call made afterwards can fail for lack of memory.  From the second
+ *    call on, free device memory is the same before and after a call.
  *  - All calls share the one array and it keeps whatever the last call left in it.  Nothing
  *    needs clearing: each call first rewrites every word its GEMM reads.  Calls are ordered on
  *    the library's single stream; work that overlaps on the GPU with one of these calls and
@@ -192,6 +199,11 @@ int32_t tmx_matmul_f32_static(int64_t a, int64_t b, int64_t c, int64_t M, int64_
                               int64_t stride_bn, int64_t stride_cm, int64_t stride_cn);
 /* Size in bytes of the fixed scratch array behind tmx_matmul_f32_static. */
 int64_t tmx_matmul_f32_static_capacity(void);
+/* The once-per-device set-up of tmx_matmul_f32_static without a matmul: resolves the array's
+ * address and thereby loads the module that holds it.  0 / -1.  No counterpart in the reference. */
+int32_t tmx_matmul_f32_static_prepare(void);
+/* Free and total device memory in bytes, as the driver reports them.  0 / -1. */
+int32_t tmx_device_memory(int64_t *free_bytes, int64_t *total_bytes);
 
 /* ---- failure-path aids (no counterpart in the reference) -------------------
  *

@@ -290,6 +290,43 @@ def test_reference_shim_binds_unchanged():
     assert out.stdout.strip() == "0"
 
 
+def test_descriptors_that_did_not_come_from_emit_are_refused(core):
+    """tm_compile_msl / tm_load_metallib re-run the scanner's checks on the descriptor they are
+    given: a truncated, stale or edited one is an error, not a kernel that later dereferences
+    a buffer it never received."""
+    good = core.emit_msl(kernels.matmul_ir(64, 64, 32, "f32"))
+    lines = good.splitlines()
+    arg_lines = [i for i, l in enumerate(lines) if l.strip().startswith("arg ")]
+    # the C pointer is gone (and the later arguments renumbered): a required role is missing
+    cut = [l for i, l in enumerate(lines) if i != arg_lines[2]]
+    renumbered, n = [], 0
+    for l in cut:
+        if l.strip().startswith("arg "):
+            parts = l.split()
+            parts[1] = str(n)
+            n += 1
+            l = "  " + " ".join(parts)
+        renumbered.append(l)
+    with pytest.raises(RuntimeError, match="missing a required argument"):
+        core.compile_msl("\n".join(renumbered) + "\n")
+    # a pointer turned into a scalar
+    edited = good.replace(lines[arg_lines[0]], lines[arg_lines[0]].replace("pointer", "scalar"))
+    with pytest.raises(RuntimeError, match="should be a pointer"):
+        core.compile_msl(edited)
+    # truncated before `end`
+    with pytest.raises(RuntimeError, match="no complete kernel"):
+        core.compile_msl("\n".join(lines[:arg_lines[1]]) + "\n")
+    # the one-dimensional kernels and the fused encoder exist for f32 only
+    sae = core.emit_msl(kernels.sae_encode_ir())
+    with pytest.raises(RuntimeError, match="f32 only|mixes element types"):
+        core.compile_msl(sae.replace("element f32", "element bf16"))
+    with pytest.raises(RuntimeError, match="not a tmcuda kernel descriptor"):
+        core.load_metallib(cut[2].encode())
+    with pytest.raises(RuntimeError, match="could not load metallib"):
+        core.load_metallib(("\n".join(renumbered) + "\n").encode())
+    assert core.last_error() == "no error"
+
+
 def test_there_is_no_cpu_fallback(core):
     """Without a GPU a launch fails loudly instead of computing on the host."""
     if core.is_active():

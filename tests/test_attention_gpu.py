@@ -133,6 +133,74 @@ def test_gradient_descent_on_projection_weights():
     assert np.allclose(losses, ref_losses, rtol=1e-5)
 
 
+def test_projection_training_step_runs_on_the_library():
+    """The same eight SGD steps with every product on the GPU: the Q/K/V/O projections and
+    their transposed gradients through matmul_kernel (transposes as strides), the head split
+    through the attention kernels' strides, the updates through scale_bias_kernel and
+    add_kernel.  Losses and weights must follow the numpy chain rule step for step."""
+    from triton_metal.attention_layer import ProjectionAttention
+    rng = np.random.default_rng(0)
+    seq, d_model, heads = 96, 128, 2
+    x = rng.standard_normal((seq, d_model), dtype=np.float32)
+    target = rng.standard_normal((seq, d_model), dtype=np.float32)
+    w_ref = [rng.standard_normal((d_model, d_model), dtype=np.float32) * np.float32(0.02)
+             for _ in range(4)]
+    scale = ref.default_scale(d_model // heads)
+    ref_fwd, ref_bwd = ref.oracle_attention(scale)
+    layer = ProjectionAttention(x, target, w_ref, heads)
+    try:
+        losses, ref_losses = [], []
+        for step in range(8):
+            before = cuda.launch_count()
+            losses.append(layer.forward())
+            grads = layer.backward()
+            layer.sgd(1e-3)
+            # 4 + 5 matmuls, 4 attention kernels, 2 + 8 element-wise launches: nothing ran elsewhere
+            assert cuda.launch_count() - before == 23
+            ref_loss, ref_grads = ref.projection_step(x, w_ref, target, heads, scale, ref_fwd, ref_bwd)
+            ref_losses.append(ref_loss)
+            for name, got, want in zip(("dWq", "dWk", "dWv", "dWo"), grads, ref_grads):
+                assert ref.relative_error(got, want) <= 1e-5, (step, name)
+            w_ref = [w - np.float32(1e-3) * g for w, g in zip(w_ref, ref_grads)]
+            for got, want in zip(layer.weights(), w_ref):
+                assert ref.relative_error(got, want) <= 1e-5, step
+    finally:
+        layer.close()
+    assert all(b < a for a, b in zip(losses, losses[1:])), losses
+    assert np.allclose(losses, ref_losses, rtol=1e-5)
+
+
+def test_gpu_gradients_match_finite_differences():
+    """python/examples/attention_training.py:286-310 and
+    Tests/TritonMetalCoreTests/AttentionBackwardTests.swift:397-482: the kernels' dQ, dK, dV of
+    0.5*||O - T||^2 on h2 s96 d64 against central differences of a float64 forward, which
+    know no backward formulas.  Four entries per tensor, bound 1e-4."""
+    rng = np.random.default_rng(0)
+    q, k, v, target = [rng.standard_normal((2, 96, 64), dtype=np.float32) * np.float32(0.5)
+                       for _ in range(4)]
+    scale = ref.default_scale(64)
+    with tmtest.AttentionRun(q, k, v, np.zeros_like(q), "f32", False, (16, 32)) as run:
+        o, _ = run.forward()
+        tmtest.put(run.bufs["do"], (o - target).astype(np.float32))
+        grads = run.backward()
+
+    def loss(qq, kk, vv):
+        out, _ = ref.attention_forward(qq, kk, vv, scale, dtype=np.float64)
+        return 0.5 * float(np.sum((out - target.astype(np.float64)) ** 2))
+
+    h, worst = 1e-5, 0.0
+    for which, grad in enumerate(grads):
+        for _ in range(4):
+            idx = tuple(rng.integers(0, s) for s in q.shape)
+            plus = [t.astype(np.float64) for t in (q, k, v)]
+            minus = [t.copy() for t in plus]
+            plus[which][idx] += h
+            minus[which][idx] -= h
+            numeric = (loss(*plus) - loss(*minus)) / (2 * h)
+            worst = max(worst, abs(numeric - float(grad[idx])) / max(1.0, abs(numeric)))
+    assert worst < 1e-4, worst
+
+
 def test_direct_descent_of_the_reference_example():
     """attention_training.py:314-329 - 8 steps on q, k, v at rate 0.5; the loss
     after the last step is below the first."""

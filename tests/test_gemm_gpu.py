@@ -168,6 +168,18 @@ def test_launch_validation_on_the_device(core):
         kinds_bad[0] = 1
         with pytest.raises(RuntimeError, match="is a pointer"):
             core.launch(mm.handle, grid, 128, kinds_bad, values)
+        # extents and strides of 2^32 carried as i64: their product does not fit 64 bits and
+        # must be refused, not wrapped into something that looks in bounds
+        wide_kinds, wide = list(kinds), list(values)
+        for position in (3, 6):                          # M and stride_am
+            wide_kinds[position] = core.ARG_I64
+            wide[position] = 1 << 32
+        with pytest.raises(RuntimeError, match="above 2\\^31|beyond its"):
+            core.launch(mm.handle, (1 << 26, 1, 1), 128, wide_kinds, wide)
+        wide[3] = 64
+        wide[6] = 1 << 62                                # (M-1) * stride_am = 63 * 2^62
+        with pytest.raises(RuntimeError, match="beyond its"):
+            core.launch(mm.handle, grid, 128, wide_kinds, wide)
     finally:
         mm.release()
         a.free()

@@ -46,6 +46,36 @@ def test_static_scratch_matmul_matches_tm_launch_twice_in_a_row():
         assert ref.relative_error(got_static, want) <= 1e-5
 
 
+def test_static_scratch_matmul_takes_strided_operands_and_allocates_nothing():
+    """A transposed A, a padded B and a padded C (stride_am = 1, row strides wider than the rows)
+    through the fixed-array entry point; and, once the first call has loaded the module, a
+    call leaves the amount of free device memory exactly as it found it."""
+    tmtest.require_gpu()
+    M, N, K = 256, 192, 320
+    a, b = inputs.gemm_normal(M, N, K, seed=4)
+    a_t = np.ascontiguousarray(a.T)
+    b_pad = np.zeros((K, N + 5), dtype=np.float32)
+    b_pad[:, :N] = b
+    ab, bb = tmtest.upload(a_t, "f32"), tmtest.upload(b_pad, "f32")
+    cb = tmtest.empty((M, N + 3), "f32")
+    try:
+        cuda.matmul_f32_static_prepare()
+        strides = (1, M, N + 5, 1, N + 3, 1)
+        tmtest.put(cb, np.full((M, N + 3), -9.0, dtype=np.float32))
+        cuda.matmul_f32_static(ab.tm_handle, bb.tm_handle, cb.tm_handle, M, N, K, strides)
+        free_before, _ = cuda.device_memory()
+        tmtest.put(cb, np.full((M, N + 3), -9.0, dtype=np.float32))
+        cuda.matmul_f32_static(ab.tm_handle, bb.tm_handle, cb.tm_handle, M, N, K, strides)
+        free_after, _ = cuda.device_memory()
+        c = tmtest.fetch(cb)
+        assert free_after == free_before
+        assert ref.relative_error(c[:, :N], ref.matmul(a, b)) <= 1e-5
+        assert np.all(c[:, N:] == -9.0)
+    finally:
+        for buf in (ab, bb, cb):
+            buf.free()
+
+
 def test_static_scratch_matmul_refuses_what_does_not_fit(core):
     tmtest.require_gpu()
     capacity = cuda.matmul_f32_static_capacity()
@@ -60,5 +90,12 @@ def test_static_scratch_matmul_refuses_what_does_not_fit(core):
             cuda.matmul_f32_static(big.tm_handle, big.tm_handle, big.tm_handle, 64, 64, 64)
         with pytest.raises(RuntimeError, match="beyond its"):
             cuda.matmul_f32_static(big.tm_handle, big.tm_handle, big.tm_handle, 4096, 128, 2048)
+        # extents and strides whose product does not fit 64 bits are refused, not wrapped
+        with pytest.raises(RuntimeError, match="beyond its|above 2\\^31"):
+            cuda.matmul_f32_static(big.tm_handle, big.tm_handle, big.tm_handle, 1 << 31, 128, 64,
+                                   (1 << 33, 1, 128, 1, 128, 1))
+        with pytest.raises(RuntimeError, match="beyond its"):
+            cuda.matmul_f32_static(big.tm_handle, big.tm_handle, big.tm_handle, 1 << 20, 128, 64,
+                                   (1 << 44, 1, 128, 1, 128, 1))
     finally:
         big.free()

@@ -407,29 +407,42 @@ size_t gemm_tf32_static_capacity() { return kStaticScratchBytes; }
 // device current); nothing here allocates or frees device memory.  Every call uses the same
 // array: the split kernels rewrite every word the GEMM will read (including the zero padding
 // of K up to a multiple of 4), so nothing left by an earlier call is ever consumed.
-std::string run_gemm_tf32_static(const GemmProblem& p, const LaunchCtx& ctx, int device) {
+// Device address of the fixed array on `device` (which must be current): looked up once per
+// device with cudaGetSymbolAddress and cached.  With CUDA's lazy module loading this lookup is
+// also what loads this translation unit's module, i.e. the moment the driver reserves the
+// array's 8 MiB and the kernel images on that GPU.
+static std::string static_scratch_address(int device, void** out) {
   static std::mutex lock;
   static void* address[kMaxDevices] = {};
   if (device < 0 || device >= kMaxDevices) return "device ordinal outside 0..63";
+  std::lock_guard<std::mutex> guard(lock);
+  if (!address[device]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr) {
+      cudaGetLastError();
+      return std::string("could not resolve the fixed scratch array on this device: ") + cudaGetErrorString(e);
+    }
+    address[device] = ptr;
+  }
+  *out = address[device];
+  return std::string();
+}
+
+std::string prepare_gemm_tf32_static(int device) {
+  void* scratch = nullptr;
+  return static_scratch_address(device, &scratch);
+}
+
+std::string run_gemm_tf32_static(const GemmProblem& p, const LaunchCtx& ctx, int device) {
   const size_t need = gemm_tf32_scratch_bytes(p.M, p.N, p.K);
   if (need > kStaticScratchBytes) {
     return "the operand split needs " + std::to_string(need) + " bytes of scratch (8*(M+N)*roundup(K,4)), more than the " +
            std::to_string(kStaticScratchBytes) + "-byte fixed array; use tm_launch for this size";
   }
   void* scratch = nullptr;
-  {
-    std::lock_guard<std::mutex> guard(lock);
-    if (!address[device]) {
-      void* ptr = nullptr;
-      cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
-      if (e != cudaSuccess || !ptr) {
-        cudaGetLastError();
-        return std::string("could not resolve the fixed scratch array on this device: ") + cudaGetErrorString(e);
-      }
-      address[device] = ptr;
-    }
-    scratch = address[device];
-  }
+  std::string e = static_scratch_address(device, &scratch);
+  if (!e.empty()) return e;
   return run_gemm_tf32(p, ctx, scratch);
 }
 

@@ -1123,6 +1123,38 @@ int32_t tmx_matmul_f32_static(int64_t a, int64_t b, int64_t c, int64_t M, int64_
 
 int64_t tmx_matmul_f32_static_capacity(void) { return (int64_t)gemm_tf32_static_capacity(); }
 
+// The once-per-device set-up of tmx_matmul_f32_static on its own: resolves the fixed array's
+// device address, which under lazy module loading is also when the driver reserves the array
+// and the kernel images on the GPU.  A host calls this before it hands the rest of device
+// memory to its own pool; afterwards tmx_matmul_f32_static changes the amount of free device
+// memory by nothing.
+int32_t tmx_matmul_f32_static_prepare(void) {
+  std::string err;
+  if (!bind_device(err)) { store_error(err); return -1; }
+  std::string e = prepare_gemm_tf32_static(g_dev.ordinal);
+  if (!e.empty()) { store_error(cuda_error(e)); return -1; }
+  return 0;
+}
+
+// Free and total bytes of device memory as the driver reports them (cudaMemGetInfo).
+int32_t tmx_device_memory(int64_t* free_bytes, int64_t* total_bytes) {
+  std::string err;
+  if (!free_bytes || !total_bytes) {
+    store_error(invalid_argument("tmx_device_memory needs two result pointers"));
+    return -1;
+  }
+  if (!bind_device(err)) { store_error(err); return -1; }
+  size_t f = 0, t = 0;
+  cudaError_t e = cudaMemGetInfo(&f, &t);
+  if (e != cudaSuccess) {
+    store_error(cuda_error(std::string("cudaMemGetInfo: ") + cudaGetErrorString(e)));
+    return -1;
+  }
+  *free_bytes = (int64_t)f;
+  *total_bytes = (int64_t)t;
+  return 0;
+}
+
 // ---- failure-path aids ------------------------------------------------------
 
 // Runs the bounded-wait self-test kernel (csrc/selftest.cu) with the given cycle budget and

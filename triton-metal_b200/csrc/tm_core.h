@@ -157,6 +157,7 @@ size_t gemm_tf32_scratch_bytes(int64_t M, int64_t N, int64_t K);
 std::string run_gemm_tf32(const GemmProblem& p, const LaunchCtx& ctx, void* scratch);  // caller's scratch
 std::string run_gemm_tf32_static(const GemmProblem& p, const LaunchCtx& ctx, int device);  // fixed device array
 size_t gemm_tf32_static_capacity();
+std::string prepare_gemm_tf32_static(int device);   // resolves the array's address (loads the module)
 bool attn_fwd_tc_eligible(const AttnProblem& p, std::string* why);
 std::string launch_attn_fwd_tc(const AttnProblem& p, const LaunchCtx& ctx);
 bool attn_bwd_tc_eligible(const AttnProblem& p, std::string* why);

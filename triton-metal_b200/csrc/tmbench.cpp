@@ -261,6 +261,11 @@ std::string fmt(const char* f, double v) {
   return buf;
 }
 
+// The last column of a result row: what the verification found, or that it was skipped.
+std::string verdict(bool verified, double err) {
+  return verified ? "  verified (max error " + fmt("%.2e", err) + ")" : "  not verified";
+}
+
 struct Options {
   std::vector<int> sizes{512, 1024, 2048};
   std::vector<std::string> configs{"128,256,64,4"};
@@ -324,6 +329,7 @@ void run_gemm(const Options& opt) {
       if (opt.verbose) std::printf("  %d  %s  %.1f GFLOP/s\n", n, name, 2.0 * n * n * n / ms / 1e6);
       if (ms < best_ms) { best_ms = ms; best_name = name; }
     }
+    double gemm_err = 0;
     if (opt.verify) {
       // CPU reference in double on a band of rows (GEMMBenchmark.swift:325-375 checks the winner)
       std::vector<float> c = el.decode(cb.read((size_t)n * n * el.size()));
@@ -342,11 +348,13 @@ void run_gemm(const Options& opt) {
       const double err = max_rel_error(want, got);
       const double tol = el.name == "f32" ? 1e-4 : 2e-2;   // DotTests.swift tolerances, widened for K = n
       if (!(err <= tol)) die("GEMM " + std::to_string(n) + " failed verification: error " + std::to_string(err));
+      gemm_err = err;
     }
     const double gflops = 2.0 * n * n * n / best_ms / 1e6;
-    std::printf("%s%s%s%s\n", pad(std::to_string(n), 8).c_str(), pad(best_name, 25).c_str(),
+    std::printf("%s%s%s%s%s\n", pad(std::to_string(n), 8).c_str(), pad(best_name, 25).c_str(),
                 pad(fmt("%.1f", gflops), 18).c_str(),
-                opt.peak_tflops > 0 ? fmt("%.0f%%", gflops / 10.0 / opt.peak_tflops).c_str() : "");
+                opt.peak_tflops > 0 ? pad(fmt("%.0f%%", gflops / 10.0 / opt.peak_tflops), 6).c_str() : "",
+                verdict(opt.verify, gemm_err).c_str());
   }
 }
 
@@ -399,11 +407,14 @@ HeadRef reference_head(const float* q, const float* k, const float* v, const flo
   return r;
 }
 
-void check(const char* what, const std::vector<double>& want, const std::vector<float>& got, size_t offset,
-           double tol) {
+// Returns the error; a result outside `tol` ends the program (exit status 1), as the reference's
+// benchmarks refuse to print a number for a kernel that computed something else.
+double check(const char* what, const std::vector<double>& want, const std::vector<float>& got, size_t offset,
+             double tol) {
   std::vector<float> slice(got.begin() + offset, got.begin() + offset + want.size());
   const double err = max_rel_error(want, slice);
   if (!(err <= tol)) die(std::string(what) + " failed verification: error " + std::to_string(err));
+  return err;
 }
 
 void run_attention(const Options& opt, bool backward) {
@@ -439,11 +450,13 @@ void run_attention(const Options& opt, bool backward) {
       ref = reference_head(q.data(), k.data(), v.data(), d_o.data(), S, D, scale, opt.causal, backward);
     if (!backward) {
       const double ms = measure({{&fwd, &lf}});
-      if (opt.verify) check("attn_fwd O", ref.o, el.decode(ob.read(n * el.size())), 0, tol);
+      double err = 0;
+      if (opt.verify) err = check("attn_fwd O", ref.o, el.decode(ob.read(n * el.size())), 0, tol);
       const double gflops = 4.0 * credit / ms / 1e6;
-      std::printf("%s%s%s%s\n", pad(name, 26).c_str(), pad("attn_fwd", 16).c_str(),
+      std::printf("%s%s%s%s%s\n", pad(name, 26).c_str(), pad("attn_fwd", 16).c_str(),
                   pad(fmt("%.1f", gflops), 18).c_str(),
-                  opt.peak_tflops > 0 ? fmt("%.0f%%", gflops / 10.0 / opt.peak_tflops).c_str() : "");
+                  opt.peak_tflops > 0 ? pad(fmt("%.0f%%", gflops / 10.0 / opt.peak_tflops), 6).c_str() : "",
+                  verdict(opt.verify, err).c_str());
       continue;
     }
     Kernel pre(attn_ir("attn_bwd_preprocess", kPreArgs, bm, D, 0, el.name), "attn_bwd_preprocess");
@@ -464,15 +477,17 @@ void run_attention(const Options& opt, bool backward) {
     for (int x : {S * D, D, S, S}) lk.i32(x);
     run_once(pre, lp); run_once(dq, lq); run_once(dkdv, lk);
     const double ms = measure({{&pre, &lp}, {&dq, &lq}, {&dkdv, &lk}});
+    double err = 0;
     if (opt.verify) {
-      check("attn_bwd dQ", ref.dq, el.decode(dqb.read(n * el.size())), 0, tol * 5);
-      check("attn_bwd dK", ref.dk, el.decode(dkb.read(n * el.size())), 0, tol * 5);
-      check("attn_bwd dV", ref.dv, el.decode(dvb.read(n * el.size())), 0, tol * 5);
+      err = check("attn_bwd dQ", ref.dq, el.decode(dqb.read(n * el.size())), 0, tol * 5);
+      err = std::max(err, check("attn_bwd dK", ref.dk, el.decode(dkb.read(n * el.size())), 0, tol * 5));
+      err = std::max(err, check("attn_bwd dV", ref.dv, el.decode(dvb.read(n * el.size())), 0, tol * 5));
     }
     const double gflops = 10.0 * credit / ms / 1e6;
-    std::printf("%s%s%s%s\n", pad(name, 26).c_str(), pad("attn_bwd (3)", 16).c_str(),
+    std::printf("%s%s%s%s%s\n", pad(name, 26).c_str(), pad("attn_bwd (3)", 16).c_str(),
                 pad(fmt("%.1f", gflops), 18).c_str(),
-                opt.peak_tflops > 0 ? fmt("%.0f%%", gflops / 10.0 / opt.peak_tflops).c_str() : "");
+                opt.peak_tflops > 0 ? pad(fmt("%.0f%%", gflops / 10.0 / opt.peak_tflops), 6).c_str() : "",
+                verdict(opt.verify, err).c_str());
   }
 }
 

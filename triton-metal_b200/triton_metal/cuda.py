@@ -32,6 +32,8 @@ EXPORTS = {
     "tmx_stream_handle": (_PTR, ()),
     "tmx_matmul_f32_static": (_I32, (_I64,) * 12),
     "tmx_matmul_f32_static_capacity": (_I64, ()),
+    "tmx_matmul_f32_static_prepare": (_I32, ()),
+    "tmx_device_memory": (_I32, (_I64P, _I64P)),
     "tmx_selftest_bounded_wait": (_I32, (_I64, _I32P)),
     "tmx_debug_inject_status": (_I32, (_I32, _I32, _I32, _I32)),
 }
@@ -157,3 +159,14 @@ def selftest_bounded_wait(budget_cycles: int):
 
 def inject_status(code: int, where: int = 0, block: int = 0, extra: int = 0) -> None:
     _ok(_lib.tmx_debug_inject_status(code, where, block, extra))
+
+
+def matmul_f32_static_prepare() -> None:
+    _ok(_lib.tmx_matmul_f32_static_prepare())
+
+
+def device_memory():
+    """(free, total) bytes of device memory."""
+    free, total = ctypes.c_int64(0), ctypes.c_int64(0)
+    _ok(_lib.tmx_device_memory(ctypes.byref(free), ctypes.byref(total)))
+    return free.value, total.value

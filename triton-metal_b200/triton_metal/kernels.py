@@ -12,20 +12,30 @@ python/examples/matmul.py with all six strides present.
 
 import math
 
-from . import _core, cuda
+from . import _core, cuda, launcher
 
 ELEMENT = {"float32": "f32", "float16": "f16", "bfloat16": "bf16",
            "f32": "f32", "f16": "f16", "bf16": "bf16"}
 
 
-def matmul_ir(block_m=128, block_n=128, block_k=64, element="f32"):
+def matmul_ir(block_m=128, block_n=128, block_k=64, element="f32", fold_unit_strides=False,
+              positional_names=False):
+    """`fold_unit_strides`: the nine-argument form real Triton emits for a row-major call - it
+    specialises integer arguments equal to 1 into constants, so stride_ak, stride_bn and
+    stride_cn are not in the signature (Tests/TritonMetalCoreTests/DotFixtures.swift:108-110).
+    `positional_names`: %arg0, %arg1, ... as in the Swift generators' output."""
     e = ELEMENT[element]
+    names = ["a_ptr", "b_ptr", "c_ptr", "M", "N", "K", "stride_am", "stride_ak", "stride_bk",
+             "stride_bn", "stride_cm", "stride_cn"]
+    if fold_unit_strides:
+        names = [n for n in names if n not in ("stride_ak", "stride_bn", "stride_cn")]
+    parts = []
+    for i, n in enumerate(names):
+        ty = f"!tt.ptr<{e}>" if n.endswith("_ptr") else "i32"
+        parts.append(f"%{'arg' + str(i) if positional_names else n}: {ty}")
     return f"""module {{
   tt.func public @matmul_kernel(
-      %a_ptr: !tt.ptr<{e}>, %b_ptr: !tt.ptr<{e}>, %c_ptr: !tt.ptr<{e}>,
-      %M: i32, %N: i32, %K: i32,
-      %stride_am: i32, %stride_ak: i32, %stride_bk: i32, %stride_bn: i32,
-      %stride_cm: i32, %stride_cn: i32) {{
+      {", ".join(parts)}) {{
     %acc = tt.dot %a, %b, %zero, inputPrecision = tf32 : tensor<{block_m}x{block_k}x{e}> * tensor<{block_k}x{block_n}x{e}> -> tensor<{block_m}x{block_n}xf32>
     tt.return
   }}
@@ -46,10 +56,19 @@ def _attn_ir(name, arguments, lhs, rhs, out, element, causal):
             f"{dot}    tt.return\n  }}\n}}\n")
 
 
-def attn_fwd_ir(block_m=128, block_n=128, head_dim=128, element="f32", causal=False):
-    args = ("%Q: !tt.ptr<{e}>, %K: !tt.ptr<{e}>, %V: !tt.ptr<{e}>, %O: !tt.ptr<{e}>, "
-            "%L: !tt.ptr<f32>, %sm_scale: f32, %stride_head: i32, %stride_seq: i32, "
-            "%stride_lse: i32, %N_CTX: i32")
+def attn_fwd_ir(block_m=128, block_n=128, head_dim=128, element="f32", causal=False, order="python"):
+    """`order`: "python" - python/examples/attention_training.py:38 (L fifth, N_CTX last);
+    "swift" - Sources/TritonMetalBench/AttentionKernel.swift:75-78 with the row statistic
+    (sm_scale fifth, L and stride_lse last); "swift_no_stats" - its eight-argument form."""
+    if order == "python":
+        args = ("%Q: !tt.ptr<{e}>, %K: !tt.ptr<{e}>, %V: !tt.ptr<{e}>, %O: !tt.ptr<{e}>, "
+                "%L: !tt.ptr<f32>, %sm_scale: f32, %stride_head: i32, %stride_seq: i32, "
+                "%stride_lse: i32, %N_CTX: i32")
+    else:
+        args = ("%Q: !tt.ptr<{e}>, %K: !tt.ptr<{e}>, %V: !tt.ptr<{e}>, %O: !tt.ptr<{e}>, "
+                "%sm_scale: f32, %stride_head: i32, %stride_seq: i32, %n_ctx: i32")
+        if order == "swift":
+            args += ", %L: !tt.ptr<f32>, %stride_lse: i32"
     return _attn_ir("attn_fwd", args, (block_m, head_dim), (head_dim, block_n),
                     (block_m, block_n), element, causal)
 
@@ -192,20 +211,41 @@ def sae_encode_ir(block_m=64, block_f=64, block_d=16):
 """
 
 
-class Kernel:
-    """emit -> compile -> load, the flow of MetalUtils.load_binary
-    (python/plugin/backend/driver.py:31-40); `release()` drops both handles."""
+class _Handle:
+    """A bare buffer handle presented the way the launcher takes pointer arguments."""
+    __slots__ = ("tm_handle",)
 
-    def __init__(self, ir, name, num_warps=4):
+    def __init__(self, handle):
+        self.tm_handle = handle
+
+
+class Kernel:
+    """IR -> metadata + descriptor -> library -> pipeline, the flow of MetalBackend.make_msl and
+    MetalUtils.load_binary (python/plugin/backend/compiler.py:131-146, driver.py:31-40), and
+    launches marshalled by MetalLauncher's rules (driver.py:58-92) from the `metal_args` that
+    `tm_kernel_info` reports - no per-kernel list of argument kinds is written down here.
+    `release()` drops both handles."""
+
+    def __init__(self, ir, name, num_warps=4, signature=None):
         self.name = name
         self.threads = 32 * num_warps
-        self.descriptor = _core.emit_msl(ir, num_warps)
-        self.library = _core.compile_msl(self.descriptor)
-        try:
-            self.handle = _core.load_kernel(self.library, name)
-        except Exception:
-            _core.release_library(self.library)
-            raise
+        self.metadata, image = launcher.make_msl(ir, num_warps)
+        self.descriptor = image.decode("utf-8")
+        self.metal_args = self.metadata["metal_args"]
+        if signature is None:       # every parameter of the Python definition is in the IR
+            signature = {f"arg{i}": "runtime" for i in range(len(self.metal_args))}
+        self.launcher = launcher.Launcher(signature)
+        self.library, self.handle, _, _, _ = launcher.load_binary(name, image)
+
+    def marshal(self, *call_args):
+        """(kinds, values) for the arguments of a Python-level call; integers in pointer
+        positions are buffer handles."""
+        call_args = list(call_args)
+        for index, kind, _dtype in self.metal_args:
+            pos = self.launcher.positions[index]
+            if kind == "pointer" and isinstance(call_args[pos], int):
+                call_args[pos] = _Handle(call_args[pos])
+        return self.launcher.marshal(self.metal_args, call_args)
 
     def set_path(self, path):
         cuda.set_option(self.handle, "path", path)
@@ -232,9 +272,6 @@ class Kernel:
             self.handle = self.library = 0
 
 
-B, I, F = _core.ARG_BUFFER, _core.ARG_I32, _core.ARG_F32
-
-
 def cdiv(a, b):
     return (a + b - 1) // b
 
@@ -249,8 +286,7 @@ class Matmul(Kernel):
     def arguments(self, a, b, c, M, N, K, strides=None):
         if strides is None:
             strides = (K, 1, N, 1, N, 1)
-        kinds = [B, B, B] + [I] * 9
-        values = [a, b, c, M, N, K, *strides]
+        kinds, values = self.marshal(a, b, c, M, N, K, *strides)
         grid = (cdiv(M, self.block[0]), cdiv(N, self.block[1]), 1)
         return grid, kinds, values
 
@@ -266,8 +302,7 @@ class AttnFwd(Kernel):
 
     def arguments(self, q, k, v, o, lse, scale, bh, seq):
         d = self.head_dim
-        kinds = [B, B, B, B, B, F, I, I, I, I]
-        values = [q, k, v, o, lse, _core.float_bits(scale), seq * d, d, seq, seq]
+        kinds, values = self.marshal(q, k, v, o, lse, scale, seq * d, d, seq, seq)
         return (cdiv(seq, self.block[0]), bh, 1), kinds, values
 
     def __call__(self, *args):
@@ -282,8 +317,8 @@ class AttnBwdPreprocess(Kernel):
 
     def arguments(self, o, do, delta, bh, seq):
         d = self.head_dim
-        return ((cdiv(seq, self.block_m), bh, 1), [B, B, B, I, I, I, I],
-                [o, do, delta, seq * d, d, seq, seq])
+        kinds, values = self.marshal(o, do, delta, seq * d, d, seq, seq)
+        return (cdiv(seq, self.block_m), bh, 1), kinds, values
 
     def __call__(self, *args):
         self.launch(*self.arguments(*args))
@@ -297,8 +332,7 @@ class AttnBwdDq(Kernel):
 
     def arguments(self, q, k, v, do, dq, lse, delta, scale, bh, seq):
         d = self.head_dim
-        kinds = [B] * 7 + [F, I, I, I, I]
-        values = [q, k, v, do, dq, lse, delta, _core.float_bits(scale), seq * d, d, seq, seq]
+        kinds, values = self.marshal(q, k, v, do, dq, lse, delta, scale, seq * d, d, seq, seq)
         return (cdiv(seq, self.block[0]), bh, 1), kinds, values
 
     def __call__(self, *args):
@@ -313,8 +347,7 @@ class AttnBwdDkdv(Kernel):
 
     def arguments(self, q, k, v, do, dk, dv, lse, delta, scale, bh, seq):
         d = self.head_dim
-        kinds = [B] * 8 + [F, I, I, I, I]
-        values = [q, k, v, do, dk, dv, lse, delta, _core.float_bits(scale), seq * d, d, seq, seq]
+        kinds, values = self.marshal(q, k, v, do, dk, dv, lse, delta, scale, seq * d, d, seq, seq)
         return (cdiv(seq, self.block[1]), bh, 1), kinds, values
 
     def __call__(self, *args):
@@ -330,7 +363,8 @@ class SaeEncode(Kernel):
 
     def arguments(self, x, w, bias, out, rows, model, features):
         grid = (cdiv(rows, self.block[0]), cdiv(features, self.block[1]), 1)
-        return grid, [B, B, B, B, I, I, I], [x, w, bias, out, rows, model, features]
+        kinds, values = self.marshal(x, w, bias, out, rows, model, features)
+        return grid, kinds, values
 
     def __call__(self, *a):
         self.launch(*self.arguments(*a))
@@ -350,9 +384,10 @@ class Elementwise(Kernel):
         """operands: buffer handles (in, out) or (a, b, out)."""
         grid = (programs if programs is not None else max(1, cdiv(n, self.block)), 1, 1)
         if self.kind == "scale_bias":
-            return grid, [B, B, F, F, I], [operands[0], operands[1], _core.float_bits(scale),
-                                           _core.float_bits(bias), n]
-        return grid, [B] * len(operands) + [I], list(operands) + [n]
+            kinds, values = self.marshal(operands[0], operands[1], scale, bias, n)
+        else:
+            kinds, values = self.marshal(*operands, n)
+        return grid, kinds, values
 
     def __call__(self, *operands, **kw):
         self.launch(*self.arguments(*operands, **kw))
@@ -368,7 +403,8 @@ class Softmax(Kernel):
     def arguments(self, x, y, rows, n_cols, stride_in=None, stride_out=None):
         stride_in = n_cols if stride_in is None else stride_in
         stride_out = n_cols if stride_out is None else stride_out
-        return (rows, 1, 1), [B, B, I, I, I], [x, y, stride_in, stride_out, n_cols]
+        kinds, values = self.marshal(x, y, stride_in, stride_out, n_cols)
+        return (rows, 1, 1), kinds, values
 
     def __call__(self, *a, **kw):
         self.launch(*self.arguments(*a, **kw))
