@@ -300,7 +300,12 @@ class GemmJob(Job):
         if M % dist.world:
             raise SystemExit("M must be a multiple of the number of ranks")
         self.rows = M // dist.world
-        blocks = gemm_row_blocks(M, dist.rank, dist.world)
+        # fused gather: one launch per step computes the rank's whole share of rows and stores
+        # it into every rank's copy of C; NCCL gather: block-cyclic row blocks, one launch and
+        # one all-gather per block
+        self.fused = dist.world > 1 and dist.gather_mode == "fused"
+        blocks = [(dist.rank * self.rows, self.rows)] if self.fused else gemm_row_blocks(M, dist.rank, dist.world)
+        self.row0 = blocks[0][0]
         self.chunks, self.block = len(blocks), blocks[0][1]
         self.a_host, self.b_host = [], None
         for row0, _ in blocks:
@@ -327,6 +332,18 @@ class GemmJob(Job):
         if self.dist.world > 1:
             torch = self.dist.torch
             self.stream = torch.cuda.ExternalStream(cuda.stream_handle())
+        if self.fused:
+            from triton_metal.gather import ReplicatedC
+
+            def exchange(mine):
+                out = [None] * self.dist.world
+                self.dist.dist.all_gather_object(out, mine)
+                return out
+
+            self.replicated = ReplicatedC(w["M"], w["N"], self.dist.rank, self.dist.world, exchange)
+            self.c_full = self.replicated.c
+        elif self.dist.world > 1:
+            torch = self.dist.torch
             self.c_full = self.track(cuda.alloc_device_buffer(w["M"] * w["N"] * 2))
             full = torch.as_tensor(DeviceView(cuda.device_pointer(self.c_full), (w["M"] * w["N"],), "<i2"),
                                    device="cuda").view(torch.bfloat16)
@@ -338,6 +355,9 @@ class GemmJob(Job):
     def step(self):
         if self.dist.world == 1:
             self.kernel.launch_async(*self.args[0])
+            return
+        if self.fused:
+            self.replicated.launch(self.kernel.handle, self.a[0], self.b, self.row0, self.rows, self.w["K"])
             return
         torch, works = self.dist.torch, []
         with torch.cuda.stream(self.stream):
@@ -411,11 +431,15 @@ class GemmJob(Job):
         N, rows = w["N"], 48
         b = from_bf16_bits(self.b_host)
         got = np.empty((rows, N), dtype=np.uint16)
-        self.core.buffer_read(self.c_local[0], 0, got.ctypes.data, got.nbytes)
+        if self.fused:
+            self.core.buffer_read(self.c_full, self.row0 * N * 2, got.ctypes.data, got.nbytes)
+        else:
+            self.core.buffer_read(self.c_local[0], 0, got.ctypes.data, got.nbytes)
         worst = ref.relative_error(from_bf16_bits(got), ref.matmul(from_bf16_bits(self.a_host[0][:rows]), b))
         if world > 1:
             other, chunk = (rank + 1) % world, self.chunks - 1
-            row0 = (chunk * world + other) * self.block          # first row of that block in C
+            # first row of that block in C
+            row0 = other * self.rows if self.fused else (chunk * world + other) * self.block
             tail = row0 + self.block - rows
             a_other, _ = gemm_inputs_bf16(w["M"], N, w["K"], self.seed, row0, self.block)
             self.core.buffer_read(self.c_full, tail * N * 2, got.ctypes.data, got.nbytes)
@@ -429,6 +453,12 @@ class GemmJob(Job):
 
     def all_kernels(self):
         return [self.kernel]
+
+    def close(self):
+        if self.fused:
+            self.dist.barrier()          # no rank is still storing into another's copy
+            self.replicated.close()
+        super().close()
 
     def path(self):
         return self.kernel.last_path()

@@ -205,6 +205,43 @@ int32_t tmx_matmul_f32_static_prepare(void);
 /* Free and total device memory in bytes, as the driver reports them.  0 / -1. */
 int32_t tmx_device_memory(int64_t *free_bytes, int64_t *total_bytes);
 
+/* ---- row-sharded matmul over several GPUs (no counterpart in the reference: it drives one
+ * device, Sources/TritonMetalCore/Runtime.swift:10-11) -------------------------------------
+ *
+ * One process per GPU.  Each rank computes a block of rows of C = A @ B (B replicated) and
+ * every rank ends up with the whole C.  Instead of a collective behind the kernel, the
+ * kernel's epilogue stores each finished tile into every rank's copy of C - its own and,
+ * through memory mapped from the other processes, the peers' - so the exchange overlaps the
+ * main loop.  Set-up, once: every rank allocates its copy of C and a flag array
+ * (tmx_alloc_device_buffer; tmx_gather_flag_bytes() bytes, zero-filled), exports both
+ * (tmx_ipc_export), passes the 64-byte tokens to the other ranks by any means, and imports
+ * theirs (tmx_ipc_import). */
+
+/* The token for another process to map `buffer` (plain device memory only).  0 / -1. */
+int32_t tmx_ipc_export(int64_t buffer, void *handle64);
+/* Map another process's buffer of `nbytes` bytes; enables peer access to its GPU.  A buffer
+ * handle (device-only; tm_free_buffer unmaps it), 0 on failure. */
+int64_t tmx_ipc_import(const void *handle64, int64_t nbytes);
+/* Size of a flag array in bytes (64 slots x 8 ranks x 4). */
+int64_t tmx_gather_flag_bytes(void);
+/* Enqueue C[row0 : row0+rows, :] = A[rows, K] @ B[K, N] (16-bit, row-major, dense) on the
+ * tensor cores and store the result rows into every copy c_replicas[0..world-1] of the whole
+ * C (c_replicas[rank] is this rank's own buffer, the others are imported).  When this rank's
+ * last tile is out it writes `epoch` into word slot*8 + rank of every peer's flag array; with
+ * wait_for_peers != 0 the kernel then waits (bounded; on expiry the launch fails like any
+ * other bounded wait) until words slot*8 + r of its own flag array have reached `epoch` for all
+ * r, so that on completion this rank's copy of C holds every rank's rows.
+ *  - `epoch` must be positive and grow from launch to launch on the same slot, on all ranks
+ *    alike; slots 0...63 let independent row blocks be in flight at once.
+ *  - All ranks must make the matching call; a rank that does not lets the others' waits run out.
+ *  - A later launch overwrites the peers' copies: the caller makes sure (a barrier, or a second
+ *    set of copies) that every rank is done reading C before any rank computes into it again.
+ * Returns 0 / -1 at once; tmx_synchronize or any blocking call waits for the kernel. */
+int32_t tmx_matmul_gathered(int64_t kernel, int64_t a, int64_t b, const int64_t *c_replicas,
+                            const int64_t *flag_buffers, int32_t world, int32_t rank, int64_t row0,
+                            int64_t rows, int64_t N, int64_t K, int32_t slot, uint32_t epoch,
+                            int32_t wait_for_peers);
+
 /* ---- failure-path aids (no counterpart in the reference) -------------------
  *
  * Every wait inside the tensor-core kernels is bounded: when its cycle budget runs out the
@@ -219,6 +256,14 @@ int32_t tmx_device_memory(int64_t *free_bytes, int64_t *total_bytes);
  * thread) and results[1] (a wait by a whole warp) are 1 when the wait reported "gave up".
  * The status word is left set: the next synchronising call returns -1. */
 int32_t tmx_selftest_bounded_wait(int64_t budget_cycles, int32_t *results);
+/* The per-CTA work lists the persistent attention kernels walk for a problem shape (kind 0
+ * forward: 256-row query blocks; 1 dq, 2 dkdv: 128-row tiles), for inspection and tests.  Up to
+ * `capacity` (batch-head, block) pairs go to items_out, ctas + 1 list offsets to begin_out, the
+ * modelled cost of every CTA to load_out (each may be NULL; a list never has more CTAs than
+ * items, so fewer than `ctas` + 1 offsets may be written).  Returns the item count or -1. */
+int64_t tmx_debug_attention_schedule(int32_t kind, int32_t bh, int32_t rows, int32_t n_ctx, int32_t causal,
+                                     int32_t ctas, int32_t *items_out, int64_t capacity, int32_t *begin_out,
+                                     int64_t *load_out);
 /* Set the device status word from the host, as a kernel whose wait gave up would. */
 int32_t tmx_debug_inject_status(int32_t code, int32_t where, int32_t block, int32_t extra);
 

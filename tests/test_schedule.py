@@ -1,0 +1,72 @@
+"""The per-CTA work lists of the persistent attention kernels (csrc/attn_schedule.h), on the host.
+
+Every item is dealt out exactly once; the CTAs' modelled loads differ by less than one item;
+a CTA's list follows the global (batch, head)-major order, so CTAs that run side by side are
+on the same few heads; and a shard of a job spread over eight GPUs - 16 (batch, head) slices,
+about as many items as SMs - still keeps every SM busy."""
+
+import numpy as np
+import pytest
+
+from triton_metal import cuda
+
+SHAPES = [
+    # kind, bh, rows, n_ctx, causal
+    ("fwd", 128, 4096, 4096, True), ("fwd", 16, 4096, 4096, True), ("fwd", 16, 4096, 4096, False),
+    ("fwd", 16, 16384, 16384, True), ("fwd", 3, 1000, 1000, True), ("fwd", 1, 128, 128, True),
+    ("fwd", 5, 384, 1024, False),
+    ("dq", 128, 4096, 4096, True), ("dq", 16, 4096, 4096, True), ("dq", 2, 1000, 1000, False),
+    ("dkdv", 128, 4096, 4096, True), ("dkdv", 16, 4096, 4096, True), ("dkdv", 7, 640, 640, True),
+]
+
+
+def cost_of(kind, block, n_ctx, causal):
+    all_blocks = -(-n_ctx // 128)
+    if not causal:
+        return all_blocks
+    if kind == "fwd":
+        return min(all_blocks, -(-min(n_ctx, (block + 1) * 256) // 128))
+    return min(all_blocks, block + 1) if kind == "dq" else max(1, all_blocks - block)
+
+
+@pytest.mark.parametrize("kind,bh,rows,n_ctx,causal", SHAPES)
+def test_every_item_once_and_loads_level(kind, bh, rows, n_ctx, causal):
+    ctas = 148
+    lists, loads = cuda.attention_schedule(kind, bh, rows, n_ctx, causal, ctas)
+    block_rows = 256 if kind == "fwd" else 128
+    blocks = -(-rows // block_rows)
+    seen = sorted(item for lst in lists for item in lst)
+    assert seen == [(h, b) for h in range(bh) for b in range(blocks)]
+    assert len(lists) == min(ctas, bh * blocks) and all(lists)
+    overhead = 3 if kind == "fwd" else 2
+    costs = [cost_of(kind, b, n_ctx, causal) + overhead for b in range(blocks)]
+    # the model's loads are what the items add up to, and no CTA is more than one item behind
+    for lst, load in zip(lists, loads):
+        assert load == sum(costs[b] for _, b in lst)
+    assert max(loads) - min(loads) <= max(costs)
+    # a CTA meets its items in dispatch order.  Before the tail (the last whole heads holding at
+    # most three items per CTA, dealt longest first whatever their head) that is head-major with
+    # the long blocks of a head first; inside the tail, by decreasing cost.
+    tail_heads = max(1, min(bh, (3 * len(lists)) // blocks))
+    for lst in lists:
+        body = [(h, b) for h, b in lst if h < bh - tail_heads]
+        tail = [(h, b) for h, b in lst if h >= bh - tail_heads]
+        assert lst == body + tail
+        assert [h for h, _ in body] == sorted(h for h, _ in body)
+        for (h0, b0), (h1, b1) in zip(body, body[1:]):
+            if h0 == h1:
+                assert costs[b0] >= costs[b1]
+        assert [costs[b] for _, b in tail] == sorted((costs[b] for _, b in tail), reverse=True)
+
+
+def test_an_eighth_of_the_job_keeps_the_sms_busy():
+    """16 of 128 (batch, head) slices at seq 4096, causal: the busiest CTA's load over the mean
+    bounds the loss against perfect division of the work."""
+    for kind, bound in (("fwd", 1.10), ("dq", 1.05), ("dkdv", 1.05)):
+        _, loads = cuda.attention_schedule(kind, 16, 4096, 4096, True, 148)
+        assert len(loads) == 148
+        assert max(loads) / np.mean(loads) <= bound, (kind, max(loads), np.mean(loads))
+    # the whole job on one GPU: within a few per cent of perfect
+    for kind in ("fwd", "dq", "dkdv"):
+        _, loads = cuda.attention_schedule(kind, 128, 4096, 4096, True, 148)
+        assert max(loads) / np.mean(loads) <= 1.03, kind

@@ -9,9 +9,9 @@
 // directions stay separate kernels, as in the reference, so every gradient is
 // deterministic (no atomics).
 //
-// Both kernels are persistent: one CTA per SM walks work units of 128 resident rows of one
-// (batch, head) (queries for dq, keys for dkdv; under a causal mask a long tile paired with a
-// short one); the other side streams through in blocks of 128 rows (MMAs with N = 128:
+// Both kernels are persistent: one CTA per SM walks its list of work items - 128 resident rows
+// of one (batch, head) (queries for dq, keys for dkdv); the other side streams through in
+// blocks of 128 rows (MMAs with N = 128:
 // narrower score tiles ran the tensor pipe at half rate, measured).
 // Warp 16 issues TMA loads, warp 17 - converged, one lane elected per instruction - issues every
 // tcgen05.mma, and four warpgroups (warps
@@ -34,6 +34,7 @@
 // HBM layout: Q, K, V, dO, dQ, dK, dV [BH, S, D] with D contiguous; L, Delta
 // [BH, S] fp32.
 
+#include "attn_schedule.h"
 #include "sm100_ptx.cuh"
 
 #include <cuda_bf16.h>
@@ -244,31 +245,10 @@ struct SharedDq {
   int abort_flag;
 };
 
-// Work list of a persistent kernel: a unit is one (batch, head) and one 128-row tile of the
-// resident side - or, under a causal mask, a long tile paired with a short one, so that every
-// unit costs the same.  `long_last` says which end of the sequence is long: query tile i sees
-// i + 1 key blocks (dq: the last tiles are long), key tile i is seen by T - i query blocks
-// (dkdv: the first are).  Units of one head are adjacent, so CTAs running side by side share
-// that head's streamed tensors in L2.
-struct TileSchedule {
-  int tiles;            // 128-row tiles per head
-  int units_per_head;
-  int total_units;
-  int causal;
-  int long_last;
-  __device__ __forceinline__ int subs(int u) const {
-    if (!causal) return 1;
-    const int k = u % units_per_head;
-    return (tiles - 1 - k != k) ? 2 : 1;
-  }
-  __device__ __forceinline__ int head(int u) const { return u / units_per_head; }
-  __device__ __forceinline__ int tile(int u, int sub) const {   // the long tile first
-    const int k = u % units_per_head;
-    if (!causal) return k;
-    const int far = tiles - 1 - k;
-    return (sub == 0) == (long_last != 0) ? far : k;
-  }
-};
+// Work of a persistent kernel: every CTA walks its own list of items (attn_schedule.h), an item
+// being one (batch, head) and one 128-row tile of the resident side.  Under a causal mask the
+// tiles differ in length - query tile i sees i + 1 key blocks, key tile i is seen by T - i query
+// blocks - and the lists are balanced on the host.
 
 // Pipeline of block j (keys j*128 ...):
 //   MMA   S(j) = Q K(j)^T into S[j&1]            (issued two blocks ahead)
@@ -284,7 +264,7 @@ template <typename T, int D, uint32_t FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                      Params prm, TileSchedule sch, DeviceStatus* status) {
+                      Params prm, DeviceWorkList work, DeviceStatus* status) {
   constexpr int TILE = BLK * D * 2;
   constexpr int S_COL = 0, DP_COL = 256, DQ_COL = 384;     // S[b] at b*128
   extern __shared__ uint8_t smem_raw[];
@@ -355,10 +335,11 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ++v_issued;
         return true;
       };
-      for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
-        const int bh = sch.head(u);
-        for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
-          const int m0 = sch.tile(u, sub) * BLK;
+      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
+      {
+        for (int it = first_item; it < end_item && ok; ++it, ++item) {
+          const int bh = __ldg(&work.items[it].bh);
+          const int m0 = __ldg(&work.items[it].block) * BLK;
           const int n_blocks = key_blocks(m0);
           // Q and dO are single-buffered: the previous tile's last S and dP must have retired
           if (!mbar_wait(smem_u32(&ss.qdo_empty), (item & 1) ^ 1, wc, 30)) { ok = false; break; }
@@ -435,9 +416,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ++c;
         if (++ks == K_STAGES) ks = 0;
       };
-      for (int u = blockIdx.x; u < sch.total_units; u += gridDim.x) {
-        for (int sub = 0; sub < sch.subs(u); ++sub, ++item) {
-          const int n_blocks = key_blocks(sch.tile(u, sub) * BLK);
+      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
+      {
+        for (int it = first_item; it < end_item; ++it, ++item) {
+          const int n_blocks = key_blocks(__ldg(&work.items[it].block) * BLK);
           // The first S and dP of this tile go out while the element-wise warps may still be
           // storing the previous dQ: they use other TMEM columns, and the first dQ MMA waits
           // for ds_full, which those warps only signal after that store.
@@ -463,10 +445,11 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const float qk_scale = prm.sm_scale * kLog2e;
     uint32_t item = 0, c = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
-      const int bh = sch.head(u);
-      for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
-        const int m0 = sch.tile(u, sub) * BLK;
+    const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
+    {
+      for (int it = first_item; it < end_item && ok; ++it, ++item) {
+        const int bh = __ldg(&work.items[it].bh);
+        const int m0 = __ldg(&work.items[it].block) * BLK;
         const int n_blocks = key_blocks(m0);
         const int q_row = m0 + row_in_tile;
         float lse = 0.f, delta = 0.f;
@@ -552,7 +535,7 @@ template <typename T, int D, uint32_t FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                        Params prm, TileSchedule sch, DeviceStatus* status) {
+                        Params prm, DeviceWorkList work, DeviceStatus* status) {
   constexpr int TILE = BLK * D * 2;
   constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -613,10 +596,11 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       uint32_t issued = 0, do_issued = 0;
       uint32_t item = 0, c = 0;          // key tiles and query blocks loaded so far
       bool ok = true;
-      for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
-        const int bh = sch.head(u);
-        for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
-          const int n0 = sch.tile(u, sub) * BLK;
+      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
+      {
+        for (int it = first_item; it < end_item && ok; ++it, ++item) {
+          const int bh = __ldg(&work.items[it].bh);
+          const int n0 = __ldg(&work.items[it].block) * BLK;
           const int first = first_block(n0), n_iter = total_q_blocks - first;
           // K and V are single-buffered: the previous tile's last S^T and dP^T must have retired
           if (!mbar_wait(smem_u32(&ss.kv_empty), (item & 1) ^ 1, wc, 50)) { ok = false; break; }
@@ -710,9 +694,10 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         ++c;
       };
-      for (int u = blockIdx.x; u < sch.total_units; u += gridDim.x) {
-        for (int sub = 0; sub < sch.subs(u); ++sub, ++item) {
-          const int n_iter = total_q_blocks - first_block(sch.tile(u, sub) * BLK);
+      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
+      {
+        for (int it = first_item; it < end_item; ++it, ++item) {
+          const int n_iter = total_q_blocks - first_block(__ldg(&work.items[it].block) * BLK);
           // The first S^T and dP^T of this tile go out while the element-wise warps may still be
           // storing the previous dK and dV: they use other TMEM columns, and the first dV and dK
           // MMAs wait for p_full / ds_full, which those warps only signal after that store.
@@ -744,12 +729,13 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t p_chunk0 = (group % 2) * 4, p_xor = row_in_tile & 7;
     uint32_t item = 0, c = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < sch.total_units && ok; u += gridDim.x) {
-      const int bh = sch.head(u);
-      const float* lse_base = prm.lse + (int64_t)bh * prm.stride_lse;
-      const float* delta_base = prm.delta + (int64_t)bh * prm.stride_lse;
-      for (int sub = 0; sub < sch.subs(u) && ok; ++sub, ++item) {
-        const int n0 = sch.tile(u, sub) * BLK;
+    const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
+    {
+      for (int it = first_item; it < end_item && ok; ++it, ++item) {
+        const int bh = __ldg(&work.items[it].bh);
+        const float* lse_base = prm.lse + (int64_t)bh * prm.stride_lse;
+        const float* delta_base = prm.delta + (int64_t)bh * prm.stride_lse;
+        const int n0 = __ldg(&work.items[it].block) * BLK;
         const int first = first_block(n0), n_iter = total_q_blocks - first;
         const int k_row = n0 + row_in_tile;
         // Row statistics of the streamed query block go through shared memory (every thread
@@ -869,6 +855,8 @@ Params make_params(const AttnProblem& p) {
   return prm;
 }
 
+WorkListCache g_lists;     // work lists already in device memory, by problem shape
+
 template <typename T, int D, uint32_t FMT>
 std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type, bool dkdv) {
   CUtensorMap maps[4];
@@ -882,25 +870,24 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   size_t smem = dkdv ? 6 * (size_t)(BLK * D * 2) + P_TILE + sizeof(SharedDkdv)
                      : (2 + K_STAGES + V_STAGES) * (size_t)(BLK * D * 2) + sizeof(SharedDq) + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
-  dim3 grid((unsigned)((p.rows + BLK - 1) / BLK), (unsigned)p.bh, 1);
   cudaError_t e;
-  TileSchedule sch{};
-  sch.tiles = (int)((p.rows + BLK - 1) / BLK);
-  sch.causal = p.causal;
-  sch.long_last = dkdv ? 0 : 1;       // early key tiles are seen by every query block, late query tiles see every key
-  sch.units_per_head = p.causal ? (sch.tiles + 1) / 2 : sch.tiles;
-  sch.total_units = sch.units_per_head * (int)p.bh;
-  const int persistent = sch.total_units < ctx.sm_count ? sch.total_units : ctx.sm_count;
+  std::string werr;
+  const WorkListCache::Key key{dkdv ? 2 : 1, (int)p.bh, (int)p.rows, (int)p.n_ctx, p.causal, ctx.sm_count};
+  const DeviceWorkList work = g_lists.get(
+      key,
+      [&] { return schedule_attn_bwd((int)p.bh, (int)p.rows, (int)p.n_ctx, p.causal != 0, !dkdv, ctx.sm_count); },
+      ctx.stream, werr);
+  if (!werr.empty()) return werr;
   if (dkdv) {
     auto kernel = attn_bwd_dkdv_tc_kernel<T, D, FMT>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return std::string(what) + ": " + cudaGetErrorString(e);
-    kernel<<<persistent, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, sch, ctx.status);
+    kernel<<<work.ctas, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, work, ctx.status);
   } else {
     auto kernel = attn_bwd_dq_tc_kernel<T, D, FMT>;
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return std::string(what) + ": " + cudaGetErrorString(e);
-    kernel<<<persistent, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, sch, ctx.status);
+    kernel<<<work.ctas, NUM_THREADS, smem, ctx.stream>>>(maps[0], maps[1], maps[2], maps[3], prm, work, ctx.status);
   }
   ++*ctx.launches;
   e = cudaGetLastError();

@@ -17,6 +17,18 @@
 // HBM layout: A [M,K] row-major, B [K,N] row-major, C [M,N] row-major, element
 // strides multiples of 8 (16 bytes); ragged M, N, K edges are handled by TMA
 // zero fill on loads and by masks on stores.
+//
+// Gathered form (row-sharded GEMM over several GPUs, one process per GPU): the same kernel
+// with an epilogue that writes every finished tile of this rank's rows into every rank's
+// copy of the whole C - its own and, through peer-mapped memory, the others' - with plain
+// 16-byte global stores, so the exchange that replicates C runs tile by tile under the main
+// loop instead of as a collective behind it.  Tiles are staged through shared memory so that
+// a warp's store instruction covers two 256-byte row segments (NVLink moves 256-byte
+// payloads; the thread-per-row layout of the accumulator would give 64-byte pieces).  When a
+// rank's last tile is out it raises one flag per peer (release, system scope); the last CTA
+// then waits - bounded - until every peer's flag for this launch has arrived, so that when
+// the kernel completes this rank's copy of C is whole.  No TMA instruction and no library
+// call ever touches a peer's memory.
 
 #include "sm100_ptx.cuh"
 
@@ -84,9 +96,23 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KiB
 constexpr int GROUP_M = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
+constexpr int MAX_RANKS = 8;                    // copies of C a gathered launch can feed
+constexpr int STAGING_COLS = 128;               // columns staged per pass: 256-byte row segments
+constexpr int STAGING_BYTES = 4 * 32 * STAGING_COLS * 2;   // four epilogue warps x 32 rows
+
+// What a gathered launch adds to the plain one.
+struct GatherArgs {
+  void* replica[MAX_RANKS];        // rank r's copy of the whole C (own memory or peer-mapped)
+  uint32_t* flags[MAX_RANKS];      // rank r's flag array: word slot*MAX_RANKS + s is raised by rank s
+  unsigned int* finished;          // this rank's counter of CTAs that have stored their last tile
+  int world, rank, slot;
+  uint32_t epoch;                  // value the flags take for this launch (grows launch by launch)
+  int wait_for_peers;
+  long long wait_budget;           // cycles the final wait may take
+};
 
 // site codes reported by bounded waits
-enum Site : uint32_t { kProdEmpty = 1, kMmaFull = 2, kMmaAccEmpty = 3, kEpiAccFull = 4, kDrain = 5 };
+enum Site : uint32_t { kProdEmpty = 1, kMmaFull = 2, kMmaAccEmpty = 3, kEpiAccFull = 4, kDrain = 5, kPeerFlag = 6 };
 
 struct SharedStorage {
   alignas(8) uint64_t full[STAGES];
@@ -117,10 +143,11 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <typename T, uint32_t FMT>
+template <typename T, uint32_t FMT, bool GATHER>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               T* __restrict__ C, int M, int N, int K, int64_t scm, DeviceStatus* status) {
+               T* __restrict__ C, int M, int N, int K, int64_t scm, DeviceStatus* status,
+               const __grid_constant__ GatherArgs gather) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the 128-byte swizzle atoms
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -244,25 +271,77 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(smem_u32(&ss.acc_full[acc]), acc_phase, wc, kEpiAccFull)) { ok = false; break; }
       tc_fence_after();
-      const int row = tm * BM + warp * 32 + lane;
-      T* crow = C + (int64_t)row * scm + (int64_t)tn * BN;
-      const int cols_left = N - tn * BN;
+      if constexpr (GATHER) {
+        // C is this rank's first row inside a copy of the whole matrix: the same element offset
+        // holds in every copy.  128 columns at a time go through this warp's staging rows
+        // (16-byte chunks XORed with the row so that neither side of the exchange conflicts on
+        // banks), then out to every copy, two 256-byte row segments per store instruction.
+        const uint32_t stage_addr = smem_base + STAGES * STAGE_BYTES + 1024 + warp * (32 * STAGING_COLS * 2);
+        const int64_t base_off = C - (T*)gather.replica[gather.rank];
+        const int cols_left = N - tn * BN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + acc * BN + c0, r);
-        tmem_ld_wait();
-        if (row < M) {
+        for (int h = 0; h < BN / STAGING_COLS; ++h) {
+#pragma unroll 1
+          for (int c4 = 0; c4 < STAGING_COLS / 32; ++c4) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + acc * BN + h * STAGING_COLS + c4 * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const int col = c0 + v * 8;
-            if (col + 8 <= cols_left) {
-              uint4 out;
-              out.x = pack2<T>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-              out.y = pack2<T>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-              out.z = pack2<T>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-              out.w = pack2<T>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-              *reinterpret_cast<uint4*>(crow + col) = out;
+            for (int v = 0; v < 4; ++v) {
+              const uint32_t chunk = (uint32_t)(c4 * 4 + v) ^ (uint32_t)(lane & 15);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_addr + lane * 256 + chunk * 16),
+                           "r"(pack2<T>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]))),
+                           "r"(pack2<T>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]))),
+                           "r"(pack2<T>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]))),
+                           "r"(pack2<T>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7])))
+                           : "memory");
+            }
+          }
+          __syncwarp();
+          const int chunk = lane & 15;                         // 16-byte piece of a 256-byte segment
+          const int col = h * STAGING_COLS + chunk * 8;
+          const bool col_ok = col + 8 <= cols_left;
+#pragma unroll 1
+          for (int it = 0; it < 16; ++it) {
+            const int r_in = it * 2 + (lane >> 4);
+            const int row = tm * BM + warp * 32 + r_in;
+            uint4 val;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                         : "r"(stage_addr + r_in * 256 + ((chunk ^ (r_in & 15)) * 16)));
+            if (row < M && col_ok) {
+              const int64_t off = base_off + (int64_t)row * scm + (int64_t)tn * BN + col;
+              // peers first, each rank starting with a different one, the local copy last
+              for (int p = 1; p <= gather.world; ++p) {
+                int dst = gather.rank + p;
+                if (dst >= gather.world) dst -= gather.world;
+                *reinterpret_cast<uint4*>((T*)gather.replica[dst] + off) = val;
+              }
+            }
+          }
+          __syncwarp();
+        }
+      } else {
+        const int row = tm * BM + warp * 32 + lane;
+        T* crow = C + (int64_t)row * scm + (int64_t)tn * BN;
+        const int cols_left = N - tn * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + acc * BN + c0, r);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int col = c0 + v * 8;
+              if (col + 8 <= cols_left) {
+                uint4 out;
+                out.x = pack2<T>(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+                out.y = pack2<T>(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+                out.z = pack2<T>(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+                out.w = pack2<T>(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+                *reinterpret_cast<uint4*>(crow + col) = out;
+              }
             }
           }
         }
@@ -270,6 +349,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ss.acc_empty[acc]));
+    }
+    if constexpr (GATHER) {
+      // Every store of this CTA is out.  Make them visible to the other GPUs, count the CTA, and
+      // let the last one of this rank tell the peers - then wait for what they have to tell.
+      __threadfence_system();
+      asm volatile("bar.sync 1, 128;" ::: "memory");          // the four epilogue warps
+      if (threadIdx.x == 0) {
+        const unsigned int before = atomicAdd(gather.finished, 1u);
+        if (before == gridDim.x - 1) {
+          *gather.finished = 0;                                // ready for the next launch
+          __threadfence_system();
+          const int word = gather.slot * MAX_RANKS;
+          for (int p = 1; p < gather.world; ++p) {
+            int dst = gather.rank + p;
+            if (dst >= gather.world) dst -= gather.world;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(gather.flags[dst] + word + gather.rank),
+                         "r"(gather.epoch)
+                         : "memory");
+          }
+          if (gather.wait_for_peers) {
+            const long long start = clock64();
+            for (int r = 0; r < gather.world; ++r) {
+              if (r == gather.rank) continue;
+              const uint32_t* flag = gather.flags[gather.rank] + word + r;
+              for (;;) {
+                uint32_t seen;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+                if ((int32_t)(seen - gather.epoch) >= 0) break;      // this launch's flag, or a later one
+                if (clock64() - start > gather.wait_budget) {
+                  report_timeout(wc, kPeerFlag, (uint32_t)r);
+                  r = gather.world;                                  // give up on the others as well
+                  break;
+                }
+              }
+            }
+          }
+        }
+      }
     }
   }
 
@@ -282,7 +399,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 template <typename T, uint32_t FMT>
-std::string launch_typed(const GemmProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type) {
+std::string launch_typed(const GemmProblem& p, const LaunchCtx& ctx, CUtensorMapDataType type,
+                         const GatherArgs* gather) {
   CUtensorMap map_a, map_b;
   {
     uint64_t dims[2] = {(uint64_t)p.K, (uint64_t)p.M};
@@ -298,14 +416,15 @@ std::string launch_typed(const GemmProblem& p, const LaunchCtx& ctx, CUtensorMap
     std::string e = make_tensor_map(&map_b, type, 2, p.b, dims, strides, box);
     if (!e.empty()) return e;
   }
-  const size_t smem = STAGES * STAGE_BYTES + sizeof(SharedStorage) + 1024;
-  auto kernel = gemm_tc_kernel<T, FMT>;
+  const size_t smem = STAGES * STAGE_BYTES + 1024 + 1024 + (gather ? STAGING_BYTES : 0);
+  auto kernel = gather ? gemm_tc_kernel<T, FMT, true> : gemm_tc_kernel<T, FMT, false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return std::string("matmul_kernel: ") + cudaGetErrorString(e);
   const int tiles = (int)(((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN));
   const int grid = tiles < ctx.sm_count ? tiles : ctx.sm_count;
+  GatherArgs none{};
   kernel<<<grid, NUM_THREADS, smem, ctx.stream>>>(map_a, map_b, (T*)p.c, (int)p.M, (int)p.N, (int)p.K,
-                                                 p.scm, ctx.status);
+                                                 p.scm, ctx.status, gather ? *gather : none);
   ++*ctx.launches;
   e = cudaGetLastError();
   if (e != cudaSuccess) return std::string("matmul_kernel launch failed: ") + cudaGetErrorString(e);
@@ -332,8 +451,30 @@ bool gemm_tc_eligible(const GemmProblem& p, std::string* why) {
 
 std::string launch_gemm_tc(const GemmProblem& p, const LaunchCtx& ctx) {
   if (p.elt == Elt::BF16)
-    return launch_typed<__nv_bfloat16, 1>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
-  return launch_typed<__half, 0>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+    return launch_typed<__nv_bfloat16, 1>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, nullptr);
+  return launch_typed<__half, 0>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, nullptr);
+}
+
+// The gathered form: p.c points at this rank's first row inside its own copy of the whole C
+// (g.replica[g.rank] + row0 * stride_cm); every finished tile also goes to the same place in
+// the other copies.
+std::string launch_gemm_tc_gathered(const GemmProblem& p, const GemmGather& g, const LaunchCtx& ctx) {
+  if (g.world < 1 || g.world > MAX_RANKS || g.rank < 0 || g.rank >= g.world) return "rank / world out of range";
+  GatherArgs a{};
+  for (int r = 0; r < g.world; ++r) {
+    a.replica[r] = g.replica[r];
+    a.flags[r] = g.flags[r];
+  }
+  a.finished = g.finished;
+  a.world = g.world;
+  a.rank = g.rank;
+  a.slot = g.slot;
+  a.epoch = g.epoch;
+  a.wait_for_peers = g.wait_for_peers;
+  a.wait_budget = g.wait_budget_cycles > 0 ? g.wait_budget_cycles : ptx::kWaitCycles;
+  if (p.elt == Elt::BF16)
+    return launch_typed<__nv_bfloat16, 1>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, &a);
+  return launch_typed<__half, 0>(p, ctx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, &a);
 }
 
 }  // namespace tmc

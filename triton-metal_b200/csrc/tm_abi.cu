@@ -5,6 +5,7 @@
 
 #include "../../include/tm.h"
 #include "tm_core.h"
+#include "attn_schedule.h"
 
 #include <algorithm>
 #include <atomic>
@@ -73,9 +74,12 @@ struct BufferObj : Object {
   int64_t length = 0;
   bool host_exposed = false;   // tm_buffer_contents handed the pointer to the host
   bool device_only = false;    // plain device memory (tmx_alloc_device_buffer): no host pointer
+  bool imported = false;       // another process's device memory, mapped by tmx_ipc_import
   BufferObj() : Object(ObjKind::Buffer) {}
   ~BufferObj() override {
-    if (ptr) cudaFree(ptr);
+    if (!ptr) return;
+    if (imported) cudaIpcCloseMemHandle(ptr);
+    else cudaFree(ptr);
   }
 };
 
@@ -160,6 +164,7 @@ struct Device {
   bool probed = false;
   std::string unusable;      // empty when usable
   int64_t launches = 0;
+  unsigned int* gather_counter = nullptr;   // device word: CTAs of a gathered GEMM that are done
 };
 
 Device g_dev;
@@ -1155,6 +1160,131 @@ int32_t tmx_device_memory(int64_t* free_bytes, int64_t* total_bytes) {
   return 0;
 }
 
+// ---- buffers shared between the processes of a multi-GPU job --------------------------
+
+// The 64-byte token another process on this machine turns into a mapping of this buffer
+// (cudaIpcGetMemHandle).  Only plain device memory (tmx_alloc_device_buffer) can be shared.
+int32_t tmx_ipc_export(int64_t buffer, void* handle64) {
+  std::string err;
+  if (!handle64) { store_error(invalid_argument("tmx_ipc_export needs 64 bytes for the handle")); return -1; }
+  auto b = lookup_as<BufferObj>(buffer, ObjKind::Buffer, err);
+  if (!b) { store_error(err); return -1; }
+  if (!b->device_only || b->imported) {
+    store_error(invalid_argument("only a buffer made by tmx_alloc_device_buffer can be exported"));
+    return -1;
+  }
+  if (!bind_device(err)) { store_error(err); return -1; }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, b->ptr);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    store_error(cuda_error(std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e)));
+    return -1;
+  }
+  std::memcpy(handle64, &h, 64);
+  return 0;
+}
+
+// Maps another process's exported buffer (of `nbytes` bytes) into this one and enables peer
+// access to its GPU.  The result is a device-only buffer handle: kernels may write it, copies
+// may read it; tm_free_buffer unmaps it.
+int64_t tmx_ipc_import(const void* handle64, int64_t nbytes) {
+  std::string err;
+  if (!handle64 || nbytes <= 0) {
+    store_error(invalid_argument("tmx_ipc_import needs a handle and a positive length"));
+    return 0;
+  }
+  if (!bind_device(err)) { store_error(err); return 0; }
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, 64);
+  auto b = std::make_shared<BufferObj>();
+  cudaError_t e = cudaIpcOpenMemHandle(&b->ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    b->ptr = nullptr;
+    store_error(cuda_error(std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e)));
+    return 0;
+  }
+  b->length = nbytes;
+  b->device_only = true;
+  b->imported = true;
+  return g_handles.insert(b);
+}
+
+int64_t tmx_gather_flag_bytes(void) { return (int64_t)kGatherFlagSlots * kGatherMaxRanks * 4; }
+
+// Row-sharded matmul whose epilogue replicates C (see include/tm.h).  Enqueues and returns.
+int32_t tmx_matmul_gathered(int64_t kernel, int64_t a, int64_t b, const int64_t* c_replicas,
+                            const int64_t* flag_buffers, int32_t world, int32_t rank, int64_t row0,
+                            int64_t rows, int64_t N, int64_t K, int32_t slot, uint32_t epoch,
+                            int32_t wait_for_peers) {
+  std::string err;
+  auto fail = [&](const std::string& m) { store_error(m); return -1; };
+  auto k = lookup_as<KernelObj>(kernel, ObjKind::Kernel, err);
+  if (!k) return fail(err);
+  if (k->desc.id != KernelId::Matmul || k->desc.elt == Elt::F32)
+    return fail(invalid_argument("tmx_matmul_gathered takes a 16-bit matmul_kernel"));
+  if (!c_replicas || !flag_buffers || world < 1 || world > kGatherMaxRanks || rank < 0 || rank >= world)
+    return fail(invalid_argument("tmx_matmul_gathered needs 1...8 ranks, this rank among them, and their buffers"));
+  if (slot < 0 || slot >= kGatherFlagSlots || epoch == 0)
+    return fail(invalid_argument("flag slot must be 0...63 and the epoch positive"));
+  if (row0 < 0 || rows <= 0 || N <= 0 || K <= 0)
+    return fail(invalid_argument("tmx_matmul_gathered needs positive extents"));
+  auto A = lookup_as<BufferObj>(a, ObjKind::Buffer, err);
+  auto B = A ? lookup_as<BufferObj>(b, ObjKind::Buffer, err) : nullptr;
+  if (!B) return fail(err);
+  GemmGather g{};
+  std::vector<std::shared_ptr<BufferObj>> keep;
+  for (int r = 0; r < world; ++r) {
+    auto c = lookup_as<BufferObj>(c_replicas[r], ObjKind::Buffer, err);
+    auto f = c ? lookup_as<BufferObj>(flag_buffers[r], ObjKind::Buffer, err) : nullptr;
+    if (!f) return fail(err);
+    if (!c->device_only || !f->device_only)
+      return fail(invalid_argument("copies of C and flag arrays must be plain device memory"));
+    if (!check_int32(row0 + rows, "row0 + rows", err) || !check_int32(N, "N", err) || !check_int32(K, "K", err) ||
+        !check_extent(*c, {{row0 + rows, N}, {N, 1}}, 2, "a copy of C", err))
+      return fail(err);
+    if (f->length < tmx_gather_flag_bytes())
+      return fail(invalid_argument("a flag array is smaller than tmx_gather_flag_bytes()"));
+    g.replica[r] = c->ptr;
+    g.flags[r] = (uint32_t*)f->ptr;
+    keep.push_back(c);
+    keep.push_back(f);
+  }
+  if (!check_extent(*A, {{rows, K}, {K, 1}}, 2, "A", err) || !check_extent(*B, {{K, N}, {N, 1}}, 2, "B", err))
+    return fail(err);
+  if (!bind_device(err)) return fail(err);
+  {
+    const std::string& why = unusable_reason();
+    if (!why.empty()) return fail(cuda_error(why));
+  }
+  if (!g_dev.gather_counter) {
+    cudaError_t e = cudaMalloc((void**)&g_dev.gather_counter, sizeof(unsigned int));
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(cuda_error(std::string("cudaMalloc: ") + cudaGetErrorString(e))); }
+    cudaMemsetAsync(g_dev.gather_counter, 0, sizeof(unsigned int), g_dev.stream);
+  }
+  GemmProblem p{};
+  p.elt = k->desc.elt;
+  p.a = A->ptr;
+  p.b = B->ptr;
+  p.c = (char*)g.replica[rank] + (size_t)row0 * (size_t)N * 2;
+  p.M = rows; p.N = N; p.K = K;
+  p.sam = K; p.sak = 1; p.sbk = N; p.sbn = 1; p.scm = N; p.scn = 1;
+  std::string why;
+  if (!gemm_tc_eligible(p, &why))
+    return fail(invalid_argument("this problem cannot take the tcgen05 kernel: " + why));
+  g.finished = g_dev.gather_counter;
+  g.world = world; g.rank = rank; g.slot = slot; g.epoch = epoch;
+  g.wait_for_peers = wait_for_peers;
+  g.wait_budget_cycles = 0;
+  if (const char* env = std::getenv("TMCUDA_GATHER_WAIT_CYCLES")) g.wait_budget_cycles = std::atoll(env);
+  std::string e = launch_gemm_tc_gathered(p, g, launch_ctx());
+  if (!e.empty()) return fail(cuda_error(e));
+  k->last_path = 2;
+  return 0;
+}
+
 // ---- failure-path aids ------------------------------------------------------
 
 // Runs the bounded-wait self-test kernel (csrc/selftest.cu) with the given cycle budget and
@@ -1177,6 +1307,32 @@ int32_t tmx_selftest_bounded_wait(int64_t budget_cycles, int32_t* results) {
   results[0] = got[0];
   results[1] = got[1];
   return 0;
+}
+
+// The work lists the persistent attention kernels would walk for a problem shape, for
+// inspection: kind 0 forward (256-row query blocks), 1 dq, 2 dkdv (128-row tiles).  Writes up
+// to `capacity` (batch-head, block) pairs into items_out, ctas + 1 offsets into begin_out and
+// the modelled cost of each CTA into load_out (any of them may be NULL); returns the number of
+// items, or -1.  Needs no device.
+int64_t tmx_debug_attention_schedule(int32_t kind, int32_t bh, int32_t rows, int32_t n_ctx, int32_t causal,
+                                     int32_t ctas, int32_t* items_out, int64_t capacity, int32_t* begin_out,
+                                     int64_t* load_out) {
+  if (kind < 0 || kind > 2 || bh <= 0 || rows <= 0 || n_ctx <= 0 || ctas <= 0) {
+    store_error(invalid_argument("tmx_debug_attention_schedule needs kind 0...2 and positive extents"));
+    return -1;
+  }
+  const AttnWorkList list = kind == 0 ? schedule_attn_fwd(bh, rows, n_ctx, causal != 0, ctas)
+                                      : schedule_attn_bwd(bh, rows, n_ctx, causal != 0, kind == 1, ctas);
+  const int64_t n = (int64_t)list.items.size();
+  if (items_out) {
+    for (int64_t i = 0; i < n && i < capacity; ++i) {
+      items_out[2 * i] = list.items[i].bh;
+      items_out[2 * i + 1] = list.items[i].block;
+    }
+  }
+  if (begin_out) std::copy(list.begin.begin(), list.begin.end(), begin_out);
+  if (load_out) std::copy(list.load.begin(), list.load.end(), load_out);
+  return n;
 }
 
 // Writes a device status record from the host, as if a kernel's bounded wait had given up.

@@ -150,6 +150,22 @@ std::string launch_attn_bwd_dkdv_simt(const AttnProblem& p, const LaunchCtx& ctx
 // tcgen05 paths: `eligible` says whether the shape can take the path.
 bool gemm_tc_eligible(const GemmProblem& p, std::string* why);
 std::string launch_gemm_tc(const GemmProblem& p, const LaunchCtx& ctx);
+// Row-sharded GEMM whose epilogue replicates C: every rank's copy of the whole C (device
+// pointers: this rank's own memory at [rank], peer-mapped memory elsewhere), one flag array
+// per rank (FLAG_SLOTS x 8 words; word slot*8 + s is raised by rank s), a counter in this
+// rank's memory.
+constexpr int kGatherMaxRanks = 8;
+constexpr int kGatherFlagSlots = 64;
+struct GemmGather {
+  void* replica[kGatherMaxRanks];
+  uint32_t* flags[kGatherMaxRanks];
+  unsigned int* finished;
+  int world, rank, slot;
+  uint32_t epoch;
+  int wait_for_peers;
+  long long wait_budget_cycles;   // 0: the library's default (about a second)
+};
+std::string launch_gemm_tc_gathered(const GemmProblem& p, const GemmGather& g, const LaunchCtx& ctx);
 // fp32 operands: 3xTF32 on the tensor cores, operands split into scratch memory.
 bool gemm_tf32_eligible(const GemmProblem& p, std::string* why);
 std::string launch_gemm_tf32(const GemmProblem& p, const LaunchCtx& ctx);           // library workspace

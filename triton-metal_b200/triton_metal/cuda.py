@@ -34,6 +34,12 @@ EXPORTS = {
     "tmx_matmul_f32_static_capacity": (_I64, ()),
     "tmx_matmul_f32_static_prepare": (_I32, ()),
     "tmx_device_memory": (_I32, (_I64P, _I64P)),
+    "tmx_ipc_export": (_I32, (_I64, _PTR)),
+    "tmx_ipc_import": (_I64, (_PTR, _I64)),
+    "tmx_gather_flag_bytes": (_I64, ()),
+    "tmx_matmul_gathered": (_I32, (_I64, _I64, _I64, _I64P, _I64P, _I32, _I32, _I64, _I64, _I64, _I64, _I32,
+                                   ctypes.c_uint32, _I32)),
+    "tmx_debug_attention_schedule": (_I64, (_I32, _I32, _I32, _I32, _I32, _I32, _I32P, _I64, _I32P, _I64P)),
     "tmx_selftest_bounded_wait": (_I32, (_I64, _I32P)),
     "tmx_debug_inject_status": (_I32, (_I32, _I32, _I32, _I32)),
 }
@@ -170,3 +176,46 @@ def device_memory():
     free, total = ctypes.c_int64(0), ctypes.c_int64(0)
     _ok(_lib.tmx_device_memory(ctypes.byref(free), ctypes.byref(total)))
     return free.value, total.value
+
+
+def ipc_export(handle: int) -> bytes:
+    """The 64-byte token with which another process maps this device buffer."""
+    token = ctypes.create_string_buffer(64)
+    _ok(_lib.tmx_ipc_export(handle, token))
+    return token.raw
+
+
+def ipc_import(token: bytes, nbytes: int) -> int:
+    handle = _lib.tmx_ipc_import(bytes(token), nbytes)
+    if handle == 0:
+        raise RuntimeError(_core.last_error())
+    return handle
+
+
+def gather_flag_bytes() -> int:
+    return _lib.tmx_gather_flag_bytes()
+
+
+def matmul_gathered(kernel, a, b, replicas, flags, rank, row0, rows, N, K, slot, epoch, wait=True) -> None:
+    world = len(replicas)
+    c_arr = (ctypes.c_int64 * world)(*replicas)
+    f_arr = (ctypes.c_int64 * world)(*flags)
+    _ok(_lib.tmx_matmul_gathered(kernel, a, b, c_arr, f_arr, world, rank, row0, rows, N, K, slot, epoch,
+                                 1 if wait else 0))
+
+
+def attention_schedule(kind: str, bh: int, rows: int, n_ctx: int, causal: bool, ctas: int):
+    """The per-CTA work lists of a persistent attention kernel: (lists, loads) where lists[c] is
+    CTA c's sequence of (batch-head, block) pairs and loads[c] its modelled cost."""
+    code = {"fwd": 0, "dq": 1, "dkdv": 2}[kind]
+    block_rows = 256 if code == 0 else 128
+    capacity = bh * ((rows + block_rows - 1) // block_rows)
+    items = (ctypes.c_int32 * (2 * capacity))()
+    begin = (ctypes.c_int32 * (ctas + 1))()
+    load = (ctypes.c_int64 * ctas)()
+    n = _lib.tmx_debug_attention_schedule(code, bh, rows, n_ctx, int(causal), ctas, items, capacity, begin, load)
+    if n < 0:
+        raise RuntimeError(_core.last_error())
+    used = min(ctas, n)
+    lists = [[(items[2 * i], items[2 * i + 1]) for i in range(begin[c], begin[c + 1])] for c in range(used)]
+    return lists, list(load)[:used]
