@@ -1,9 +1,11 @@
 """The per-CTA work lists of the persistent attention kernels (csrc/attn_schedule.h), on the host.
 
-Every item is dealt out exactly once; the CTAs' modelled loads differ by less than one item;
-a CTA's list follows the global (batch, head)-major order, so CTAs that run side by side are
-on the same few heads; and a shard of a job spread over eight GPUs - 16 (batch, head) slices,
-about as many items as SMs - still keeps every SM busy."""
+Two schedules are built for every shape - equal-cost units dealt in rounds, and list scheduling
+onto the least-loaded CTA - and the one that finishes earlier by the cost model is used, rounds
+winning near-ties.  Every item is dealt out exactly once; a CTA's modelled load is what its
+items add up to; the whole job on one GPU goes in rounds (long block paired with short one); a
+shard of a job spread over eight GPUs - 16 (batch, head) slices, about as many items as SMs -
+goes by the list and still keeps every SM busy."""
 
 import numpy as np
 import pytest
@@ -40,13 +42,31 @@ def test_every_item_once_and_loads_level(kind, bh, rows, n_ctx, causal):
     assert len(lists) == min(ctas, bh * blocks) and all(lists)
     overhead = 3 if kind == "fwd" else 2
     costs = [cost_of(kind, b, n_ctx, causal) + overhead for b in range(blocks)]
-    # the model's loads are what the items add up to, and no CTA is more than one item behind
+    # the model's loads are what the items add up to
     for lst, load in zip(lists, loads):
         assert load == sum(costs[b] for _, b in lst)
+    # either the rounds (unit u = long block k + short block n-1-k of a head, to CTA u mod ctas) ...
+    varying = costs[0] != costs[-1]
+    units = (blocks + 1) // 2 if varying else blocks
+    long_last = costs[-1] > costs[0]
+    rounds = [[] for _ in lists]
+    u = 0
+    for h in range(bh):
+        for k in range(units):
+            far = blocks - 1 - k
+            pair = [k] if not varying else ([far, k] if long_last else [k, far])
+            if len(pair) == 2 and pair[0] == pair[1]:
+                pair = pair[:1]
+            rounds[u % len(lists)] += [(h, b) for b in pair]
+            u += 1
+    if lists == rounds:
+        return
+    # ... or the list: no CTA more than one item behind, and every CTA meets its items in dispatch
+    # order - head-major with the long blocks of a head first before the tail (the last whole heads
+    # holding at most three items per CTA), by decreasing cost inside it
+    round_loads = [sum(costs[b] for _, b in lst) for lst in rounds]
+    assert max(round_loads) * 100 > max(loads) * 105          # the list was taken because it is shorter
     assert max(loads) - min(loads) <= max(costs)
-    # a CTA meets its items in dispatch order.  Before the tail (the last whole heads holding at
-    # most three items per CTA, dealt longest first whatever their head) that is head-major with
-    # the long blocks of a head first; inside the tail, by decreasing cost.
     tail_heads = max(1, min(bh, (3 * len(lists)) // blocks))
     for lst in lists:
         body = [(h, b) for h, b in lst if h < bh - tail_heads]

@@ -151,31 +151,49 @@ template <typename T, bool MASKED>
 __device__ __forceinline__ void ds_part(uint32_t s_tmem, const uint32_t (&s)[32], const uint32_t (&d)[32],
                                         float qk_scale, float neg_lse, float delta, const KeyMask& km) {
   uint32_t packed[16];
+  if (!MASKED) {
+    // two elements per instruction wherever the hardware has one (fma / add / mul on register
+    // pairs): per element half an fma, the exponential, half an add, half a mul, half a conversion
+    const uint64_t scale2 = pack_f32x2(qk_scale, qk_scale), neg_lse2 = pack_f32x2(neg_lse, neg_lse);
+    const uint64_t neg_delta2 = pack_f32x2(-delta, -delta);
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float x0, x1, r0, r1;
+      unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), scale2, neg_lse2), x0, x1);
+      const uint64_t p2 = pack_f32x2(fast_exp2(x0), fast_exp2(x1));
+      const uint64_t t2 = add_f32x2(pack_f32x2(__uint_as_float(d[i]), __uint_as_float(d[i + 1])), neg_delta2);
+      unpack_f32x2(mul_f32x2(p2, t2), r0, r1);
+      packed[i / 2] = pack2<T>(r0, r1);
+    }
+    tmem_st_32x16(s_tmem, packed);
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
     float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, neg_lse));
     float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_lse));
-    if (MASKED) {
-      if (km.masked(i)) p0 = 0.f;
-      if (km.masked(i + 1)) p1 = 0.f;
-    }
+    if (km.masked(i)) p0 = 0.f;
+    if (km.masked(i + 1)) p1 = 0.f;
     packed[i / 2] = pack2<T>(p0 * (__uint_as_float(d[i]) - delta), p1 * (__uint_as_float(d[i + 1]) - delta));
   }
   tmem_st_32x16(s_tmem, packed);
 }
 
 // dkdv pass A: P^T = exp2(S^T*qk_scale - L[query]) from the register copy `s` of the group's
-// 32 columns, rounded and packed (16 words).  `k_minus_q0` > column means key row > query: masked.
+// 32 columns, rounded and packed (16 words).  `neg_lse_s` holds -L of the 32 queries (the sign is
+// flipped once when the statistics are staged, so that the scaling is one two-wide fma per pair).
+// `k_minus_q0` > column means key row > query: masked.
 template <typename T, bool DIAG>
-__device__ __forceinline__ void pt_part(const uint32_t (&s)[32], float qk_scale, const float* lse_s,
+__device__ __forceinline__ void pt_part(const uint32_t (&s)[32], float qk_scale, const float* neg_lse_s,
                                         int k_minus_q0, uint32_t (&keep)[16]) {
+  const uint64_t scale2 = pack_f32x2(qk_scale, qk_scale);
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
-    const float4 l = *reinterpret_cast<const float4*>(lse_s + i);
-    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, -l.x));
-    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, -l.y));
-    float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), qk_scale, -l.z));
-    float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), qk_scale, -l.w));
+    const float4 nl = *reinterpret_cast<const float4*>(neg_lse_s + i);
+    float x0, x1, x2, x3;
+    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), scale2, pack_f32x2(nl.x, nl.y)), x0, x1);
+    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), scale2, pack_f32x2(nl.z, nl.w)), x2, x3);
+    float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
     if (DIAG) {
       if (k_minus_q0 > i) p0 = 0.f;
       if (k_minus_q0 > i + 1) p1 = 0.f;
@@ -187,24 +205,29 @@ __device__ __forceinline__ void pt_part(const uint32_t (&s)[32], float qk_scale,
   }
 }
 
-// dkdv pass B: dS^T = P^T * (dP^T - Delta[query]) from the register copy of P^T.
+// dkdv pass B: dS^T = P^T * (dP^T - Delta[query]) from the register copy of P^T; `neg_delta_s`
+// holds -Delta of the 32 queries.
 template <typename T>
-__device__ __forceinline__ void dst_part(uint32_t dpt_tmem, const float* delta_s, const uint32_t (&keep)[16]) {
-  float4 dv[8];
+__device__ __forceinline__ void dst_part(uint32_t dpt_tmem, const float* neg_delta_s, const uint32_t (&keep)[16]) {
+  float4 nd[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) dv[i] = *reinterpret_cast<const float4*>(delta_s + i * 4);
+  for (int i = 0; i < 8; ++i) nd[i] = *reinterpret_cast<const float4*>(neg_delta_s + i * 4);
   uint32_t d[32];
   tmem_ld_32x32(dpt_tmem, d);
   tmem_ld_wait();
   uint32_t packed[16];
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
-    const float4 dl = dv[i / 4];
-    float p0, p1, p2, p3;
+    const float4 dl = nd[i / 4];
+    float p0, p1, p2, p3, r0, r1, r2, r3;
     unpack2<T>(keep[i / 2], p0, p1);
     unpack2<T>(keep[i / 2 + 1], p2, p3);
-    packed[i / 2] = pack2<T>(p0 * (__uint_as_float(d[i]) - dl.x), p1 * (__uint_as_float(d[i + 1]) - dl.y));
-    packed[i / 2 + 1] = pack2<T>(p2 * (__uint_as_float(d[i + 2]) - dl.z), p3 * (__uint_as_float(d[i + 3]) - dl.w));
+    const uint64_t ta = add_f32x2(pack_f32x2(__uint_as_float(d[i]), __uint_as_float(d[i + 1])), pack_f32x2(dl.x, dl.y));
+    const uint64_t tb = add_f32x2(pack_f32x2(__uint_as_float(d[i + 2]), __uint_as_float(d[i + 3])), pack_f32x2(dl.z, dl.w));
+    unpack_f32x2(mul_f32x2(pack_f32x2(p0, p1), ta), r0, r1);
+    unpack_f32x2(mul_f32x2(pack_f32x2(p2, p3), tb), r2, r3);
+    packed[i / 2] = pack2<T>(r0, r1);
+    packed[i / 2 + 1] = pack2<T>(r2, r3);
   }
   tmem_st_32x16(dpt_tmem, packed);
 }
@@ -742,7 +765,8 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         // needs 32 of each): the threads of group 0 fetch the 128 values of L, those of group 1
         // the 128 values of Delta.  The global load for block t+1 is issued at the top of
         // iteration t into a register and stored to shared memory at its end, so its latency is
-        // off the critical path.  +inf as L makes exp2(x - L) vanish for queries past the end.
+        // off the critical path.  Both are staged negated (the passes add them); -inf as -L makes
+        // exp2(x - L) vanish for queries past the end.
         auto fetch_stat = [&](int t) -> float {
           const int q = (first + t) * BLK + row_in_tile;
           float v = group ? 0.f : INFINITY;
@@ -750,7 +774,7 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const float* src = (group ? delta_base : lse_base) + q;
             asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(src));
           }
-          return v;
+          return -v;           // the passes add: -L and -Delta are staged
         };
         auto put_stat = [&](uint32_t slot, float v) {
           if (group == 1) ss.delta[slot & 1][row_in_tile] = v;

@@ -108,11 +108,16 @@ template <bool MASKED>
 __device__ __forceinline__ float max_chunk(const uint32_t (&r)[32], int col0, const MaskInfo& mi) {
   float m0 = -INFINITY, m1 = -INFINITY;
   if (!MASKED) {
+    // four independent chains of three-input maxima (the four chunks of a row make sixteen)
+    float m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {
+    for (int i = 0; i < 32; i += 8) {
       m0 = max3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
       m1 = max3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+      m2 = max3(m2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+      m3 = max3(m3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
     }
+    return max3(m0, m1, fmaxf(m2, m3));
   } else {
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
@@ -165,6 +170,80 @@ __device__ __forceinline__ float exp_chunk(const uint32_t (&r)[32], uint32_t dst
   }
   tmem_st_32x16(dst, packed);
   return s0 + s1;
+}
+
+// ---- the plain score block, scheduled by hand -----------------------------------------
+// A softmax warp is alone on its scheduler while it works (the other tile's warp waits for its
+// scores), it issues in order, and every exponential costs the special-function unit 8 cycles:
+// the exponentials of a row take 1024 cycles at best, and they only do if an ex2 is issued
+// every 8 cycles with the scaling of later elements and the sum / rounding of earlier ones
+// filling the slots in between.  Left to the compiler the pass took about 1800 cycles (the
+// dependent instructions of one element end up back to back and wait for each other), so the
+// order is fixed here: every statement is a volatile asm, which the compiler keeps in sequence.
+// Values are transformed in place (score -> scaled score -> probability).
+__device__ __forceinline__ void scale_pair(uint32_t& a, uint32_t& b, uint64_t scale2, uint64_t neg_m2) {
+  asm volatile(
+      "{\n.reg .b64 t;\nmov.b64 t, {%0, %1};\nfma.rn.f32x2 t, t, %2, %3;\nmov.b64 {%0, %1}, t;\n}"
+      : "+r"(a), "+r"(b)
+      : "l"(scale2), "l"(neg_m2));
+}
+__device__ __forceinline__ void exp2_inplace(uint32_t& a) {
+  asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+r"(a));
+}
+__device__ __forceinline__ void sum_pair(uint64_t& acc, uint32_t a, uint32_t b) {
+  asm volatile("{\n.reg .b64 t;\nmov.b64 t, {%1, %2};\nadd.rn.f32x2 %0, %0, t;\n}" : "+l"(acc) : "r"(a), "r"(b));
+}
+template <typename T> __device__ __forceinline__ uint32_t round_pair(uint32_t lo, uint32_t hi);
+template <> __device__ __forceinline__ uint32_t round_pair<__nv_bfloat16>(uint32_t lo, uint32_t hi) {
+  uint32_t d;
+  asm volatile("cvt.rn.bf16x2.f32 %0, %2, %1;" : "=r"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+template <> __device__ __forceinline__ uint32_t round_pair<__half>(uint32_t lo, uint32_t hi) {
+  uint32_t d;
+  asm volatile("cvt.rn.f16x2.f32 %0, %2, %1;" : "=r"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
+// P = exp2(s * qk_scale + neg_m) over a whole row (four 32-column chunks), rounded and written
+// to `dst` (64 packed columns); returns the fp32 row sum.  LAG pairs separate an ex2 from the
+// instructions that consume its result.
+template <typename T>
+__device__ __forceinline__ float exp_row_plain(uint32_t (&s0)[32], uint32_t (&s1)[32], uint32_t (&s2)[32],
+                                               uint32_t (&s3)[32], uint32_t dst, float qk_scale, float neg_m) {
+  constexpr int LAG = 4;
+  const uint64_t scale2 = pack_f32x2(qk_scale, qk_scale), neg_m2 = pack_f32x2(neg_m, neg_m);
+  uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
+  uint32_t packed[64];
+  auto elem = [&](int i) -> uint32_t& {          // element i of the row, 0 ... 127
+    return i < 32 ? s0[i] : (i < 64 ? s1[i - 32] : (i < 96 ? s2[i - 64] : s3[i - 96]));
+  };
+  // scale the first LAG + 2 pairs ahead of the exponentials
+#pragma unroll
+  for (int q = 0; q < LAG + 2; ++q) scale_pair(elem(2 * q), elem(2 * q + 1), scale2, neg_m2);
+#pragma unroll
+  for (int q = 0; q < 64 + LAG; ++q) {
+    if (q < 64) {
+      exp2_inplace(elem(2 * q));
+      if (q + LAG + 2 < 64) scale_pair(elem(2 * (q + LAG + 2)), elem(2 * (q + LAG + 2) + 1), scale2, neg_m2);
+      exp2_inplace(elem(2 * q + 1));
+    }
+    if (q >= LAG) {
+      const int d = q - LAG;                       // the pair whose exponentials have had time to finish
+      if (d & 1) sum_pair(acc1, elem(2 * d), elem(2 * d + 1));
+      else sum_pair(acc0, elem(2 * d), elem(2 * d + 1));
+      packed[d] = round_pair<T>(elem(2 * d), elem(2 * d + 1));
+      if (d % 16 == 15) {                           // a chunk of P is complete: store it
+        uint32_t out[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) out[k] = packed[d - 15 + k];
+        tmem_st_32x16(dst + (d / 16) * 16, out);
+      }
+    }
+  }
+  float a, b;
+  unpack_f32x2(add_f32x2(acc0, acc1), a, b);
+  return a + b;
 }
 
 // The chunk of a diagonal block that the diagonal itself crosses: row `lane` of the warp keeps
@@ -512,10 +591,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (wchunk >= 3) sum += exp_chunk_diag<T>(s3, s_tmem + 48, qk_scale, neg_m, lane);
             else zero_chunk(s_tmem + 48);
           } else {
-            sum = exp_chunk<T, false>(s0, s_tmem, qk_scale, neg_m, 0, mi) +
-                  exp_chunk<T, false>(s1, s_tmem + 16, qk_scale, neg_m, 32, mi);
-            sum += exp_chunk<T, false>(s2, s_tmem + 32, qk_scale, neg_m, 64, mi) +
-                   exp_chunk<T, false>(s3, s_tmem + 48, qk_scale, neg_m, 96, mi);
+            sum = exp_row_plain<T>(s0, s1, s2, s3, s_tmem, qk_scale, neg_m);
           }
           l = l * alpha + sum;
           tmem_st_wait();
