@@ -165,16 +165,15 @@ __device__ __forceinline__ void ds_part(uint32_t s_tmem, const uint32_t (&s)[32]
       unpack_f32x2(mul_f32x2(p2, t2), r0, r1);
       packed[i / 2] = pack2<T>(r0, r1);
     }
-    tmem_st_32x16(s_tmem, packed);
-    return;
-  }
+  } else {
 #pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, neg_lse));
-    float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_lse));
-    if (km.masked(i)) p0 = 0.f;
-    if (km.masked(i + 1)) p1 = 0.f;
-    packed[i / 2] = pack2<T>(p0 * (__uint_as_float(d[i]) - delta), p1 * (__uint_as_float(d[i + 1]) - delta));
+    for (int i = 0; i < 32; i += 2) {
+      float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), qk_scale, neg_lse));
+      float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), qk_scale, neg_lse));
+      if (km.masked(i)) p0 = 0.f;
+      if (km.masked(i + 1)) p1 = 0.f;
+      packed[i / 2] = pack2<T>(p0 * (__uint_as_float(d[i]) - delta), p1 * (__uint_as_float(d[i + 1]) - delta));
+    }
   }
   tmem_st_32x16(s_tmem, packed);
 }
@@ -358,11 +357,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ++v_issued;
         return true;
       };
-      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
       {
-        for (int it = first_item; it < end_item && ok; ++it, ++item) {
-          const int bh = __ldg(&work.items[it].bh);
-          const int m0 = __ldg(&work.items[it].block) * BLK;
+        for (WorkCursor w(work); w.valid() && ok; w.advance(), ++item) {
+          const int bh = w.cur.x;
+          const int m0 = w.cur.y * BLK;
           const int n_blocks = key_blocks(m0);
           // Q and dO are single-buffered: the previous tile's last S and dP must have retired
           if (!mbar_wait(smem_u32(&ss.qdo_empty), (item & 1) ^ 1, wc, 30)) { ok = false; break; }
@@ -439,10 +437,9 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ++c;
         if (++ks == K_STAGES) ks = 0;
       };
-      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
       {
-        for (int it = first_item; it < end_item; ++it, ++item) {
-          const int n_blocks = key_blocks(__ldg(&work.items[it].block) * BLK);
+        for (WorkCursor w(work); w.valid(); w.advance(), ++item) {
+          const int n_blocks = key_blocks(w.cur.y * BLK);
           // The first S and dP of this tile go out while the element-wise warps may still be
           // storing the previous dQ: they use other TMEM columns, and the first dQ MMA waits
           // for ds_full, which those warps only signal after that store.
@@ -468,11 +465,10 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const float qk_scale = prm.sm_scale * kLog2e;
     uint32_t item = 0, c = 0;
     bool ok = true;
-    const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
     {
-      for (int it = first_item; it < end_item && ok; ++it, ++item) {
-        const int bh = __ldg(&work.items[it].bh);
-        const int m0 = __ldg(&work.items[it].block) * BLK;
+      for (WorkCursor w(work); w.valid() && ok; w.advance(), ++item) {
+        const int bh = w.cur.x;
+        const int m0 = w.cur.y * BLK;
         const int n_blocks = key_blocks(m0);
         const int q_row = m0 + row_in_tile;
         float lse = 0.f, delta = 0.f;
@@ -528,9 +524,20 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 // ===========================================================================
 // dK, dV
 // ===========================================================================
+constexpr int MAX_RING = 4;
+// Stages of the Q and dO rings of dkdv.  At D = 128 shared memory is full (K, V, four streamed
+// tiles and the P^T tile take 224 KiB): two stages each.  A Q tile is held from the scores of
+// its block to the dK of that block, two blocks later, so the refill of the slot that dK(t-1)
+// frees (about 1300 cycles for 32 KiB) sits in front of S^T(t+1) in every block - the issuing
+// warp spends 1280 of a block's 3100 cycles waiting for it (timestamps taken inside the
+// kernel).  Splitting the four tiles 3 + 1 moves the wait to dO (measured: 3400 cycles a
+// block); a fifth tile does not fit.  At D = 64 there is room for four stages of each.
+template <int D> __host__ __device__ constexpr int q_stages() { return D == 64 ? 4 : 2; }
+template <int D> __host__ __device__ constexpr int do_stages() { return D == 64 ? 4 : 2; }
+
 struct SharedDkdv {
   alignas(8) uint64_t kv_full, kv_empty;
-  alignas(8) uint64_t q_full[2][2], q_empty[2], do_full[2], do_empty[2];   // q_full[stage][64-column half]
+  alignas(8) uint64_t q_full[MAX_RING][2], q_empty[MAX_RING], do_full[MAX_RING], do_empty[MAX_RING];   // q_full[stage][64-column half]
   alignas(8) uint64_t st_full, s_read, p_full, dpt_full, ds_full, done;
   alignas(16) float lse[2][BLK];
   alignas(16) float delta[2][BLK];
@@ -560,13 +567,14 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                         Params prm, DeviceWorkList work, DeviceStatus* status) {
   constexpr int TILE = BLK * D * 2;
+  constexpr int NQ = q_stages<D>(), NDO = do_stages<D>();   // stages of the Q and dO rings
   constexpr int ST_COL = 0, DPT_COL = 128, DV_COL = 256, DK_COL = 256 + D;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
-  // layout: K | V | Q0 Q1 | dO0 dO1 | P^T | barriers and row statistics
+  // layout: K | V | Q ring | dO ring | P^T | barriers and row statistics
   const uint32_t k_addr = smem_u32(smem), v_addr = k_addr + TILE, q_addr = v_addr + TILE,
-                 do_addr = q_addr + 2 * TILE, p_addr = do_addr + 2 * TILE;
-  SharedDkdv& ss = *reinterpret_cast<SharedDkdv*>(smem + 6 * TILE + P_TILE);
+                 do_addr = q_addr + NQ * TILE, p_addr = do_addr + NDO * TILE;
+  SharedDkdv& ss = *reinterpret_cast<SharedDkdv*>(smem + (2 + NQ + NDO) * TILE + P_TILE);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   WaitCtx wc{&ss.abort_flag, status};
   const int total_q_blocks = (prm.n_ctx + BLK - 1) / BLK;
@@ -585,10 +593,12 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&ss.kv_full), 1);
     mbar_init(smem_u32(&ss.kv_empty), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NQ; ++s) {
       mbar_init(smem_u32(&ss.q_full[s][0]), 1);
       mbar_init(smem_u32(&ss.q_full[s][1]), 1);
       mbar_init(smem_u32(&ss.q_empty[s]), 1);
+    }
+    for (int s = 0; s < NDO; ++s) {
       mbar_init(smem_u32(&ss.do_full[s]), 1);
       mbar_init(smem_u32(&ss.do_empty[s]), 1);
     }
@@ -619,11 +629,10 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       uint32_t issued = 0, do_issued = 0;
       uint32_t item = 0, c = 0;          // key tiles and query blocks loaded so far
       bool ok = true;
-      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
       {
-        for (int it = first_item; it < end_item && ok; ++it, ++item) {
-          const int bh = __ldg(&work.items[it].bh);
-          const int n0 = __ldg(&work.items[it].block) * BLK;
+        for (WorkCursor w(work); w.valid() && ok; w.advance(), ++item) {
+          const int bh = w.cur.x;
+          const int n0 = w.cur.y * BLK;
           const int first = first_block(n0), n_iter = total_q_blocks - first;
           // K and V are single-buffered: the previous tile's last S^T and dP^T must have retired
           if (!mbar_wait(smem_u32(&ss.kv_empty), (item & 1) ^ 1, wc, 50)) { ok = false; break; }
@@ -631,33 +640,33 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           load_tile<D>(k_addr, &map_k, smem_u32(&ss.kv_full), n0, bh);
           load_tile<D>(v_addr, &map_v, smem_u32(&ss.kv_full), n0, bh);
           for (int t = 0; t < n_iter; ++t, ++c) {
-            const int s = c & 1;
-            const uint32_t ph = (c >> 1) & 1;
+            const int sq = c % NQ, sd = c % NDO;
+            const uint32_t phq = (c / NQ) & 1, phd = (c / NDO) & 1;
             const int row0 = (first + t) * BLK;
-            // dO(t)'s slot is freed by dV(t-2), half a block before dK(t-2) frees Q(t)'s: dO goes
-            // first, and the Q refill - 32 KB, on the critical path of S^T(t) - is not held up by it
-            if (!mbar_wait(smem_u32(&ss.do_empty[s]), ph ^ 1, wc, 52)) { ok = false; break; }
-            mbar_expect_tx(smem_u32(&ss.do_full[s]), TILE);
-            load_tile<D>(do_addr + s * TILE, &map_do, smem_u32(&ss.do_full[s]), row0, bh);
-            ++do_issued;
-            if (!mbar_wait(smem_u32(&ss.q_empty[s]), ph ^ 1, wc, 51)) { ok = false; break; }
+            // Q first: its slot was freed by dK(t - NQ), long ago, so the refill - which S^T(t) will
+            // wait for - goes out at once; the wait for dO's slot (freed by dV(t - NDO)) comes after it
+            if (!mbar_wait(smem_u32(&ss.q_empty[sq]), phq ^ 1, wc, 51)) { ok = false; break; }
             // one barrier per 64-column half: the scores start on the first half while the second
             // is still in flight
 #pragma unroll
             for (int h = 0; h < D / 64; ++h) {
-              mbar_expect_tx(smem_u32(&ss.q_full[s][h]), BLK * 128);
-              tma_load_3d(q_addr + s * TILE + h * (BLK * 128), &map_q, smem_u32(&ss.q_full[s][h]), h * 64, row0, bh);
+              mbar_expect_tx(smem_u32(&ss.q_full[sq][h]), BLK * 128);
+              tma_load_3d(q_addr + sq * TILE + h * (BLK * 128), &map_q, smem_u32(&ss.q_full[sq][h]), h * 64, row0, bh);
             }
             ++issued;
+            if (!mbar_wait(smem_u32(&ss.do_empty[sd]), phd ^ 1, wc, 52)) { ok = false; break; }
+            mbar_expect_tx(smem_u32(&ss.do_full[sd]), TILE);
+            load_tile<D>(do_addr + sd * TILE, &map_do, smem_u32(&ss.do_full[sd]), row0, bh);
+            ++do_issued;
           }
         }
       }
       // every copy started here must have landed before the CTA exits
       if (item) drain(smem_u32(&ss.kv_full), (item - 1) & 1, wc, 59);
-      for (uint32_t n = issued > 2 ? issued - 2 : 0; n < issued; ++n)
-        for (int h = 0; h < D / 64; ++h) drain(smem_u32(&ss.q_full[n & 1][h]), (n >> 1) & 1, wc, 59);
-      for (uint32_t n = do_issued > 2 ? do_issued - 2 : 0; n < do_issued; ++n)
-        drain(smem_u32(&ss.do_full[n & 1]), (n >> 1) & 1, wc, 59);
+      for (uint32_t n = issued > NQ ? issued - NQ : 0; n < issued; ++n)
+        for (int h = 0; h < D / 64; ++h) drain(smem_u32(&ss.q_full[n % NQ][h]), (n / NQ) & 1, wc, 59);
+      for (uint32_t n = do_issued > NDO ? do_issued - NDO : 0; n < do_issued; ++n)
+        drain(smem_u32(&ss.do_full[n % NDO]), (n / NDO) & 1, wc, 59);
     }
   } else if (warp == MMA_WARP) {
     // One warp issues every MMA (cost of issuing: see the head of this file): per block five
@@ -686,29 +695,30 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         mma_commit_elect(smem_u32(&ss.st_full));
       };
-      // One query block; c counts them across tiles (ring stage c & 1, phases from c).
+      // One query block; c counts them across tiles (ring stages c mod NQ / NDO, phases from c).
       // `first` = first block of its key tile, `more` = another block of this tile follows;
       // every block but a tile's last also starts the next block's S^T and dP^T.
       uint32_t item = 0, c = 0;
       auto block = [&](bool first, bool more, bool release_kv) {
-        const int s = c & 1;
+        const int sq = c % NQ, sd = c % NDO, sq_next = (c + 1) % NQ, sd_next = (c + 1) % NDO;
+        const uint32_t phq_next = ((c + 1) / NQ) & 1, phd_next = ((c + 1) / NDO) & 1;
         if (more) {
           // S^T(t) is in registers and Q(t+1) has landed: the next scores can go
           wait(&ss.s_read, c & 1, 63);
-          issue_scores(s ^ 1, ((c + 1) >> 1) & 1);
+          issue_scores(sq_next, phq_next);
         }
         wait(&ss.p_full, c & 1, 56);
         tc_fence_after();
-        mma_sn<D>(tmem + DV_COL, p_km, do_mn.advanced(s * TILE), idesc_tn, !first);
-        mma_commit_elect(smem_u32(&ss.do_empty[s]));         // last use of dO(t)
+        mma_sn<D>(tmem + DV_COL, p_km, do_mn.advanced(sd * TILE), idesc_tn, !first);
+        mma_commit_elect(smem_u32(&ss.do_empty[sd]));         // last use of dO(t)
         wait(&ss.ds_full, c & 1, 57);
         tc_fence_after();
-        mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_mn.advanced(s * TILE), idesc_tn, !first);
-        mma_commit_elect(smem_u32(&ss.q_empty[s]));          // last use of Q(t)
+        mma_tn<D>(tmem + DK_COL, tmem + DPT_COL, q_mn.advanced(sq * TILE), idesc_tn, !first);
+        mma_commit_elect(smem_u32(&ss.q_empty[sq]));          // last use of Q(t)
         if (more) {
-          wait(&ss.do_full[s ^ 1], ((c + 1) >> 1) & 1, 55);
+          wait(&ss.do_full[sd_next], phd_next, 55);
           tc_fence_after();
-          mma_nt<D>(tmem + DPT_COL, v_km, do_km.advanced((s ^ 1) * TILE), idesc_nt);
+          mma_nt<D>(tmem + DPT_COL, v_km, do_km.advanced(sd_next * TILE), idesc_nt);
           mma_commit_elect(smem_u32(&ss.dpt_full));
           // K and V are free once the tile's last S^T and dP^T (both just issued) retire
           if (release_kv) mma_commit_elect(smem_u32(&ss.kv_empty));
@@ -717,18 +727,17 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         ++c;
       };
-      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
       {
-        for (int it = first_item; it < end_item; ++it, ++item) {
-          const int n_iter = total_q_blocks - first_block(__ldg(&work.items[it].block) * BLK);
+        for (WorkCursor w(work); w.valid(); w.advance(), ++item) {
+          const int n_iter = total_q_blocks - first_block(w.cur.y * BLK);
           // The first S^T and dP^T of this tile go out while the element-wise warps may still be
           // storing the previous dK and dV: they use other TMEM columns, and the first dV and dK
           // MMAs wait for p_full / ds_full, which those warps only signal after that store.
           wait(&ss.kv_full, item & 1, 53);
-          issue_scores(c & 1, (c >> 1) & 1);
-          wait(&ss.do_full[c & 1], (c >> 1) & 1, 55);
+          issue_scores(c % NQ, (c / NQ) & 1);
+          wait(&ss.do_full[c % NDO], (c / NDO) & 1, 55);
           tc_fence_after();
-          mma_nt<D>(tmem + DPT_COL, v_km, do_km.advanced((c & 1) * TILE), idesc_nt);
+          mma_nt<D>(tmem + DPT_COL, v_km, do_km.advanced((c % NDO) * TILE), idesc_nt);
           mma_commit_elect(smem_u32(&ss.dpt_full));
           if (n_iter == 1) mma_commit_elect(smem_u32(&ss.kv_empty));
           int t = 0;
@@ -752,13 +761,12 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t p_chunk0 = (group % 2) * 4, p_xor = row_in_tile & 7;
     uint32_t item = 0, c = 0;
     bool ok = true;
-    const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
     {
-      for (int it = first_item; it < end_item && ok; ++it, ++item) {
-        const int bh = __ldg(&work.items[it].bh);
+      for (WorkCursor w(work); w.valid() && ok; w.advance(), ++item) {
+        const int bh = w.cur.x;
         const float* lse_base = prm.lse + (int64_t)bh * prm.stride_lse;
         const float* delta_base = prm.delta + (int64_t)bh * prm.stride_lse;
-        const int n0 = __ldg(&work.items[it].block) * BLK;
+        const int n0 = w.cur.y * BLK;
         const int first = first_block(n0), n_iter = total_q_blocks - first;
         const int k_row = n0 + row_in_tile;
         // Row statistics of the streamed query block go through shared memory (every thread
@@ -891,7 +899,7 @@ std::string launch_typed(const AttnProblem& p, const LaunchCtx& ctx, CUtensorMap
   // never less than 120 KiB so two CTAs (each wanting all of TMEM) do not share an SM
   // dkdv: six operand tiles and the P^T tile, on a 1024-byte aligned base (no slack: 227 KiB
   // is the limit at D = 128); dq: its tiles plus slack for rounding the base up
-  size_t smem = dkdv ? 6 * (size_t)(BLK * D * 2) + P_TILE + sizeof(SharedDkdv)
+  size_t smem = dkdv ? (2 + q_stages<D>() + do_stages<D>()) * (size_t)(BLK * D * 2) + P_TILE + sizeof(SharedDkdv)
                      : (2 + K_STAGES + V_STAGES) * (size_t)(BLK * D * 2) + sizeof(SharedDq) + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;
   cudaError_t e;

@@ -350,11 +350,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tma_prefetch_desc(&map_v);
       uint32_t item = 0, g = 0, q_loads = 0, k_loads = 0, v_loads = 0;
       bool ok = true;
-      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
       {
-        for (int it = first_item; it < end_item && ok; ++it, ++item) {
-          const int bh = __ldg(&work.items[it].bh);
-          const int m0 = __ldg(&work.items[it].block) * (TILES * BLOCK_M);
+        for (WorkCursor w(work); w.valid() && ok; w.advance(), ++item) {
+          const int bh = w.cur.x;
+          const int m0 = w.cur.y * (TILES * BLOCK_M);
           const int nb_max = key_blocks(m0, TILES - 1);
           // Q is single-buffered: the previous block's last score MMA must have retired
           if (!mbar_wait(smem_u32(&ss.q_empty), (item & 1) ^ 1, wc, kLoadQEmpty)) { ok = false; break; }
@@ -419,10 +418,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       };
       uint32_t item = 0, g = 0, c[TILES] = {0, 0};
       bool ok = true;
-      const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
       {
-        for (int it = first_item; it < end_item && ok; ++it, ++item) {
-          const int m0 = __ldg(&work.items[it].block) * (TILES * BLOCK_M);
+        for (WorkCursor w(work); w.valid() && ok; w.advance(), ++item) {
+          const int m0 = w.cur.y * (TILES * BLOCK_M);
           int nb[TILES];
 #pragma unroll
           for (int t = 0; t < TILES; ++t) nb[t] = key_blocks(m0, t);
@@ -502,11 +500,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint32_t c = 0;                               // score blocks this tile has consumed
     uint32_t item = 0;                            // query blocks done (phase of pv_done)
     bool ok = true;
-    const int first_item = __ldg(work.begin + blockIdx.x), end_item = __ldg(work.begin + blockIdx.x + 1);
     {
-      for (int it = first_item; it < end_item && ok; ++it, ++item) {
-        const int bh = __ldg(&work.items[it].bh);
-        const int m0 = __ldg(&work.items[it].block) * (TILES * BLOCK_M);
+      for (WorkCursor w(work); w.valid() && ok; w.advance(), ++item) {
+        const int bh = w.cur.x;
+        const int m0 = w.cur.y * (TILES * BLOCK_M);
         const int q_row = m0 + t * BLOCK_M + row_in_tile;
         const int my_blocks = key_blocks(m0, t);
         float m_used = -INFINITY, l = 0.f;

@@ -161,6 +161,31 @@ struct DeviceWorkList {
   int ctas = 0;
 };
 
+#ifdef __CUDACC__
+// A CTA's walk over its list, with the next item fetched one item ahead: the fetch is a
+// dependent global load of several hundred cycles, and every role of the kernel would otherwise
+// wait for it at the top of each item - the loading warp before it can ask for the item's first
+// tiles, the issuing warp before its first MMA.
+struct WorkCursor {
+  const int2* items;
+  int it, end;
+  int2 cur, nxt;      // (batch-head, block) of item `it` and of item `it + 1`
+  __device__ __forceinline__ explicit WorkCursor(const DeviceWorkList& w)
+      : items(reinterpret_cast<const int2*>(w.items)) {
+    it = __ldg(w.begin + blockIdx.x);
+    end = __ldg(w.begin + blockIdx.x + 1);
+    cur = it < end ? __ldg(items + it) : make_int2(0, 0);
+    nxt = it + 1 < end ? __ldg(items + it + 1) : cur;
+  }
+  __device__ __forceinline__ bool valid() const { return it < end; }
+  __device__ __forceinline__ void advance() {
+    ++it;
+    cur = nxt;
+    if (it + 1 < end) nxt = __ldg(items + it + 1);
+  }
+};
+#endif
+
 // Work lists already uploaded, by problem shape: a list depends only on (kind, slices, rows,
 // n_ctx, mask, CTAs), so a training loop or a benchmark builds and uploads it once.  A few
 // entries are kept per device context; the oldest is dropped (after the stream has drained)
