@@ -53,6 +53,53 @@ def test_16bit_shapes(element, bh, seq, d, causal):
     check_all(q, k, v, do, element, causal, block=(32, 32))
 
 
+@pytest.mark.parametrize("bh,seq,d,causal,path", [
+    (2, 1024, 64, False, cuda.PATH_AUTO), (2, 1024, 64, True, cuda.PATH_AUTO), (1, 2048, 128, True, cuda.PATH_AUTO),
+    (2, 1000, 64, True, cuda.PATH_TCGEN05), (3, 300, 80, False, cuda.PATH_TCGEN05),
+])
+def test_fp32_long_sequences_run_on_the_tensor_cores(bh, seq, d, causal, path):
+    """fp32 attention from 1024 rows on (from 256 when the tensor-core path is asked for): every
+    contraction of the three kernels as a 3xTF32 GEMM over a materialised score matrix, the
+    softmax and dS products as row-wise fp32 kernels.  Same bound as the exact-FMA kernels -
+    1e-5 with the reference's relative_error - and agreement with them."""
+    q, k, v, do = inputs.attention_normal(bh, seq, d, seed=seq + d)
+    paths = check_all(q, k, v, do, "f32", causal, block=(16, 32), path=path)
+    assert [paths[n] for n in ("fwd", "dq", "dkdv")] == [cuda.PATH_TCGEN05] * 3
+    with tmtest.AttentionRun(q, k, v, do, "f32", causal, (16, 32), cuda.PATH_SIMT) as run:
+        o_simt, lse_simt = run.forward()
+        grads_simt = run.backward()
+    with tmtest.AttentionRun(q, k, v, do, "f32", causal, (16, 32), path) as run:
+        o_tc, lse_tc = run.forward()
+        grads_tc = run.backward()
+    assert ref.relative_error(o_tc, o_simt) <= 1e-5
+    assert np.max(np.abs(lse_tc - lse_simt)) <= 1e-4
+    for a, b in zip(grads_tc, grads_simt):
+        assert ref.relative_error(a, b) <= 1e-5
+
+
+def test_fp32_tensor_core_attention_leaves_rows_outside_the_grid_alone():
+    bh, seq, d = 1, 1024, 64
+    q, k, v, do = inputs.attention_normal(bh, seq, d, seed=77)
+    want = tmtest.oracle_attention(q, k, v, do, False)
+    with tmtest.AttentionRun(q, k, v, do, "f32", False, (128, 128), cuda.PATH_TCGEN05) as run:
+        run.forward()                                   # L for every row
+        run.kernels["pre"](run.h("o"), run.h("do"), run.h("delta"), run.bh, run.seq)
+        for name in ("o", "dq", "dk", "dv"):
+            tmtest.put(run.bufs[name], np.full((bh, seq, d), -7.0, dtype=np.float32))
+        rows = 3 * 128
+        for kern, args in (("fwd", (run.h("q"), run.h("k"), run.h("v"), run.h("o"), run.h("lse"), run.scale, bh, seq)),
+                           ("dq", (run.h("q"), run.h("k"), run.h("v"), run.h("do"), run.h("dq"), run.h("lse"),
+                                   run.h("delta"), run.scale, bh, seq)),
+                           ("dkdv", (run.h("q"), run.h("k"), run.h("v"), run.h("do"), run.h("dk"), run.h("dv"),
+                                     run.h("lse"), run.h("delta"), run.scale, bh, seq))):
+            grid, kinds, values = run.kernels[kern].arguments(*args)
+            run.kernels[kern].launch((3, grid[1], grid[2]), kinds, values)
+        got = {n: tmtest.fetch(run.bufs[n]) for n in ("o", "dq", "dk", "dv")}
+    for name, ref_value in (("o", want[0]), ("dq", want[2]), ("dk", want[3]), ("dv", want[4])):
+        assert ref.relative_error(got[name][:, :rows], ref_value[:, :rows]) <= 1e-5, name
+        assert np.all(got[name][:, rows:] == -7.0), name
+
+
 def test_golden_case_of_the_reference_example():
     """h2 s96 d64 seed 0: the outputs of the reference's own numpy functions."""
     from pathlib import Path

@@ -592,14 +592,15 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
   p.delta = (const float*)delta;
   prefetch_exposed(d);
   std::string why, e;
-  bool tc = false;
+  bool tc = false, f32 = false;     // fused 16-bit tcgen05 kernel / fp32 contractions as 3xTF32 GEMMs
   for (int r = 0; r < repeats; ++r) {
     switch (desc.id) {
       case KernelId::AttnFwd:
         p.out0 = (void*)p.o;
         tc = k.path_option != 1 && attn_fwd_tc_eligible(p, &why);
-        if (k.path_option == 2 && !tc) goto not_eligible;
-        e = tc ? launch_attn_fwd_tc(p, ctx) : launch_attn_fwd_simt(p, ctx);
+        f32 = !tc && k.path_option != 1 && attn_f32_tc_eligible(p, k.path_option == 2, &why);
+        if (k.path_option == 2 && !tc && !f32) goto not_eligible;
+        e = tc ? launch_attn_fwd_tc(p, ctx) : (f32 ? launch_attn_fwd_f32_tc(p, ctx) : launch_attn_fwd_simt(p, ctx));
         break;
       case KernelId::AttnBwdPreprocess:
         p.out0 = (void*)delta;
@@ -609,22 +610,25 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
       case KernelId::AttnBwdDq:
         p.out0 = (void*)dq;
         tc = k.path_option != 1 && attn_bwd_tc_eligible(p, &why);
-        if (k.path_option == 2 && !tc) goto not_eligible;
-        e = tc ? launch_attn_bwd_dq_tc(p, ctx) : launch_attn_bwd_dq_simt(p, ctx);
+        f32 = !tc && k.path_option != 1 && attn_f32_tc_eligible(p, k.path_option == 2, &why);
+        if (k.path_option == 2 && !tc && !f32) goto not_eligible;
+        e = tc ? launch_attn_bwd_dq_tc(p, ctx) : (f32 ? launch_attn_bwd_dq_f32_tc(p, ctx) : launch_attn_bwd_dq_simt(p, ctx));
         break;
       case KernelId::AttnBwdDkdv:
         p.out0 = (void*)dk;
         p.out1 = (void*)dv;
         tc = k.path_option != 1 && attn_bwd_tc_eligible(p, &why);
-        if (k.path_option == 2 && !tc) goto not_eligible;
-        e = tc ? launch_attn_bwd_dkdv_tc(p, ctx) : launch_attn_bwd_dkdv_simt(p, ctx);
+        f32 = !tc && k.path_option != 1 && attn_f32_tc_eligible(p, k.path_option == 2, &why);
+        if (k.path_option == 2 && !tc && !f32) goto not_eligible;
+        e = tc ? launch_attn_bwd_dkdv_tc(p, ctx)
+               : (f32 ? launch_attn_bwd_dkdv_f32_tc(p, ctx) : launch_attn_bwd_dkdv_simt(p, ctx));
         break;
       default:
         e = "unknown kernel";
     }
     if (!e.empty()) { err = cuda_error(e); return false; }
   }
-  k.last_path = tc ? 2 : 1;
+  k.last_path = (tc || f32) ? 2 : 1;
   return true;
 not_eligible:
   err = invalid_argument("the tcgen05 path was required but this launch is not eligible: " + why);

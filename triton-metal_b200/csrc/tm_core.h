@@ -180,6 +180,13 @@ bool attn_bwd_tc_eligible(const AttnProblem& p, std::string* why);
 std::string launch_attn_bwd_dq_tc(const AttnProblem& p, const LaunchCtx& ctx);
 std::string launch_attn_bwd_dkdv_tc(const AttnProblem& p, const LaunchCtx& ctx);
 
+// fp32 attention with every contraction as a 3xTF32 GEMM over a materialised score matrix (long
+// sequences); `forced`: the caller asked for the tensor-core path, so the lower length bound applies.
+bool attn_f32_tc_eligible(const AttnProblem& p, bool forced, std::string* why);
+std::string launch_attn_fwd_f32_tc(const AttnProblem& p, const LaunchCtx& ctx);
+std::string launch_attn_bwd_dq_f32_tc(const AttnProblem& p, const LaunchCtx& ctx);
+std::string launch_attn_bwd_dkdv_f32_tc(const AttnProblem& p, const LaunchCtx& ctx);
+
 std::string launch_rowwise(const RowProblem& p, const LaunchCtx& ctx);
 
 std::string launch_probe(const LaunchCtx& ctx, int* out_host);
