@@ -117,8 +117,8 @@ int32_t tmx_get_device(void);
 int32_t tmx_sm_count(void);
 /* Set an integer option on a loaded kernel.  Known options: "causal" (attention
  * kernels: mask key j > query i), "path" (0 = automatic, 1 = force the generic
- * SIMT kernel, 2 = require the tcgen05 kernel and fail if the shape is not
- * eligible).  0 / -1. */
+ * SIMT kernel, 2 = require a tensor-core kernel - tcgen05 for 16-bit elements,
+ * 3xTF32 for fp32 - and fail if the shape is not eligible).  0 / -1. */
 int32_t tmx_kernel_set_option(int64_t kernel, const char *name, int64_t value);
 /* Which implementation the most recent launch of `kernel` used:
  * 0 none yet, 1 generic SIMT, 2 tcgen05.  -1 on a bad handle. */
