@@ -93,8 +93,15 @@ def config_of(name, dist=None):
 #: dram__bytes_read.sum + dram__bytes_write.sum per step (all kernels of the step), from the ncu
 #: captures summarised under profiles/ (same workload sizes as the benchmark, one GPU).
 NCU_TRAFFIC_BYTES = {
-    "gemm_bf16_8192": {"bytes": 1106.4e6, "source": "profiles/gemm_tc_bf16_8192.md"},
-    "attn_fwd_bf16_s4096": {"bytes": 518.1e6, "source": "profiles/attn_fwd_tc_bf16_s4096_causal.md"},
+    "gemm_bf16_8192": {"bytes": 1125.5e6, "source": "profiles/gemm_tc_bf16_8192.md"},
+    "attn_fwd_bf16_s4096": {"bytes": 520.0e6, "source": "profiles/attn_fwd_tc_bf16_s4096_causal.md"},
+    "attn_fwd_bf16_s4096_full": {"bytes": 518.5e6, "source": "profiles/attn_fwd_tc_bf16_s4096_causal.md"},
+    # dq 662.9 MB + dkdv 775.9 MB + preprocess 273.9 MB
+    "attn_bwd_bf16_s4096_d128": {"bytes": 1712.7e6, "source": "profiles/attn_bwd_tc_bf16_s4096_d128_causal.md"},
+    # dq 329.8 MB + dkdv 377.6 MB; the preprocess pass (O and dO once: 134 MB) was not captured at D=64
+    "attn_bwd_bf16_s4096_d64": {"bytes": 707.4e6 + 134.2e6,
+                                "source": "profiles/attn_bwd_tc_bf16_s4096_d64_causal.md (preprocess pass counted "
+                                          "at its algorithmic bytes)"},
 }
 
 
