@@ -86,6 +86,8 @@ def config_of(name, dist=None):
     if dist is not None and dist.world > 1 and w["kind"] == "gemm":
         out["gather"] = ("peer stores from the GEMM epilogue" if dist.gather_mode == "fused"
                          else "NCCL all-gather behind each launch")
+        if getattr(dist, "gather_note", None):
+            out["gather_note"] = dist.gather_note
     out["l2"] = "inputs larger than L2, no flush"
     return out
 
@@ -464,7 +466,8 @@ class GemmJob(Job):
     def close(self):
         if self.fused:
             self.dist.barrier()          # no rank is still storing into another's copy
-            self.replicated.close()
+            if getattr(self, "replicated", None) is not None:
+                self.replicated.close()
         super().close()
 
     def path(self):
@@ -648,7 +651,29 @@ def run_workload(name, args, dist, headline):
     w = WORKLOADS[name]
     pk = peaks()
     job = (GemmJob if w["kind"] == "gemm" else AttnJob)(w, dist)
-    job.prepare()
+    if w["kind"] == "gemm" and dist.world > 1 and dist.gather_mode == "fused":
+        # The fused gather needs every rank's C mapped into every other process (CUDA IPC over
+        # NVLink).  Set it up and run one step under a guard; the ranks then agree on the outcome
+        # and, if any of them failed, all rebuild the job on the NCCL all-gather and say so.
+        why = ""
+        try:
+            job.prepare()
+            job.step()
+            cuda.synchronize()
+        except Exception as exc:      # noqa: BLE001 - reported in the JSON line
+            why = f"{type(exc).__name__}: {exc}"
+        if dist.max(1.0 if why else 0.0) > 0.0:
+            log(f"[{name}] fused gather unavailable on rank {dist.rank}: {why or 'another rank failed'}")
+            try:
+                job.close()
+            except Exception:         # noqa: BLE001
+                pass
+            dist.gather_mode = "nccl"
+            dist.gather_note = "fused gather could not be set up on every rank; NCCL all-gather used"
+            job = GemmJob(w, dist)
+            job.prepare()
+    else:
+        job.prepare()
     for _ in range(max(args.warmup, 3)):
         job.step()
     cuda.synchronize()

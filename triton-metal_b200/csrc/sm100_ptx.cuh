@@ -437,30 +437,6 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-// 2^x for a pair of values on the fma pipe instead of the special-function unit (whose 16
-// results per cycle and SM are what bounds the softmax once everything else is trimmed):
-// x is split into its nearest integer n and f = x - n in [-0.5, 0.5] by the add-a-big-constant
-// trick, 2^f is a cubic (relative error 1e-4, an order below one bf16 / f16 rounding of the
-// result), and n goes into the exponent field with an integer multiply-add.  x is clamped at
-// -125 from below (everything smaller would be a denormal; the result there is < 2^-125).
-__device__ __forceinline__ void exp2_poly_x2(uint64_t x, float& r0, float& r1) {
-  float x0, x1;
-  unpack_f32x2(x, x0, x1);
-  const uint64_t xc = pack_f32x2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
-  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);          // 1.5 * 2^23
-  const uint64_t t = add_f32x2(xc, magic);                            // low mantissa bits = round(x)
-  const uint64_t n = add_f32x2(t, pack_f32x2(-12582912.f, -12582912.f));
-  const uint64_t f = fma_f32x2(n, pack_f32x2(-1.f, -1.f), xc);
-  uint64_t p = fma_f32x2(f, pack_f32x2(0.05500893f, 0.05500893f), pack_f32x2(0.24221095f, 0.24221095f));
-  p = fma_f32x2(p, f, pack_f32x2(0.6932829f, 0.6932829f));
-  p = fma_f32x2(p, f, pack_f32x2(1.f, 1.f));
-  float p0, p1, t0, t1;
-  unpack_f32x2(p, p0, p1);
-  unpack_f32x2(t, t0, t1);
-  // bits(p) + (bits(t) << 23): the shift drops the constant's bits and leaves n in the exponent
-  r0 = __uint_as_float(__float_as_uint(t0) * 0x800000u + __float_as_uint(p0));
-  r1 = __uint_as_float(__float_as_uint(t1) * 0x800000u + __float_as_uint(p1));
-}
 __device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
