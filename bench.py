@@ -430,6 +430,26 @@ class GemmJob(Job):
             cuda.read_async(c_buf, 0, pin_c.data_ptr(), pin_c.numel())
         cuda.synchronize()           # every piece of C is in host memory
 
+    def e2e_verify(self):
+        """What the end-to-end steps left in pinned host memory against what the device-resident
+        steps left on the device (already checked against the oracle): the first rows of the first
+        piece and the last rows of the last one, which the kernels produce bit for bit alike."""
+        from triton_metal.synthetic import from_bf16_bits
+        N, rows = self.w["N"], 48
+        dev = np.empty((rows, N), dtype=np.uint16)
+        worst = 0.0
+        for piece, first in ((self.pieces[0], True), (self.pieces[-1], False)):
+            pin_c = piece[3].numpy().view(np.uint16).reshape(-1, N)
+            host = pin_c[:rows] if first else pin_c[-rows:]
+            row = 0 if first else self.chunks * self.block - rows       # row of this rank's share
+            if self.fused:
+                self.core.buffer_read(self.c_full, (self.row0 + row) * N * 2, dev.ctypes.data, dev.nbytes)
+            else:
+                chunk, r = divmod(row, self.block)
+                self.core.buffer_read(self.c_local[chunk], r * N * 2, dev.ctypes.data, dev.nbytes)
+            worst = max(worst, float(np.max(np.abs(from_bf16_bits(host.copy()) - from_bf16_bits(dev)))))
+        return worst
+
     def verify(self):
         """Relative error (the reference's `relative_error`) of sampled rows of C against the
         numpy oracle, after a step: rows of this rank's own first block and, with more than one
@@ -584,6 +604,21 @@ class AttnJob(Job):
                 cuda.read_async(buf[name], 0, self.pin_out[name].data_ptr() + offset, nbytes)
         cuda.synchronize()           # every output is in host memory
 
+    def e2e_verify(self):
+        """The end-to-end outputs in pinned host memory against the device-resident ones (checked
+        against the oracle by `verify`): first and last 128 rows of this rank's last head."""
+        from triton_metal.synthetic import from_bf16_bits
+        if not self.bh:
+            return 0.0
+        S, D, head = self.w["seq"], self.w["d"], self.bh - 1
+        worst = 0.0
+        for name in self.e2e_out:
+            host = self.pin_out[name].numpy().view(np.uint16).reshape(self.bh, S, D)[head]
+            for r0, r1 in ((0, 128), (S - 128, S)):
+                dev = self.read_rows(name, head, r0, r1)
+                worst = max(worst, float(np.max(np.abs(from_bf16_bits(host[r0:r1].copy()) - from_bf16_bits(dev)))))
+        return worst
+
     def read_rows(self, name, head, r0, r1):
         """Rows [r0, r1) of one (batch, head) slice of a tensor of this rank's slab, as bf16 words."""
         S, D = self.w["seq"], self.w["d"]
@@ -719,6 +754,8 @@ def run_workload(name, args, dist, headline):
     for _ in range(e2e_steps):
         job.e2e_step()
     e2e_ms = dist.max(cuda.timer_end())
+    # the end-to-end outputs (host memory) against the device-resident ones verified above
+    parity = max(parity, dist.max(job.e2e_verify()))
     h2d, d2h = dist.sum(h2d), dist.sum(d2h)
     per_gpu = tflops / dist.world
     long_region = ms > 1000.0

@@ -138,8 +138,12 @@ int32_t tmx_launch_timed(int64_t kernel, int64_t grid_x, int64_t grid_y, int64_t
 /* Wait for everything enqueued on the library's stream; surfaces device-side
  * status words (bounded waits that gave up) as -1. */
 int32_t tmx_synchronize(void);
-/* Asynchronous copies (host memory should be pinned).  A write is ordered on the library's
- * stream.  A read starts after everything enqueued before it but runs on a side stream, so it
+/* Asynchronous copies (host memory should be pinned).  A write runs on an upload stream of the
+ * library's own: it starts as soon as the last launch that took the buffer as an argument (and
+ * any read-back of the buffer still in flight) has finished - not behind every kernel enqueued
+ * before it - and everything enqueued after it sees the new contents, so the upload of the next
+ * piece of input overlaps the kernels working on the current one while each buffer still sees
+ * the order of the calls.  A read starts after everything enqueued before it but runs on a side stream, so it
  * overlaps the writes and launches enqueued after it: a buffer being read back must not be
  * written by later work until tmx_synchronize, tmx_timer_end or any blocking tm_* call has
  * returned (they wait for the read-backs too). */

@@ -303,3 +303,44 @@ def test_pipelined_pieces_with_side_stream_read_back(core):
         mm.release()
         for h in [bb] + a_bufs + c_bufs:
             core.free_buffer(h)
+
+
+def test_async_write_keeps_its_place_behind_a_launch_that_reads_the_buffer(core):
+    """tmx_buffer_write_async runs on a stream of its own, ahead of kernels enqueued before it -
+    except the last launch that took the buffer: a new A uploaded right behind a matmul must not
+    reach the device before that matmul has read the old one.  Four rounds, each overwriting A
+    while the product of the previous A may still be running; every C is checked bit for bit
+    against a run with blocking copies."""
+    from triton_metal import kernels
+    m, n, k = 2048, 2048, 4096
+    dt = ref.storage_dtype("bf16")
+    mm = kernels.Matmul("bf16")
+    a_buf, b_buf = core.alloc_buffer(m * k * 2), core.alloc_buffer(k * n * 2)
+    c_bufs = [cuda.alloc_device_buffer(m * n * 2) for _ in range(4)]
+    try:
+        _, b = inputs.gemm_normal(m, n, k, seed=21)
+        b_host = np.ascontiguousarray(ref.round_to(b, "bf16").astype(dt))
+        a_hosts = []
+        for i in range(4):
+            a, _ = inputs.gemm_normal(m, n, k, seed=30 + i)
+            a_hosts.append(np.ascontiguousarray(ref.round_to(a, "bf16").astype(dt)))
+        cuda.write_async(b_buf, 0, b_host.ctypes.data, b_host.nbytes)
+        for i in range(4):
+            cuda.write_async(a_buf, 0, a_hosts[i].ctypes.data, a_hosts[i].nbytes)
+            mm.launch_async(*mm.arguments(a_buf, b_buf, c_bufs[i], m, n, k))
+        cuda.synchronize()
+        got = []
+        for c in c_bufs:
+            out = np.zeros((m, n), dtype=dt)
+            core.buffer_read(c, 0, out.ctypes.data, out.nbytes)
+            got.append(out.view(np.uint16).copy())
+        for i in range(4):
+            core.buffer_write(a_buf, 0, a_hosts[i].ctypes.data, a_hosts[i].nbytes)
+            mm.launch(*mm.arguments(a_buf, b_buf, c_bufs[0], m, n, k))
+            want = np.zeros((m, n), dtype=dt)
+            core.buffer_read(c_bufs[0], 0, want.ctypes.data, want.nbytes)
+            assert np.array_equal(got[i], want.view(np.uint16)), f"round {i}"
+    finally:
+        mm.release()
+        for h in [a_buf, b_buf] + c_bufs:
+            core.free_buffer(h)

@@ -75,6 +75,9 @@ struct BufferObj : Object {
   bool host_exposed = false;   // tm_buffer_contents handed the pointer to the host
   bool device_only = false;    // plain device memory (tmx_alloc_device_buffer): no host pointer
   bool imported = false;       // another process's device memory, mapped by tmx_ipc_import
+  // Ordering of tmx_buffer_write_async (which runs on a stream of its own) against the rest:
+  uint64_t last_launch = 0;    // number of the last launch that took this buffer as an argument
+  bool read_async_since_write = false;   // a tmx_buffer_read_async of it may still be in flight
   BufferObj() : Object(ObjKind::Buffer) {}
   ~BufferObj() override {
     if (!ptr) return;
@@ -158,6 +161,20 @@ struct Device {
   cudaStream_t read_stream = nullptr;
   cudaEvent_t ev_read = nullptr, ev_join = nullptr;
   bool reads_in_flight = false;
+  // Host -> device copies of tmx_buffer_write_async run on a third stream, so that the upload
+  // of the next piece of input overlaps the kernels enqueued before it (on `stream` the copy
+  // would wait for them).  Stream order is kept per buffer: the copy waits for the last launch
+  // that took the buffer (every launch records an event once asynchronous writes are in use;
+  // the last kEventRing of them are kept) and for a read-back of it still in flight, and
+  // `stream` waits for the copy, so everything enqueued afterwards sees the new contents.
+  static constexpr int kEventRing = 64;
+  cudaStream_t write_stream = nullptr;
+  cudaEvent_t launch_events[kEventRing] = {};
+  uint64_t launch_event_number[kEventRing] = {};
+  cudaEvent_t write_events[kEventRing] = {};
+  cudaEvent_t ev_order = nullptr;
+  uint64_t launch_number = 0, write_number = 0;
+  bool async_writes = false;
   DeviceStatus* status = nullptr;   // pinned, device-visible
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   // capability probe
@@ -209,6 +226,13 @@ bool ensure_device(std::string& err) {
     return fail(std::string("could not create the read-back stream: ") + cudaGetErrorString(e));
   cudaEventCreateWithFlags(&g_dev.ev_read, cudaEventDisableTiming);
   cudaEventCreateWithFlags(&g_dev.ev_join, cudaEventDisableTiming);
+  if ((e = cudaStreamCreateWithFlags(&g_dev.write_stream, cudaStreamNonBlocking)) != cudaSuccess)
+    return fail(std::string("could not create the upload stream: ") + cudaGetErrorString(e));
+  cudaEventCreateWithFlags(&g_dev.ev_order, cudaEventDisableTiming);
+  for (int i = 0; i < Device::kEventRing; ++i) {
+    cudaEventCreateWithFlags(&g_dev.launch_events[i], cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&g_dev.write_events[i], cudaEventDisableTiming);
+  }
   g_dev.ok = true;
   return true;
 }
@@ -404,11 +428,36 @@ void prefetch_exposed(const Decoded& d) {
 }
 
 // Enqueue one launch (no wait).  Returns false with `err` on failure.
+// Called once a launch is on the stream: numbers it, remembers the number in every buffer it
+// took, and - once tmx_buffer_write_async is in use - records the event a later asynchronous
+// write into one of those buffers will wait for.
+template <typename Buffers>
+void note_launch(const Buffers& buffers) {
+  const uint64_t n = ++g_dev.launch_number;
+  for (BufferObj* b : buffers)
+    if (b) b->last_launch = n;
+  if (g_dev.async_writes) {
+    const int slot = (int)(n % Device::kEventRing);
+    cudaEventRecord(g_dev.launch_events[slot], g_dev.stream);
+    g_dev.launch_event_number[slot] = n;
+  }
+}
+
 bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
              const int32_t* kinds, const int64_t* values, int32_t argc, int repeats,
              std::string& err) {
   Decoded d;
   if (!decode_args(k, kinds, values, argc, d, err)) return false;
+  struct NoteOnExit {
+    Decoded& d;
+    bool armed = false;
+    ~NoteOnExit() {
+      if (!armed) return;
+      std::vector<BufferObj*> bufs;
+      for (auto& kv : d.buffers) bufs.push_back(kv.second.get());
+      note_launch(bufs);
+    }
+  } note{d};
   // Runtime.swift:201-211
   if (gx <= 0 || gy <= 0 || gz <= 0) {
     err = invalid_argument("threadgroup grid must be positive in every dimension");
@@ -629,6 +678,7 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
     if (!e.empty()) { err = cuda_error(e); return false; }
   }
   k.last_path = (tc || f32) ? 2 : 1;
+  note.armed = true;
   return true;
 not_eligible:
   err = invalid_argument("the tcgen05 path was required but this launch is not eligible: " + why);
@@ -684,6 +734,28 @@ int32_t do_copy(int64_t buffer, int64_t offset, const void* host, int64_t length
     cudaStreamWaitEvent(g_dev.read_stream, g_dev.ev_read, 0);
     copy_stream = g_dev.read_stream;
     g_dev.reads_in_flight = true;
+    b->read_async_since_write = true;
+  }
+  if (side_stream && to_device) {
+    // ahead of the kernels enqueued so far, except the last one that took this buffer
+    g_dev.async_writes = true;
+    copy_stream = g_dev.write_stream;
+    if (b->last_launch) {
+      const int slot = (int)(b->last_launch % Device::kEventRing);
+      if (g_dev.launch_event_number[slot] == b->last_launch) {
+        cudaStreamWaitEvent(g_dev.write_stream, g_dev.launch_events[slot], 0);
+      } else {
+        // launched before events were being recorded, or more than a ring ago: wait for
+        // everything enqueued so far
+        cudaEventRecord(g_dev.ev_order, g_dev.stream);
+        cudaStreamWaitEvent(g_dev.write_stream, g_dev.ev_order, 0);
+      }
+    }
+    if (b->read_async_since_write) {
+      cudaEventRecord(g_dev.ev_order, g_dev.read_stream);
+      cudaStreamWaitEvent(g_dev.write_stream, g_dev.ev_order, 0);
+      b->read_async_since_write = false;
+    }
   }
   cudaError_t e = to_device
       ? cudaMemcpyAsync(dev, host, (size_t)length, cudaMemcpyDefault, copy_stream)
@@ -691,6 +763,12 @@ int32_t do_copy(int64_t buffer, int64_t offset, const void* host, int64_t length
   if (e != cudaSuccess) {
     store_error(cuda_error(std::string("buffer copy failed: ") + cudaGetErrorString(e)));
     return -1;
+  }
+  if (side_stream && to_device) {
+    // everything enqueued on the library's stream from here on comes after the copy
+    const int slot = (int)(++g_dev.write_number % Device::kEventRing);
+    cudaEventRecord(g_dev.write_events[slot], g_dev.write_stream);
+    cudaStreamWaitEvent(g_dev.stream, g_dev.write_events[slot], 0);
   }
   if (wait && !sync_stream(err)) { store_error(err); return -1; }
   return 0;
@@ -985,7 +1063,7 @@ int32_t tmx_synchronize(void) {
 }
 
 int32_t tmx_buffer_write_async(int64_t buffer, int64_t offset, const void* source, int64_t length) {
-  return do_copy(buffer, offset, source, length, true, false);
+  return do_copy(buffer, offset, source, length, true, false, true);
 }
 
 int32_t tmx_buffer_read_async(int64_t buffer, int64_t offset, void* destination, int64_t length) {
@@ -1019,6 +1097,8 @@ int32_t tmx_timer_begin(void) {
   std::string err;
   if (!bind_device(err)) { store_error(err); return -1; }
   cudaEventRecord(g_dev.ev_begin, g_dev.stream);
+  // uploads enqueued from here on belong to the timed region: they start behind its first event
+  cudaStreamWaitEvent(g_dev.write_stream, g_dev.ev_begin, 0);
   return 0;
 }
 
@@ -1126,6 +1206,7 @@ int32_t tmx_matmul_f32_static(int64_t a, int64_t b, int64_t c, int64_t M, int64_
     store_error(e.rfind("the operand split needs", 0) == 0 ? invalid_argument(e) : cuda_error(e));
     return -1;
   }
+  note_launch(std::vector<BufferObj*>{A.get(), B.get(), C.get()});
   if (!sync_stream(err)) { store_error(err); return -1; }
   return 0;
 }
@@ -1286,6 +1367,9 @@ int32_t tmx_matmul_gathered(int64_t kernel, int64_t a, int64_t b, const int64_t*
   std::string e = launch_gemm_tc_gathered(p, g, launch_ctx());
   if (!e.empty()) return fail(cuda_error(e));
   k->last_path = 2;
+  std::vector<BufferObj*> launch_buffers{A.get(), B.get()};
+  for (auto& kept : keep) launch_buffers.push_back(kept.get());
+  note_launch(launch_buffers);
   return 0;
 }
 
