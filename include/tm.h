@@ -143,10 +143,12 @@ int32_t tmx_synchronize(void);
  * any read-back of the buffer still in flight) has finished - not behind every kernel enqueued
  * before it - and everything enqueued after it sees the new contents, so the upload of the next
  * piece of input overlaps the kernels working on the current one while each buffer still sees
- * the order of the calls.  A read starts after everything enqueued before it but runs on a side stream, so it
- * overlaps the writes and launches enqueued after it: a buffer being read back must not be
- * written by later work until tmx_synchronize, tmx_timer_end or any blocking tm_* call has
- * returned (they wait for the read-backs too). */
+ * the order of the calls.  A read starts after everything enqueued before it but runs on a side
+ * stream, so it overlaps the writes and launches enqueued after it; a later launch or write that
+ * takes the same buffer waits for the read-back.  tmx_synchronize, tmx_timer_end and every
+ * blocking tm_* call wait for the uploads and read-backs too.  tmx_matmul_gathered and
+ * tmx_matmul_f32_static do not look for read-backs in flight: synchronise before handing them a
+ * buffer that tmx_buffer_read_async is still reading. */
 int32_t tmx_buffer_write_async(int64_t buffer, int64_t offset, const void *source, int64_t length);
 int32_t tmx_buffer_read_async(int64_t buffer, int64_t offset, void *destination, int64_t length);
 /* Fill `length` bytes of the buffer with `byte` (asynchronous). */

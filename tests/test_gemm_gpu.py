@@ -344,3 +344,39 @@ def test_async_write_keeps_its_place_behind_a_launch_that_reads_the_buffer(core)
         mm.release()
         for h in [a_buf, b_buf] + c_bufs:
             core.free_buffer(h)
+
+
+def test_launch_waits_for_a_read_back_of_its_output(core):
+    """A read-back runs on a side stream; a later launch that writes the same buffer waits for it.
+    C of the first product is read back (pinned host memory, so the copy really is asynchronous)
+    while a second product into the same C is already enqueued: the host must still receive the
+    first product, then the second."""
+    import torch
+    from triton_metal import kernels
+    m, n, k = 4096, 4096, 512
+    dt = ref.storage_dtype("bf16")
+    mm = kernels.Matmul("bf16")
+    a_bufs = [core.alloc_buffer(m * k * 2) for _ in range(2)]
+    b_buf, c_buf = core.alloc_buffer(k * n * 2), cuda.alloc_device_buffer(m * n * 2)
+    outs = [torch.empty(m * n * 2, dtype=torch.uint8, pin_memory=True) for _ in range(2)]
+    try:
+        _, b = inputs.gemm_normal(m, n, k, seed=41)
+        b_host = np.ascontiguousarray(ref.round_to(b, "bf16").astype(dt))
+        core.buffer_write(b_buf, 0, b_host.ctypes.data, b_host.nbytes)
+        for i in range(2):
+            a, _ = inputs.gemm_normal(m, n, k, seed=50 + i)
+            a_host = np.ascontiguousarray(ref.round_to(a, "bf16").astype(dt))
+            core.buffer_write(a_bufs[i], 0, a_host.ctypes.data, a_host.nbytes)
+        for i in range(2):
+            mm.launch_async(*mm.arguments(a_bufs[i], b_buf, c_buf, m, n, k))
+            cuda.read_async(c_buf, 0, outs[i].data_ptr(), outs[i].numel())
+        cuda.synchronize()
+        for i in range(2):
+            mm.launch(*mm.arguments(a_bufs[i], b_buf, c_buf, m, n, k))
+            want = np.zeros(m * n, dtype=np.uint16)
+            core.buffer_read(c_buf, 0, want.ctypes.data, want.nbytes)
+            assert np.array_equal(outs[i].numpy().view(np.uint16), want), f"product {i}"
+    finally:
+        mm.release()
+        for h in a_bufs + [b_buf, c_buf]:
+            core.free_buffer(h)

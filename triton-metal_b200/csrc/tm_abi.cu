@@ -175,6 +175,7 @@ struct Device {
   cudaEvent_t ev_order = nullptr;
   uint64_t launch_number = 0, write_number = 0;
   bool async_writes = false;
+  std::vector<std::weak_ptr<BufferObj>> read_back;   // buffers with a read-back possibly in flight
   DeviceStatus* status = nullptr;   // pinned, device-visible
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   // capability probe
@@ -280,11 +281,16 @@ const std::string& unusable_reason() {
 
 // Wait for the stream and surface device-side status.
 // Make the library's stream wait for the read-backs enqueued on the side stream.
+// (Every caller synchronises the library's stream right afterwards, so the read-backs are
+// complete when it returns and the buffers' marks can go.)
 void join_reads() {
   if (!g_dev.reads_in_flight) return;
   cudaEventRecord(g_dev.ev_join, g_dev.read_stream);
   cudaStreamWaitEvent(g_dev.stream, g_dev.ev_join, 0);
   g_dev.reads_in_flight = false;
+  for (auto& weak : g_dev.read_back)
+    if (auto b = weak.lock()) b->read_async_since_write = false;
+  g_dev.read_back.clear();
 }
 
 bool sync_stream(std::string& err) {
@@ -478,6 +484,14 @@ bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
     if (!why.empty()) {
       err = cuda_error(why);
       return false;
+    }
+  }
+  // a buffer whose read-back may still be in flight must not be overwritten under it
+  for (auto& kv : d.buffers) {
+    if (kv.second && kv.second->read_async_since_write) {
+      cudaEventRecord(g_dev.ev_order, g_dev.read_stream);
+      cudaStreamWaitEvent(g_dev.stream, g_dev.ev_order, 0);
+      break;
     }
   }
   LaunchCtx ctx = launch_ctx();
@@ -734,6 +748,7 @@ int32_t do_copy(int64_t buffer, int64_t offset, const void* host, int64_t length
     cudaStreamWaitEvent(g_dev.read_stream, g_dev.ev_read, 0);
     copy_stream = g_dev.read_stream;
     g_dev.reads_in_flight = true;
+    if (!b->read_async_since_write) g_dev.read_back.push_back(b);
     b->read_async_since_write = true;
   }
   if (side_stream && to_device) {
@@ -754,7 +769,6 @@ int32_t do_copy(int64_t buffer, int64_t offset, const void* host, int64_t length
     if (b->read_async_since_write) {
       cudaEventRecord(g_dev.ev_order, g_dev.read_stream);
       cudaStreamWaitEvent(g_dev.write_stream, g_dev.ev_order, 0);
-      b->read_async_since_write = false;
     }
   }
   cudaError_t e = to_device
