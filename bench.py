@@ -38,8 +38,12 @@ for _p in (str(ROOT), str(ROOT / "triton-metal_b200")):
         sys.path.insert(0, _p)
 
 
-def log(*a):
-    print(*a, file=sys.stderr, flush=True)
+def log(*a, every_rank=False):
+    """Progress lines on stderr, from rank 0 unless told otherwise (one write per line, so that the
+    ranks' lines do not run into each other)."""
+    if every_rank or os.environ.get("RANK", "0") == "0":
+        sys.stderr.write(" ".join(str(x) for x in a) + "\n")
+        sys.stderr.flush()
 
 
 # --------------------------------------------------------------------------- #
@@ -698,7 +702,8 @@ def run_workload(name, args, dist, headline):
         except Exception as exc:      # noqa: BLE001 - reported in the JSON line
             why = f"{type(exc).__name__}: {exc}"
         if dist.max(1.0 if why else 0.0) > 0.0:
-            log(f"[{name}] fused gather unavailable on rank {dist.rank}: {why or 'another rank failed'}")
+            log(f"[{name}] fused gather unavailable on rank {dist.rank}: {why or 'another rank failed'}",
+                every_rank=True)
             try:
                 job.close()
             except Exception:         # noqa: BLE001
