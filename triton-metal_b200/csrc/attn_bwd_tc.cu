@@ -178,21 +178,59 @@ __device__ __forceinline__ void ds_part(uint32_t s_tmem, const uint32_t (&s)[32]
   tmem_st_32x16(s_tmem, packed);
 }
 
+// 2^x for a pair of values on the fma pipe instead of the special-function unit: x is split into
+// its nearest integer n and f = x - n in [-0.5, 0.5] by the add-a-big-constant trick, 2^f is a
+// cubic (relative error 1e-4, an order below one bf16 / f16 rounding of the result), and n goes
+// into the exponent field with an integer multiply-add.  x is clamped at -125 from below
+// (everything smaller would be a denormal; the result there is < 2^-125).
+__device__ __forceinline__ void exp2_cubic_x2(uint64_t x, float& r0, float& r1) {
+  float x0, x1;
+  unpack_f32x2(x, x0, x1);
+  const uint64_t xc = pack_f32x2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);          // 1.5 * 2^23
+  const uint64_t t = add_f32x2(xc, magic);                            // low mantissa bits = round(x)
+  const uint64_t n = add_f32x2(t, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f = fma_f32x2(n, pack_f32x2(-1.f, -1.f), xc);
+  uint64_t p = fma_f32x2(f, pack_f32x2(0.05500893f, 0.05500893f), pack_f32x2(0.24221095f, 0.24221095f));
+  p = fma_f32x2(p, f, pack_f32x2(0.6932829f, 0.6932829f));
+  p = fma_f32x2(p, f, pack_f32x2(1.f, 1.f));
+  float p0, p1, t0, t1;
+  unpack_f32x2(p, p0, p1);
+  unpack_f32x2(t, t0, t1);
+  // bits(p) + (bits(t) << 23): the shift drops the constant's bits and leaves n in the exponent
+  r0 = __uint_as_float(__float_as_uint(t0) * 0x800000u + __float_as_uint(p0));
+  r1 = __uint_as_float(__float_as_uint(t1) * 0x800000u + __float_as_uint(p1));
+}
+
 // dkdv pass A: P^T = exp2(S^T*qk_scale - L[query]) from the register copy `s` of the group's
 // 32 columns, rounded and packed (16 words).  `neg_lse_s` holds -L of the 32 queries (the sign is
 // flipped once when the statistics are staged, so that the scaling is one two-wide fma per pair).
 // `k_minus_q0` > column means key row > query: masked.
-template <typename T, bool DIAG>
+// `CUBIC` is a mask over every eight pairs of columns: the pairs whose bit is set take the cubic
+// on the fma pipe instead of ex2.  At D = 64, where the exponentials and not the MMAs bound the
+// kernel, a quarter of them there is worth 5 % of the kernel's time (measured); a half is a loss.
+template <typename T, bool DIAG, uint32_t CUBIC>
 __device__ __forceinline__ void pt_part(const uint32_t (&s)[32], float qk_scale, const float* neg_lse_s,
                                         int k_minus_q0, uint32_t (&keep)[16]) {
   const uint64_t scale2 = pack_f32x2(qk_scale, qk_scale);
+  auto exp2_pair = [](uint64_t x, int pair, float& r0, float& r1) {
+    if ((CUBIC >> (pair & 7)) & 1u) {
+      exp2_cubic_x2(x, r0, r1);
+    } else {
+      float x0, x1;
+      unpack_f32x2(x, x0, x1);
+      r0 = fast_exp2(x0);
+      r1 = fast_exp2(x1);
+    }
+  };
 #pragma unroll
   for (int i = 0; i < 32; i += 4) {
     const float4 nl = *reinterpret_cast<const float4*>(neg_lse_s + i);
-    float x0, x1, x2, x3;
-    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), scale2, pack_f32x2(nl.x, nl.y)), x0, x1);
-    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), scale2, pack_f32x2(nl.z, nl.w)), x2, x3);
-    float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+    float p0, p1, p2, p3;
+    exp2_pair(fma_f32x2(pack_f32x2(__uint_as_float(s[i]), __uint_as_float(s[i + 1])), scale2, pack_f32x2(nl.x, nl.y)),
+              i / 2, p0, p1);
+    exp2_pair(fma_f32x2(pack_f32x2(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])), scale2, pack_f32x2(nl.z, nl.w)),
+              i / 2 + 1, p2, p3);
     if (DIAG) {
       if (k_minus_q0 > i) p0 = 0.f;
       if (k_minus_q0 > i + 1) p1 = 0.f;
@@ -812,8 +850,9 @@ attn_bwd_dkdv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&ss.s_read));
           uint32_t keep[16];
-          if (diagonal) pt_part<T, true>(sv, qk_scale, lse_s, k_row - q0, keep);
-          else pt_part<T, false>(sv, qk_scale, lse_s, 0, keep);
+          constexpr uint32_t CUBIC = D == 64 ? 0x11u : 0u;     // pairs 0 and 4 of every eight
+          if (diagonal) pt_part<T, true, CUBIC>(sv, qk_scale, lse_s, k_row - q0, keep);
+          else pt_part<T, false, CUBIC>(sv, qk_scale, lse_s, 0, keep);
           // dV(t-1) must have read the previous P^T before it is replaced: dP^T(t) was issued after
           // it, so its commit covers it (and is waited for here instead of before the dS^T pass)
           if (!mbar_wait(smem_u32(&ss.dpt_full), c & 1, wc, 60)) { ok = false; continue; }
