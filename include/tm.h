@@ -63,7 +63,14 @@ char *tm_kernel_info(const char *ttir, int32_t num_simdgroups);
 /* Turn a descriptor returned by tm_emit_msl into a library handle.
  * Replaces tm_compile_msl, Compiler.swift:235-247. */
 int64_t tm_compile_msl(const char *source);
-/* Same, from a byte image of the descriptor (the cached-binary path).
+/* The cached-binary path.  The image is either the bytes of a descriptor (the text tm_emit_msl
+ * returned) or a binary of this platform - a cubin (ELF) or a fatbin holding sm_100a code.  A
+ * binary is loaded as it is: tm_load_kernel looks its entry points up by name (declare them
+ * extern "C"), and tm_launch passes argument i to parameter i - a buffer as its device address,
+ * i32 / f32 / i64 in their own width - on a grid of (x, y, z) blocks of `threads` threads, after
+ * checking count and widths against what the image declares; tm_kernel_max_threads reports the
+ * entry point's own limit.  So a caller's own CUDA kernels run behind the same calls as the
+ * library's, as arbitrary Metal kernels do behind the reference's.
  * Replaces tm_load_metallib, Compiler.swift:250-263. */
 int64_t tm_load_metallib(const void *bytes, int64_t length);
 /* Replaces tm_release_library, Compiler.swift:383-386. */

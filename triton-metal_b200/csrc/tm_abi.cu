@@ -59,13 +59,27 @@ struct Object {
 
 struct LibraryObj : Object {
   std::vector<KernelDesc> kernels;
+  // A binary image (cubin / fatbin) handed to tm_load_metallib: the caller's own kernels, loaded
+  // as they are.  The bytes are kept for as long as the image is.
+  std::string image_bytes;
+  cudaLibrary_t image = nullptr;
   LibraryObj() : Object(ObjKind::Library) {}
+  ~LibraryObj() override {
+    if (image) cudaLibraryUnload(image);
+  }
 };
 
 struct KernelObj : Object {
   KernelDesc desc;
   int path_option = 0;   // 0 auto, 1 SIMT, 2 tcgen05 required
   int last_path = 0;
+  // Entry point of a binary image (null for the library's own kernels): its name, the size of
+  // every parameter as the image declares them, and the image itself, kept loaded.
+  cudaKernel_t binary = nullptr;
+  std::string binary_name;
+  std::vector<size_t> param_sizes;
+  int max_threads = 1024;
+  std::shared_ptr<LibraryObj> owner;
   KernelObj() : Object(ObjKind::Kernel) {}
 };
 
@@ -449,9 +463,100 @@ void note_launch(const Buffers& buffers) {
   }
 }
 
+// A kernel of a binary image: the arguments go to the entry point in the order given, a buffer
+// as its device address, scalars in their own width (Runtime.swift:213-231 binds them the same
+// way: argument i at index i).  Count and widths are checked against what the image declares,
+// so that a mismatched call is an error message and not a fault on the device.
+bool enqueue_binary(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
+                    const int32_t* kinds, const int64_t* values, int32_t argc, int repeats,
+                    std::string& err) {
+  if (argc > 0 && (!kinds || !values)) {
+    err = invalid_argument("tm_launch received NULL argument arrays");
+    return false;
+  }
+  if (gx <= 0 || gy <= 0 || gz <= 0) {
+    err = invalid_argument("threadgroup grid must be positive in every dimension");
+    return false;
+  }
+  if (threads <= 0) {
+    err = invalid_argument("threadsPerThreadgroup must be positive");
+    return false;
+  }
+  if (threads > k.max_threads) {
+    err = invalid_argument("threadsPerThreadgroup " + std::to_string(threads) +
+                           " exceeds the pipeline maximum " + std::to_string(k.max_threads));
+    return false;
+  }
+  if (gx > 0x7fffffffll || gy > 65535 || gz > 65535) {
+    err = invalid_argument("threadgroup grid exceeds what the device can launch");
+    return false;
+  }
+  if ((size_t)argc != k.param_sizes.size()) {
+    err = invalid_argument("kernel '" + k.binary_name + "' takes " + std::to_string(k.param_sizes.size()) +
+                           " arguments, got " + std::to_string(argc));
+    return false;
+  }
+  std::vector<uint64_t> storage((size_t)argc);
+  std::vector<void*> args((size_t)argc);
+  std::vector<std::shared_ptr<BufferObj>> buffers;
+  for (int i = 0; i < argc; ++i) {
+    size_t width = 0;
+    switch (kinds[i]) {
+      case 0: {
+        auto b = lookup_as<BufferObj>(values[i], ObjKind::Buffer, err);
+        if (!b) return false;
+        storage[i] = (uint64_t)(uintptr_t)b->ptr;
+        buffers.push_back(b);
+        width = 8;
+        break;
+      }
+      case 1: storage[i] = (uint32_t)values[i]; width = 4; break;
+      case 2: storage[i] = (uint32_t)values[i]; width = 4; break;
+      case 3: storage[i] = (uint64_t)values[i]; width = 8; break;
+      default:
+        err = invalid_argument("unknown launch argument kind " + std::to_string(kinds[i]) + " at position " +
+                               std::to_string(i));
+        return false;
+    }
+    if (k.param_sizes[i] != width) {
+      err = invalid_argument("argument " + std::to_string(i) + " of kernel '" + k.binary_name + "' is " +
+                             std::to_string(k.param_sizes[i]) + " bytes wide, the launch passes " +
+                             std::to_string(width));
+      return false;
+    }
+    args[i] = &storage[i];
+  }
+  if (!bind_device(err)) return false;
+  std::vector<BufferObj*> raw;
+  bool waited = false;
+  for (auto& b : buffers) {
+    raw.push_back(b.get());
+    if (b->host_exposed) cudaMemPrefetchAsync(b->ptr, (size_t)b->length, g_dev.ordinal, g_dev.stream);
+    if (b->read_async_since_write && !waited) {
+      cudaEventRecord(g_dev.ev_order, g_dev.read_stream);
+      cudaStreamWaitEvent(g_dev.stream, g_dev.ev_order, 0);
+      waited = true;
+    }
+  }
+  for (int r = 0; r < repeats; ++r) {
+    cudaError_t e = cudaLaunchKernel((const void*)k.binary, dim3((unsigned)gx, (unsigned)gy, (unsigned)gz),
+                                     dim3((unsigned)threads, 1, 1), args.data(), 0, g_dev.stream);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      err = cuda_error("launch of '" + k.binary_name + "' failed: " + cudaGetErrorString(e));
+      return false;
+    }
+    ++g_dev.launches;
+  }
+  k.last_path = 0;
+  note_launch(raw);
+  return true;
+}
+
 bool enqueue(KernelObj& k, int64_t gx, int64_t gy, int64_t gz, int64_t threads,
              const int32_t* kinds, const int64_t* values, int32_t argc, int repeats,
              std::string& err) {
+  if (k.binary) return enqueue_binary(k, gx, gy, gz, threads, kinds, values, argc, repeats, err);
   Decoded d;
   if (!decode_args(k, kinds, values, argc, d, err)) return false;
   struct NoteOnExit {
@@ -872,6 +977,29 @@ int64_t tm_load_metallib(const void* bytes, int64_t length) {
     store_error(invalid_argument("tm_load_metallib received an empty image"));
     return 0;
   }
+  // A binary of this platform - a cubin (ELF) or a fatbin - is loaded as it is: the caller's own
+  // kernels behind the same launch call, which is what a metallib is to the reference
+  // (Compiler.swift:250-262).  Anything else must be the text tm_emit_msl produced.
+  const unsigned char* head = (const unsigned char*)bytes;
+  const bool elf = length >= 4 && head[0] == 0x7f && head[1] == 'E' && head[2] == 'L' && head[3] == 'F';
+  const bool fatbin = length >= 4 && head[0] == 0x50 && head[1] == 0xed && head[2] == 0x55 && head[3] == 0xba;
+  if (elf || fatbin) {
+    std::string err;
+    if (!bind_device(err)) { store_error(err); return 0; }
+    auto lib = std::make_shared<LibraryObj>();
+    lib->image_bytes.assign((const char*)bytes, (size_t)length);
+    cudaError_t e = cudaLibraryLoadData(&lib->image, lib->image_bytes.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+    // (modules load lazily: counting the entry points is what makes the driver read the image)
+    unsigned int entries = 0;
+    if (e == cudaSuccess) e = cudaLibraryGetKernelCount(&entries, lib->image);
+    if (e != cudaSuccess || entries == 0) {
+      cudaGetLastError();
+      store_error(cuda_error(std::string("could not load metallib: ") +
+                             (e != cudaSuccess ? cudaGetErrorString(e) : "the image holds no kernels")));
+      return 0;
+    }
+    return g_handles.insert(lib);
+  }
   std::string text((const char*)bytes, (size_t)length);
   auto lib = std::make_shared<LibraryObj>();
   std::string err;
@@ -892,6 +1020,43 @@ int64_t tm_load_kernel(int64_t library, const char* name) {
   std::string err;
   auto lib = lookup_as<LibraryObj>(library, ObjKind::Library, err);
   if (!lib) { store_error(err); return 0; }
+  if (lib->image) {
+    if (!bind_device(err)) { store_error(err); return 0; }
+    cudaKernel_t entry = nullptr;
+    if (cudaLibraryGetKernel(&entry, lib->image, name) != cudaSuccess || !entry) {
+      cudaGetLastError();
+      std::vector<std::string> names;
+      unsigned int count = 0;
+      if (cudaLibraryGetKernelCount(&count, lib->image) == cudaSuccess && count) {
+        std::vector<cudaKernel_t> all(count);
+        if (cudaLibraryEnumerateKernels(all.data(), count, lib->image) == cudaSuccess) {
+          for (cudaKernel_t one : all) {
+            const char* n = nullptr;
+            if (cudaFuncGetName(&n, (const void*)one) == cudaSuccess && n) names.push_back(n);
+          }
+        }
+      }
+      cudaGetLastError();
+      std::sort(names.begin(), names.end());
+      std::string available;
+      for (auto& n : names) available += (available.empty() ? "" : ", ") + n;
+      store_error(cuda_error(std::string("kernel '") + name + "' not found in library (available: " + available + ")"));
+      return 0;
+    }
+    auto obj = std::make_shared<KernelObj>();
+    obj->binary = entry;
+    obj->binary_name = name;
+    obj->owner = lib;
+    cudaFuncAttributes attr{};
+    if (cudaFuncGetAttributes(&attr, (const void*)entry) == cudaSuccess) obj->max_threads = attr.maxThreadsPerBlock;
+    for (size_t i = 0;; ++i) {
+      size_t offset = 0, size = 0;
+      if (cudaFuncGetParamInfo((const void*)entry, i, &offset, &size) != cudaSuccess) break;
+      obj->param_sizes.push_back(size);
+    }
+    cudaGetLastError();
+    return g_handles.insert(obj);
+  }
   for (auto& k : lib->kernels) {
     if (std::string(name) == kernel_entry_name(k.id)) {
       auto obj = std::make_shared<KernelObj>();
@@ -918,7 +1083,7 @@ int64_t tm_kernel_max_threads(int64_t kernel) {
   std::string err;
   auto k = lookup_as<KernelObj>(kernel, ObjKind::Kernel, err);
   if (!k) { store_error(err); return -1; }
-  return 1024;
+  return k->binary ? k->max_threads : 1024;
 }
 
 int32_t tm_release_kernel(int64_t kernel) { return g_handles.remove(kernel) ? 0 : -1; }
@@ -1026,6 +1191,10 @@ int32_t tmx_kernel_set_option(int64_t kernel, const char* name, int64_t value) {
   auto k = lookup_as<KernelObj>(kernel, ObjKind::Kernel, err);
   if (!k) { store_error(err); return -1; }
   if (!name) { store_error(invalid_argument("tmx_kernel_set_option received a NULL name")); return -1; }
+  if (k->binary) {
+    store_error(invalid_argument("kernels of a binary image take no options"));
+    return -1;
+  }
   std::string n(name);
   if (n == "causal") {
     if (k->desc.id == KernelId::Matmul || k->desc.id == KernelId::AttnBwdPreprocess || is_rowwise(k->desc.id)) {
@@ -1322,7 +1491,7 @@ int32_t tmx_matmul_gathered(int64_t kernel, int64_t a, int64_t b, const int64_t*
   auto fail = [&](const std::string& m) { store_error(m); return -1; };
   auto k = lookup_as<KernelObj>(kernel, ObjKind::Kernel, err);
   if (!k) return fail(err);
-  if (k->desc.id != KernelId::Matmul || k->desc.elt == Elt::F32)
+  if (k->binary || k->desc.id != KernelId::Matmul || k->desc.elt == Elt::F32)
     return fail(invalid_argument("tmx_matmul_gathered takes a 16-bit matmul_kernel"));
   if (!c_replicas || !flag_buffers || world < 1 || world > kGatherMaxRanks || rank < 0 || rank >= world)
     return fail(invalid_argument("tmx_matmul_gathered needs 1...8 ranks, this rank among them, and their buffers"));
