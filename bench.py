@@ -65,7 +65,7 @@ WORKLOADS = {
                                     causal=True, element="bf16"),
 }
 HEADLINE = "gemm_bf16_8192"
-ALSO = ["attn_fwd_bf16_s4096", "attn_fwd_bf16_s4096_full", "attn_fwd_bf16_s16384",
+ALSO = ["gemm_bf16_skinny", "attn_fwd_bf16_s4096", "attn_fwd_bf16_s4096_full", "attn_fwd_bf16_s16384",
         "attn_bwd_bf16_s4096_d128", "attn_bwd_bf16_s4096_d64"]
 
 
