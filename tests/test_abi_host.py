@@ -335,3 +335,6 @@ def test_there_is_no_cpu_fallback(core):
     assert "no CUDA device" in core.unusable_reason()
     with pytest.raises(RuntimeError, match="no CUDA device"):
         core.alloc_buffer(64)
+    # a binary image needs the device too: an error, not a crash and not a host interpreter
+    with pytest.raises(RuntimeError, match="no CUDA device"):
+        core.load_metallib(b"\x7fELF" + bytes(128))
