@@ -11,23 +11,26 @@
 // the next block run under the output pass of the current one.
 // A query block is two 128-row tiles that take turns on the tensor core, so the
 // exponentials of one tile overlap the MMAs of the other:
-//   warps 0-7   softmax: tile t = warp / 4.  A thread owns one query row (its TMEM lane):
-//               it copies the row's 128 scores of a key block into registers once, takes
-//               the maximum, then exp2 / row sum / round, and writes the 16-bit P back over
-//               the scores.  Nothing is exchanged between threads.
-//   warp 8      TMA: Q (both tiles) once per query block, then K and V blocks of 128
+//   warps 0-15  softmax: tile t = warp / 8; inside a tile warps 0-3 own columns 0-63
+//               of every 128-column score block and warps 4-7 columns 64-127.  A thread
+//               owns one query row (its TMEM lane) and 64 columns: max over them, one
+//               exchange of the half-row maxima through shared memory, then exp2 /
+//               partial sum / round, writing the 16-bit P back over the scores it read.
+//   warp 16     TMA: Q (both tiles) once per query block, then K and V blocks of 128
 //               keys into 2-stage rings
-//   warp 9      MMA issuer: S_t = Q_t K^T (128x128xD, operands in shared memory),
+//   warp 17     MMA issuer: S_t = Q_t K^T (128x128xD, operands in shared memory),
 //               O_t += P_t V (128xDx128, P read from TMEM)
-//   warps 10-11 idle: they complete the third warpgroup, which hands most of its registers to
-//               the softmax warpgroups (setmaxnreg), so that a softmax thread can hold a whole
-//               row of scores: with more warps (and the row split between two threads) every key block
-// cost a second TMEM read of the scores and an exchange of half-row maxima through shared
-// memory behind a named barrier, and the softmax of a tile - which sits on the critical path
-// S -> P -> P.V -> next S - took about twice the 1024 cycles its exponentials need.
 // The running max used for the exponentials only advances when it grew by more
 // than 8 (log2 units): P stays <= 256 and most iterations skip the O rescale in
-// TMEM; O/l at the end is exact either way.
+// TMEM; O/l at the end is exact either way.  The element-wise code is kept short
+// (64 columns per thread, no full unrolling over the row): straight-line code for a
+// whole row does not stay resident in the instruction cache and ran 1.6x slower.
+// Measured against this arrangement and slower on causal shapes (6 % at S4096, equal without a
+// mask): eight softmax warps with one thread per row and the whole row in registers (registers
+// traded between warpgroups, the exponential pass ordered by hand) - no exchange of maxima and
+// one TMEM read per block, but one warp per scheduler instead of two wherever a tile works
+// alone (the first and last blocks of every item, a quarter of a causal item), and four times
+// the straight-line code.
 //
 // TMEM columns: S_0 | S_1 | O_0 | O_1.
 // HBM layout: Q, K, V, O [BH, S, D] with D contiguous (stride_seq == D),
@@ -49,16 +52,9 @@ using namespace ptx;
 
 constexpr int BLOCK_M = 128, BLOCK_N = 128;
 constexpr int TILES = 2;                       // query tiles per CTA
-constexpr int NUM_THREADS = 384;                // 8 softmax warps + a warpgroup holding the TMA and MMA warps
-constexpr int LOAD_WARP = 8, MMA_WARP = 9;
-// Registers per thread after the warpgroups have traded.  The CTA owns what it was launched
-// with - LAUNCH_REGS per thread for three warpgroups - and setmaxnreg.inc WAITS, without any
-// bound, until the registers it asks for are free in that pool: the two softmax warpgroups may
-// only take what the third one gives up, or the kernel never starts.
-constexpr int LAUNCH_REGS = 168;                // what ptxas allots at 384 threads per CTA
-constexpr int SOFTMAX_REGS = 208, ISSUE_REGS = 88;
-static_assert(2 * SOFTMAX_REGS + ISSUE_REGS <= 3 * LAUNCH_REGS, "setmaxnreg.inc would wait for ever");
-static_assert(SOFTMAX_REGS % 8 == 0 && ISSUE_REGS % 8 == 0, "setmaxnreg takes multiples of 8");
+constexpr int NUM_THREADS = 576;                // 16 softmax warps + TMA warp + MMA warp
+constexpr int LOAD_WARP = 16, MMA_WARP = 17;
+constexpr int HALF_N = BLOCK_N / 2;             // columns of a score tile owned by one softmax group
 constexpr int TMEM_COLS = 512;
 constexpr float kLog2e = 1.44269504088896340736f;
 constexpr float kRescaleThreshold = 8.0f;
@@ -72,6 +68,8 @@ struct Shared {
   alignas(8) uint64_t q_full, q_empty;
   alignas(8) uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   alignas(8) uint64_t s_full[TILES], p_full[TILES], pv_done[TILES];
+  float half_max[TILES][2][2][BLOCK_M];   // [tile][block parity][column half][row]
+  float half_sum[TILES][2][BLOCK_M];      // [tile][column half][row]
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -94,67 +92,44 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// ---- softmax of one row of a 128-column score tile ---------------------------------
-// The row sits in four register arrays of 32 scores (one tcgen05.ld each).
+// ---- softmax passes over one 128-column score tile in TMEM ------------------------
+// Both passes are written as short loops (two 32-column chunks per trip, the next chunk's
+// tcgen05.ld in flight while the current one is processed) rather than fully unrolled:
+// the softmax warps execute this code once per key block, and straight-line code for 128
+// columns does not stay resident in the instruction cache.
 struct MaskInfo {
-  int n0, q_row, n_ctx, causal;     // n0: key of column 0
+  int n0, q_row, n_ctx, causal;
   __device__ __forceinline__ bool masked(int col) const {
     const int key = n0 + col;
     return key >= n_ctx || (causal && key > q_row);
   }
 };
 
+// Row max of this thread's 64 columns (raw scores).
 template <bool MASKED>
-__device__ __forceinline__ float max_chunk(const uint32_t (&r)[32], int col0, const MaskInfo& mi) {
+__device__ __forceinline__ float max_half(uint32_t s_tmem, const MaskInfo& mi) {
+  uint32_t ra[32], rb[32];
+  tmem_ld_32x32(s_tmem, ra);
+  tmem_ld_32x32(s_tmem + 32, rb);
+  tmem_ld_wait();
   float m0 = -INFINITY, m1 = -INFINITY;
-  if (!MASKED) {
-    // four independent chains of three-input maxima (the four chunks of a row make sixteen)
-    float m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 32; i += 8) {
-      m0 = max3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-      m1 = max3(m1, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-      m2 = max3(m2, __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
-      m3 = max3(m3, __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
-    }
-    return max3(m0, m1, fmaxf(m2, m3));
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      if (!mi.masked(col0 + i)) m0 = fmaxf(m0, __uint_as_float(r[i]));
-      if (!mi.masked(col0 + i + 1)) m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
-    }
+  for (int i = 0; i < 32; ++i) {
+    if (!MASKED || !mi.masked(i)) m0 = fmaxf(m0, __uint_as_float(ra[i]));
+    if (!MASKED || !mi.masked(32 + i)) m1 = fmaxf(m1, __uint_as_float(rb[i]));
   }
   return fmaxf(m0, m1);
 }
 
 // P = exp2(s*qk_scale + neg_m) for 32 columns, rounded to T and written to `dst` (16 packed
-// columns); returns the fp32 sum.  Off the mask boundary the scaling and the row sum run two
-// wide (fma.f32x2 / add.f32x2): per element that leaves half an fma, the exponential, half an
-// add and half a conversion.
+// columns); returns the fp32 sum.  The special-function unit runs at about 80% of its rate
+// over the whole kernel (16384 exponentials per score tile).  Moving one exponential in 2, 4
+// or 8 to a cubic on the FMA pipe, and taking two at a time in the 16-bit type, were all
+// measured equal or slower: the extra instructions cost as much issue time as they save.
 template <typename T, bool MASKED>
 __device__ __forceinline__ float exp_chunk(const uint32_t (&r)[32], uint32_t dst, float qk_scale,
                                            float neg_m, int col0, const MaskInfo& mi) {
   uint32_t packed[16];
-  if (!MASKED) {
-    const uint64_t scale2 = pack_f32x2(qk_scale, qk_scale), neg_m2 = pack_f32x2(neg_m, neg_m);
-    uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
-#pragma unroll
-    for (int i = 0; i < 32; i += 4) {
-      float x0, x1, x2, x3;
-      unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), scale2, neg_m2), x0, x1);
-      unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])), scale2, neg_m2), x2, x3);
-      const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
-      acc0 = add_f32x2(acc0, pack_f32x2(p0, p1));
-      acc1 = add_f32x2(acc1, pack_f32x2(p2, p3));
-      packed[i / 2] = pack2<T>(p0, p1);
-      packed[i / 2 + 1] = pack2<T>(p2, p3);
-    }
-    tmem_st_32x16(dst, packed);
-    float a, b;
-    unpack_f32x2(add_f32x2(acc0, acc1), a, b);
-    return a + b;
-  }
   float s0 = 0.f, s1 = 0.f;
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
@@ -162,8 +137,10 @@ __device__ __forceinline__ float exp_chunk(const uint32_t (&r)[32], uint32_t dst
     const float x1 = fmaf(__uint_as_float(r[i + 1]), qk_scale, neg_m);
     float p0 = fast_exp2(x0);
     float p1 = fast_exp2(x1);
-    if (mi.masked(col0 + i)) p0 = 0.f;
-    if (mi.masked(col0 + i + 1)) p1 = 0.f;
+    if (MASKED) {
+      if (mi.masked(col0 + i)) p0 = 0.f;
+      if (mi.masked(col0 + i + 1)) p1 = 0.f;
+    }
     s0 += p0;
     s1 += p1;
     packed[i / 2] = pack2<T>(p0, p1);
@@ -172,119 +149,22 @@ __device__ __forceinline__ float exp_chunk(const uint32_t (&r)[32], uint32_t dst
   return s0 + s1;
 }
 
-// ---- the plain score block, scheduled by hand -----------------------------------------
-// A softmax warp is alone on its scheduler while it works (the other tile's warp waits for its
-// scores), it issues in order, and every exponential costs the special-function unit 8 cycles:
-// the exponentials of a row take 1024 cycles at best, and they only do if an ex2 is issued
-// every 8 cycles with the scaling of later elements and the sum / rounding of earlier ones
-// filling the slots in between.  Left to the compiler the pass took about 1800 cycles (the
-// dependent instructions of one element end up back to back and wait for each other), so the
-// order is fixed here: every statement is a volatile asm, which the compiler keeps in sequence.
-// Values are transformed in place (score -> scaled score -> probability).
-__device__ __forceinline__ void scale_pair(uint32_t& a, uint32_t& b, uint64_t scale2, uint64_t neg_m2) {
-  asm volatile(
-      "{\n.reg .b64 t;\nmov.b64 t, {%0, %1};\nfma.rn.f32x2 t, t, %2, %3;\nmov.b64 {%0, %1}, t;\n}"
-      : "+r"(a), "+r"(b)
-      : "l"(scale2), "l"(neg_m2));
-}
-__device__ __forceinline__ void exp2_inplace(uint32_t& a) {
-  asm volatile("ex2.approx.ftz.f32 %0, %0;" : "+r"(a));
-}
-__device__ __forceinline__ void sum_pair(uint64_t& acc, uint32_t a, uint32_t b) {
-  asm volatile("{\n.reg .b64 t;\nmov.b64 t, {%1, %2};\nadd.rn.f32x2 %0, %0, t;\n}" : "+l"(acc) : "r"(a), "r"(b));
-}
-template <typename T> __device__ __forceinline__ uint32_t round_pair(uint32_t lo, uint32_t hi);
-template <> __device__ __forceinline__ uint32_t round_pair<__nv_bfloat16>(uint32_t lo, uint32_t hi) {
-  uint32_t d;
-  asm volatile("cvt.rn.bf16x2.f32 %0, %2, %1;" : "=r"(d) : "r"(lo), "r"(hi));
-  return d;
-}
-template <> __device__ __forceinline__ uint32_t round_pair<__half>(uint32_t lo, uint32_t hi) {
-  uint32_t d;
-  asm volatile("cvt.rn.f16x2.f32 %0, %2, %1;" : "=r"(d) : "r"(lo), "r"(hi));
-  return d;
-}
-
-// P = exp2(s * qk_scale + neg_m) over a whole row (four 32-column chunks), rounded and written
-// to `dst` (64 packed columns); returns the fp32 row sum.  LAG pairs separate an ex2 from the
-// instructions that consume its result.
-template <typename T>
-__device__ __forceinline__ float exp_row_plain(uint32_t (&s0)[32], uint32_t (&s1)[32], uint32_t (&s2)[32],
-                                               uint32_t (&s3)[32], uint32_t dst, float qk_scale, float neg_m) {
-  constexpr int LAG = 4;
-  const uint64_t scale2 = pack_f32x2(qk_scale, qk_scale), neg_m2 = pack_f32x2(neg_m, neg_m);
-  uint64_t acc0 = pack_f32x2(0.f, 0.f), acc1 = acc0;
-  uint32_t packed[64];
-  auto elem = [&](int i) -> uint32_t& {          // element i of the row, 0 ... 127
-    return i < 32 ? s0[i] : (i < 64 ? s1[i - 32] : (i < 96 ? s2[i - 64] : s3[i - 96]));
-  };
-  // scale the first LAG + 2 pairs ahead of the exponentials
-#pragma unroll
-  for (int q = 0; q < LAG + 2; ++q) scale_pair(elem(2 * q), elem(2 * q + 1), scale2, neg_m2);
-#pragma unroll
-  for (int q = 0; q < 64 + LAG; ++q) {
-    if (q < 64) {
-      exp2_inplace(elem(2 * q));
-      if (q + LAG + 2 < 64) scale_pair(elem(2 * (q + LAG + 2)), elem(2 * (q + LAG + 2) + 1), scale2, neg_m2);
-      exp2_inplace(elem(2 * q + 1));
-    }
-    if (q >= LAG) {
-      const int d = q - LAG;                       // the pair whose exponentials have had time to finish
-      if (d & 1) sum_pair(acc1, elem(2 * d), elem(2 * d + 1));
-      else sum_pair(acc0, elem(2 * d), elem(2 * d + 1));
-      packed[d] = round_pair<T>(elem(2 * d), elem(2 * d + 1));
-      if (d % 16 == 15) {                           // a chunk of P is complete: store it
-        uint32_t out[16];
-#pragma unroll
-        for (int k = 0; k < 16; ++k) out[k] = packed[d - 15 + k];
-        tmem_st_32x16(dst + (d / 16) * 16, out);
-      }
-    }
-  }
-  float a, b;
-  unpack_f32x2(add_f32x2(acc0, acc1), a, b);
-  return a + b;
-}
-
-// The chunk of a diagonal block that the diagonal itself crosses: row `lane` of the warp keeps
-// columns 0 ... lane of the chunk (key <= query), the others are masked.
-__device__ __forceinline__ float max_chunk_diag(const uint32_t (&r)[32], int lane) {
-  float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    if (i <= lane) m0 = fmaxf(m0, __uint_as_float(r[i]));
-    if (i + 1 <= lane) m1 = fmaxf(m1, __uint_as_float(r[i + 1]));
-  }
-  return fmaxf(m0, m1);
-}
-template <typename T>
-__device__ __forceinline__ float exp_chunk_diag(const uint32_t (&r)[32], uint32_t dst, float qk_scale, float neg_m,
-                                                int lane) {
-  uint32_t packed[16];
-  float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), qk_scale, neg_m));
-    float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), qk_scale, neg_m));
-    if (i > lane) p0 = 0.f;
-    if (i + 1 > lane) p1 = 0.f;
-    s0 += p0;
-    s1 += p1;
-    packed[i / 2] = pack2<T>(p0, p1);
-  }
-  tmem_st_32x16(dst, packed);
-  return s0 + s1;
-}
-__device__ __forceinline__ void zero_chunk(uint32_t dst) {
-  uint32_t packed[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) packed[i] = 0u;
-  tmem_st_32x16(dst, packed);
+// Exponentials of this thread's 64 columns; P goes back over the first 32 of them.
+template <typename T, bool MASKED>
+__device__ __forceinline__ float exp_half(uint32_t s_tmem, float qk_scale, float neg_m, const MaskInfo& mi) {
+  uint32_t ra[32], rb[32];
+  tmem_ld_32x32(s_tmem, ra);
+  tmem_ld_32x32(s_tmem + 32, rb);
+  tmem_ld_wait();
+  float sum = exp_chunk<T, MASKED>(ra, s_tmem, qk_scale, neg_m, 0, mi);
+  sum += exp_chunk<T, MASKED>(rb, s_tmem + 16, qk_scale, neg_m, 32, mi);
+  return sum;
 }
 
 // ---- persistent schedule -------------------------------------------------------------
 // A CTA walks its own list of work items (attn_schedule.h): item = one (batch, head) and one
 // 256-row query block.  All three roles read the same list.
+
 template <typename T, int D, uint32_t FMT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -322,7 +202,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     for (int t = 0; t < TILES; ++t) {
       mbar_init(smem_u32(&ss.s_full[t]), 1);
-      mbar_init(smem_u32(&ss.p_full[t]), 4);
+      mbar_init(smem_u32(&ss.p_full[t]), 8);
       mbar_init(smem_u32(&ss.pv_done[t]), 1);
     }
     ss.abort_flag = 0;
@@ -340,8 +220,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   // All three roles walk the same sequence of query blocks.  Barrier phases follow running
   // counters that never reset: `item` counts query blocks, `g` key blocks through the K/V
   // rings, `c` score blocks of one tile.
-  if (warp >= LOAD_WARP) {
-  warpgroup_reg_dec<ISSUE_REGS>();
   if (warp == LOAD_WARP) {
     // ---------------------------------------------------------------- loads
     if (lane == 0) {
@@ -412,7 +290,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * HALF_BYTES + (kk % 4) * 32;
-          mma_f16_ss_elect(tmem + S_COL + t * BLOCK_N, qb.at_here(off), kb.at_here(off), idesc_qk, kk != 0);
+          mma_f16_ss_elect(tmem + S_COL + t * BLOCK_N, qb.at(off), kb.at(off), idesc_qk, kk != 0);
         }
         mma_commit_elect(smem_u32(&ss.s_full[t]));
       };
@@ -457,11 +335,12 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const SmemDesc vb = v_desc.advanced(s * TILE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-                  // P: TMEM operand, 16 keys = 8 packed 32-bit columns from the start of the score
-                  // buffer.  V: MN-major, 16 keys = 2048 bytes further, 64-column halves
-                  // HALF_BYTES apart.
-                  mma_f16_ts_elect(tmem + O_COL + t * D, tmem + S_COL + t * BLOCK_N + kk * 8,
-                             vb.at_here(kk * 2048), idesc_pv, (j | kk) != 0);
+                  // P: TMEM operand, 16 keys = 8 packed 32-bit columns; keys 0-63 sit at the start
+                  // of the score buffer, keys 64-127 at its column 64 (one piece per softmax group).
+                  // V: MN-major, 16 keys = 2048 bytes further, 64-column halves HALF_BYTES apart.
+                  mma_f16_ts_elect(tmem + O_COL + t * D,
+                             tmem + S_COL + t * BLOCK_N + (kk / 4) * HALF_N + (kk % 4) * 8,
+                             vb.at(kk * 2048), idesc_pv, (j | kk) != 0);
                 }
                 // O_t is only read after the last block; rescales in between are ordered by the
                 // next s_full (a commit covers every MMA issued before it, P.V(j) included)
@@ -485,18 +364,20 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
     }
-  }
   } else {
-    warpgroup_reg_inc<SOFTMAX_REGS>();
     // ---------------------------------------------------------------- softmax
-    // Tile t = warp / 4; thread = query row = TMEM lane; the whole row of a score block lives
-    // in this thread's registers between the max and the exponentials.
-    const int t = warp / 4;
+    // Tile t = warp / 8; within a tile, warps 0-3 own columns 0-63 of every score block and
+    // warps 4-7 columns 64-127.  The two threads that share a row exchange their half-row
+    // maxima through shared memory once per block and otherwise work independently (each
+    // keeps a partial row sum; the halves are added at the end).
+    const int t = warp / 8;
+    const int half = (warp / 4) & 1;
     const int row_in_tile = (warp % 4) * 32 + lane;
     const uint32_t lane_addr = (uint32_t)((warp % 4) * 32) << 16;
-    const uint32_t s_tmem = tmem + lane_addr + S_COL + t * BLOCK_N;
-    const uint32_t o_tmem = tmem + lane_addr + O_COL + t * D;
+    const uint32_t s_tmem = tmem + lane_addr + S_COL + t * BLOCK_N + half * HALF_N;
+    const uint32_t o_tmem = tmem + lane_addr + O_COL + t * D + half * (D / 2);
     const float qk_scale = prm.sm_scale * kLog2e;
+    const int pair_barrier = 1 + t;               // named barrier of the tile's 256 threads
     uint32_t c = 0;                               // score blocks this tile has consumed
     uint32_t item = 0;                            // query blocks done (phase of pv_done)
     bool ok = true;
@@ -507,41 +388,23 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int q_row = m0 + t * BLOCK_M + row_in_tile;
         const int my_blocks = key_blocks(m0, t);
         float m_used = -INFINITY, l = 0.f;
-        for (int j = 0; j < my_blocks; ++j, ++c) {
-          if (!mbar_wait(smem_u32(&ss.s_full[t]), c & 1, wc, kSoftS)) { ok = false; break; }
+        for (int j = 0; j < my_blocks && ok; ++j, ++c) {
+          // A wait that gave up is not acted on alone: the flag goes through the tile's named
+          // barrier below, and all 256 threads leave in this same iteration.
+          const bool got = mbar_wait(smem_u32(&ss.s_full[t]), c & 1, wc, kSoftS);
           tc_fence_after();
-          uint32_t s0[32], s1[32], s2[32], s3[32];
-          tmem_ld_32x32(s_tmem, s0);
-          tmem_ld_32x32(s_tmem + 32, s1);
-          tmem_ld_32x32(s_tmem + 64, s2);
-          tmem_ld_32x32(s_tmem + 96, s3);
-          tmem_ld_wait();
-          const int n0 = j * BLOCK_N;
-          // Three kinds of block.  Plain: no key is masked.  Diagonal: the block on the causal
-          // diagonal of this tile, all of it inside the sequence - for the rows of this warp the
-          // 32-column chunks left of the diagonal are plain, the chunks right of it are masked as
-          // a whole (P = 0, nothing is computed), and only the chunk the diagonal crosses needs a
-          // test per element.  Ragged: a block that runs past the end of the sequence.
-          const bool ragged = n0 + BLOCK_N > prm.n_ctx;
-          const bool diagonal = !ragged && prm.causal && n0 == m0 + t * BLOCK_M;
-          const int wchunk = warp % 4;                     // the chunk the diagonal crosses for this warp
+          const int n0 = j * BLOCK_N + half * HALF_N;
+          const bool boundary = (n0 + HALF_N > prm.n_ctx) || (prm.causal && n0 + HALF_N > m0 + t * BLOCK_M);
           const MaskInfo mi{n0, q_row, prm.n_ctx, prm.causal};
-          // row max of the raw scores (qk_scale > 0, so the scaled max is max * qk_scale)
-          float mx;
-          if (ragged) {
-            mx = fmaxf(fmaxf(max_chunk<true>(s0, 0, mi), max_chunk<true>(s1, 32, mi)),
-                       fmaxf(max_chunk<true>(s2, 64, mi), max_chunk<true>(s3, 96, mi)));
-          } else if (diagonal) {
-            mx = wchunk == 0 ? max_chunk_diag(s0, lane) : max_chunk<false>(s0, 0, mi);
-            if (wchunk >= 1) mx = fmaxf(mx, wchunk == 1 ? max_chunk_diag(s1, lane) : max_chunk<false>(s1, 32, mi));
-            if (wchunk >= 2) mx = fmaxf(mx, wchunk == 2 ? max_chunk_diag(s2, lane) : max_chunk<false>(s2, 64, mi));
-            if (wchunk >= 3) mx = fmaxf(mx, max_chunk_diag(s3, lane));
-          } else {
-            mx = fmaxf(fmaxf(max_chunk<false>(s0, 0, mi), max_chunk<false>(s1, 32, mi)),
-                       fmaxf(max_chunk<false>(s2, 64, mi), max_chunk<false>(s3, 96, mi)));
-          }
-          mx *= qk_scale;
-          // advance the working max only when it moved far (or on the first block)
+          // pass 1: max of the raw scores over this half row, then over the whole row
+          // (qk_scale > 0, so the scaled max is max * qk_scale)
+          // (after a failed wait the scores read here are stale: harmless, the block is abandoned)
+          float mx = boundary ? max_half<true>(s_tmem, mi) : max_half<false>(s_tmem, mi);
+          ss.half_max[t][c & 1][half][row_in_tile] = mx;
+          if (!bar_sync_and(pair_barrier, 256, got)) { ok = false; break; }
+          mx = fmaxf(mx, ss.half_max[t][c & 1][half ^ 1][row_in_tile]) * qk_scale;
+          // advance the working max only when it moved far (or on the first block); both
+          // threads of a row see the same numbers and take the same decision
           float alpha = 1.f;
           bool rescale = false;
           if (mx > m_used + kRescaleThreshold) {
@@ -551,9 +414,10 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           }
           if (__any_sync(0xffffffffu, rescale)) {
             // O_t may only be touched once the P.V MMA of block j-1 has finished: it has, the
-            // s_full this thread waited for above was committed after it.
+            // s_full this thread waited for above was committed after it.  Each half rescales
+            // its own D/2 columns of the accumulator.
 #pragma unroll 1
-            for (int cc = 0; cc < D / 32; ++cc) {
+            for (int cc = 0; cc < D / 64; ++cc) {
               uint32_t r[32];
               tmem_ld_32x32(o_tmem + cc * 32, r);
               tmem_ld_wait();
@@ -561,50 +425,31 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
               for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
               tmem_st_32x32(o_tmem + cc * 32, r);
             }
+            tmem_st_wait();
           }
-          // exponentials, row sum, 16-bit P over the first 64 columns of the scores
-          float sum;
-          const float neg_m = -m_used;
-          if (ragged) {
-            sum = exp_chunk<T, true>(s0, s_tmem, qk_scale, neg_m, 0, mi) +
-                  exp_chunk<T, true>(s1, s_tmem + 16, qk_scale, neg_m, 32, mi);
-            sum += exp_chunk<T, true>(s2, s_tmem + 32, qk_scale, neg_m, 64, mi) +
-                   exp_chunk<T, true>(s3, s_tmem + 48, qk_scale, neg_m, 96, mi);
-          } else if (diagonal) {
-            sum = wchunk == 0 ? exp_chunk_diag<T>(s0, s_tmem, qk_scale, neg_m, lane)
-                              : exp_chunk<T, false>(s0, s_tmem, qk_scale, neg_m, 0, mi);
-            if (wchunk >= 1) {
-              sum += wchunk == 1 ? exp_chunk_diag<T>(s1, s_tmem + 16, qk_scale, neg_m, lane)
-                                 : exp_chunk<T, false>(s1, s_tmem + 16, qk_scale, neg_m, 32, mi);
-            } else {
-              zero_chunk(s_tmem + 16);
-            }
-            if (wchunk >= 2) {
-              sum += wchunk == 2 ? exp_chunk_diag<T>(s2, s_tmem + 32, qk_scale, neg_m, lane)
-                                 : exp_chunk<T, false>(s2, s_tmem + 32, qk_scale, neg_m, 64, mi);
-            } else {
-              zero_chunk(s_tmem + 32);
-            }
-            if (wchunk >= 3) sum += exp_chunk_diag<T>(s3, s_tmem + 48, qk_scale, neg_m, lane);
-            else zero_chunk(s_tmem + 48);
-          } else {
-            sum = exp_row_plain<T>(s0, s1, s2, s3, s_tmem, qk_scale, neg_m);
-          }
+          // pass 2: exponentials, partial row sum, 16-bit P over the scores already read
+          const float sum = boundary ? exp_half<T, true>(s_tmem, qk_scale, -m_used, mi)
+                                     : exp_half<T, false>(s_tmem, qk_scale, -m_used, mi);
           l = l * alpha + sum;
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&ss.p_full[t]));   // one arrival per warp
         }
-        // ---- O / l and the row statistic of this query block
+        // ---- whole-row sum, O / l and the row statistic of this query block
+        ss.half_sum[t][half][row_in_tile] = l;
+        // the last P.V must have retired before O is read; the outcome of that wait, too, is
+        // agreed on by the whole tile at the barrier that publishes the half-row sums
         if (ok && my_blocks > 0) ok = mbar_wait(smem_u32(&ss.pv_done[t]), item & 1, wc, kSoftFinal);
+        ok = bar_sync_and(pair_barrier, 256, ok);
+        l += ss.half_sum[t][half ^ 1][row_in_tile];
         tc_fence_after();
         if (ok && my_blocks > 0) {
           const float inv_l = 1.f / l;
           const bool live = q_row < prm.rows;
-          T* orow = (T*)prm.o + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq;
+          T* orow = (T*)prm.o + (int64_t)bh * prm.stride_head + (int64_t)q_row * prm.stride_seq + half * (D / 2);
 #pragma unroll 1
-          for (int cc = 0; cc < D / 32; ++cc) {
+          for (int cc = 0; cc < D / 64; ++cc) {
             uint32_t r[32];
             tmem_ld_32x32(o_tmem + cc * 32, r);
             tmem_ld_wait();
@@ -620,7 +465,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
               }
             }
           }
-          if (live && prm.lse) prm.lse[(int64_t)bh * prm.stride_lse + q_row] = m_used + log2f(l);
+          if (live && half == 0 && prm.lse) prm.lse[(int64_t)bh * prm.stride_lse + q_row] = m_used + log2f(l);
         }
       }
     }

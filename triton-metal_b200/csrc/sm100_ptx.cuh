@@ -201,15 +201,6 @@ struct SmemDesc {
     asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo + (bytes >> 4)), "r"(hi));
     return d;
   }
-  // The same, but formed at the point of use: the compiler cannot hoist it out of a loop, so an
-  // unrolled issue loop does not keep one 64-bit descriptor per instruction alive in registers
-  // (an issuer warp that has given most of its registers away would spill them).
-  __device__ __forceinline__ uint64_t at_here(uint32_t bytes) const {
-    uint64_t d;
-    asm volatile("{\n.reg .b32 t;\nadd.u32 t, %1, %2;\nmov.b64 %0, {t, %3};\n}"
-                 : "=l"(d) : "r"(lo), "r"(bytes >> 4), "r"(hi));
-    return d;
-  }
   __device__ __forceinline__ SmemDesc advanced(uint32_t bytes) const { return SmemDesc{lo + (bytes >> 4), hi}; }
 };
 __device__ __forceinline__ SmemDesc make_desc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -389,15 +380,6 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// Move registers between the warpgroups of a CTA (all four warps of a warpgroup execute it):
-// the roles that only issue copies or MMAs give theirs up, the arithmetic warps take them.
-template <int REGS> __device__ __forceinline__ void warpgroup_reg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
-}
-template <int REGS> __device__ __forceinline__ void warpgroup_reg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
-}
-
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile(
@@ -411,14 +393,8 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 // ---- small numeric helpers shared by the attention kernels -------------------------
-// sm_100 has a three-input max and two-wide fp32 fma / add on 64-bit register pairs: the
-// element-wise passes of the attention kernels are bound by how many instructions a warp can
-// issue per element, and these halve the count of everything but the exponential itself.
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
+// sm_100 has two-wide fp32 fma / add / mul on 64-bit register pairs: they halve the instruction
+// count of everything but the exponential itself in the element-wise passes of the backward.
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t v;
   asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));

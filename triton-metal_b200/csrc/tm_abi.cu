@@ -190,6 +190,7 @@ struct Device {
   uint64_t launch_number = 0, write_number = 0;
   bool async_writes = false;
   std::vector<std::weak_ptr<BufferObj>> read_back;   // buffers with a read-back possibly in flight
+  std::recursive_mutex order_lock;   // guards the ordering state above (callers may be threads)
   DeviceStatus* status = nullptr;   // pinned, device-visible
   cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
   // capability probe
@@ -298,6 +299,7 @@ const std::string& unusable_reason() {
 // (Every caller synchronises the library's stream right afterwards, so the read-backs are
 // complete when it returns and the buffers' marks can go.)
 void join_reads() {
+  std::lock_guard<std::recursive_mutex> guard(g_dev.order_lock);
   if (!g_dev.reads_in_flight) return;
   cudaEventRecord(g_dev.ev_join, g_dev.read_stream);
   cudaStreamWaitEvent(g_dev.stream, g_dev.ev_join, 0);
@@ -453,6 +455,7 @@ void prefetch_exposed(const Decoded& d) {
 // write into one of those buffers will wait for.
 template <typename Buffers>
 void note_launch(const Buffers& buffers) {
+  std::lock_guard<std::recursive_mutex> guard(g_dev.order_lock);
   const uint64_t n = ++g_dev.launch_number;
   for (BufferObj* b : buffers)
     if (b) b->last_launch = n;
@@ -846,6 +849,7 @@ int32_t do_copy(int64_t buffer, int64_t offset, const void* host, int64_t length
   if (length == 0) return 0;
   if (!bind_device(err)) { store_error(err); return -1; }
   char* dev = (char*)b->ptr + offset;
+  std::unique_lock<std::recursive_mutex> guard(g_dev.order_lock);
   cudaStream_t copy_stream = g_dev.stream;
   if (side_stream && !to_device) {
     // after everything enqueued so far, but not in the way of what is enqueued next
@@ -889,6 +893,7 @@ int32_t do_copy(int64_t buffer, int64_t offset, const void* host, int64_t length
     cudaEventRecord(g_dev.write_events[slot], g_dev.write_stream);
     cudaStreamWaitEvent(g_dev.stream, g_dev.write_events[slot], 0);
   }
+  guard.unlock();
   if (wait && !sync_stream(err)) { store_error(err); return -1; }
   return 0;
 }
