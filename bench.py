@@ -101,7 +101,7 @@ def config_of(name, dist=None):
 NCU_TRAFFIC_BYTES = {
     "gemm_bf16_8192": {"bytes": 1075.6e6, "source": "profiles/gemm_tc_bf16_8192.md"},
     "attn_fwd_bf16_s4096": {"bytes": 520.0e6, "source": "profiles/attn_fwd_tc_bf16_s4096_causal.md"},
-    "attn_fwd_bf16_s4096_full": {"bytes": 518.5e6, "source": "profiles/attn_fwd_tc_bf16_s4096_causal.md"},
+    "attn_fwd_bf16_s4096_full": {"bytes": 517.7e6, "source": "profiles/attn_fwd_tc_bf16_s4096_causal.md"},
     # dq 662.9 MB + dkdv 775.9 MB + preprocess 273.9 MB
     "attn_bwd_bf16_s4096_d128": {"bytes": 1712.7e6, "source": "profiles/attn_bwd_tc_bf16_s4096_d128_causal.md"},
     # dq 329.8 MB + dkdv 377.6 MB; the preprocess pass (O and dO once: 134 MB) was not captured at D=64
