@@ -103,6 +103,12 @@ struct MaskInfo {
     const int key = n0 + col;
     return key >= n_ctx || (causal && key > q_row);
   }
+  // Every column from `col` on is masked for all 32 rows of this warp (which start at a multiple
+  // of 32): right of the causal diagonal, or past the end of the sequence.  Uniform over the warp.
+  __device__ __forceinline__ bool all_masked_from(int col) const {
+    const int key = n0 + col;
+    return key >= n_ctx || (causal && key > (q_row | 31));
+  }
 };
 
 // Row max of this thread's 64 columns (raw scores).
@@ -131,6 +137,13 @@ __device__ __forceinline__ float exp_chunk(const uint32_t (&r)[32], uint32_t dst
                                            float neg_m, int col0, const MaskInfo& mi) {
   uint32_t packed[16];
   float s0 = 0.f, s1 = 0.f;
+  if (MASKED && mi.all_masked_from(col0)) {
+    // nothing of this chunk survives for any row of the warp: P = 0 without the exponentials
+#pragma unroll
+    for (int i = 0; i < 16; ++i) packed[i] = 0u;
+    tmem_st_32x16(dst, packed);
+    return 0.f;
+  }
 #pragma unroll
   for (int i = 0; i < 32; i += 2) {
     const float x0 = fmaf(__uint_as_float(r[i]), qk_scale, neg_m);
