@@ -393,8 +393,14 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 // ---- small numeric helpers shared by the attention kernels -------------------------
-// sm_100 has two-wide fp32 fma / add / mul on 64-bit register pairs: they halve the instruction
-// count of everything but the exponential itself in the element-wise passes of the backward.
+// sm_100 has a three-input max and two-wide fp32 fma / add / mul on 64-bit register pairs: they
+// halve the instruction count of everything but the exponential itself in the element-wise passes
+// of the attention kernels.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   uint64_t v;
   asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
