@@ -380,3 +380,34 @@ def test_launch_waits_for_a_read_back_of_its_output(core):
         mm.release()
         for h in a_bufs + [b_buf, c_buf]:
             core.free_buffer(h)
+
+
+def test_async_write_behind_a_launch_older_than_the_event_ring(core):
+    """The upload stream waits for the event of the last launch that took the buffer; only the last
+    64 launches keep theirs.  A buffer last used 100 launches ago falls back to waiting for
+    everything enqueued so far - its new contents must still arrive after that old launch and
+    before the next one that reads it."""
+    from triton_metal import kernels
+    n = 1 << 22
+    copy = kernels.Elementwise("copy")
+    src, mid, out, other_in, other_out = (core.alloc_buffer(4 * n) for _ in range(5))
+    first = np.arange(n, dtype=np.float32)
+    second = first[::-1].copy()
+    try:
+        core.buffer_write(src, 0, first.ctypes.data, first.nbytes)
+        core.buffer_write(other_in, 0, first.ctypes.data, first.nbytes)
+        copy.launch_async(*copy.arguments(src, mid, n=n))             # reads src
+        for _ in range(100):                                          # pushes that launch out of the ring
+            copy.launch_async(*copy.arguments(other_in, other_out, n=n))
+        cuda.write_async(src, 0, second.ctypes.data, second.nbytes)   # must not land before the first copy
+        copy.launch_async(*copy.arguments(src, out, n=n))             # must see the new contents
+        cuda.synchronize()
+        got_mid, got_out = np.empty(n, dtype=np.float32), np.empty(n, dtype=np.float32)
+        core.buffer_read(mid, 0, got_mid.ctypes.data, got_mid.nbytes)
+        core.buffer_read(out, 0, got_out.ctypes.data, got_out.nbytes)
+        assert np.array_equal(got_mid, first)
+        assert np.array_equal(got_out, second)
+    finally:
+        copy.release()
+        for h in (src, mid, out, other_in, other_out):
+            core.free_buffer(h)
