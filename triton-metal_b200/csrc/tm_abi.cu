@@ -1552,6 +1552,9 @@ int32_t tmx_matmul_gathered(int64_t kernel, int64_t a, int64_t b, const int64_t*
   g.wait_for_peers = wait_for_peers;
   g.wait_budget_cycles = 0;
   if (const char* env = std::getenv("TMCUDA_GATHER_WAIT_CYCLES")) g.wait_budget_cycles = std::atoll(env);
+  // finished tiles leave through TMA stores; $TMCUDA_GATHER_TMA_STORE=0 selects plain st.global
+  g.tma_store = 1;
+  if (const char* env = std::getenv("TMCUDA_GATHER_TMA_STORE")) g.tma_store = std::atoi(env) != 0;
   std::string e = launch_gemm_tc_gathered(p, g, launch_ctx());
   if (!e.empty()) return fail(cuda_error(e));
   k->last_path = 2;

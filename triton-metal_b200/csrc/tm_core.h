@@ -164,6 +164,7 @@ struct GemmGather {
   uint32_t epoch;
   int wait_for_peers;
   long long wait_budget_cycles;   // 0: the library's default (about a second)
+  int tma_store;                  // tiles leave through TMA stores instead of st.global
 };
 std::string launch_gemm_tc_gathered(const GemmProblem& p, const GemmGather& g, const LaunchCtx& ctx);
 // fp32 operands: 3xTF32 on the tensor cores, operands split into scratch memory.
